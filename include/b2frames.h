@@ -1,0 +1,206 @@
+/*
+ * b2frames -- C ABI of the B200 post-decode frame path.
+ *
+ * One shared library, libb2frames.so, built for sm_100a.  Plain pointers and
+ * sizes only; no C++ or torch types cross this boundary.  Each entry point names
+ * the piece of facebookresearch/spdl it stands in for (path within that project).
+ *
+ * Conventions
+ *   - Every function returns 0 on success.  On failure it returns a non-zero
+ *     B2_ERR_* code and b2_last_error() gives a message for the calling thread.
+ *     (The reference throws std::runtime_error from the same places; a binding
+ *     turns the status into the host language's exception.)
+ *   - Pointers named src/dst/base/descs are DEVICE pointers unless stated.
+ *   - `stream` is a cudaStream_t passed as void*; 0x2 is the per-thread default
+ *     stream (the reference's default, src/libspdl/cuda/types.h:32-39).
+ *   - Work is enqueued on `stream` and the call returns without waiting unless
+ *     the function says otherwise.  Inputs must stay alive until the stream has
+ *     run past the call.
+ *   - Re-entrant: no global mutable state; a call that takes `device` makes that
+ *     device current for its duration and restores the caller's device.
+ */
+#ifndef B2FRAMES_H_
+#define B2FRAMES_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B2_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define B2_API __attribute__((visibility("default")))
+#else
+#define B2_API
+#endif
+
+enum b2_status {
+  B2_OK = 0,
+  B2_ERR_INVALID = 1, /* bad argument (shape, alignment of a required field, null pointer) */
+  B2_ERR_CUDA = 2,    /* a CUDA runtime call failed; message holds the CUDA error name       */
+  B2_ERR_LIMIT = 3    /* a size is beyond a stated maximum                                   */
+};
+
+enum b2_src_format { B2_SRC_NV12 = 0, B2_SRC_I420 = 1 };
+enum b2_layout { B2_NCHW = 0, B2_NHWC = 1 };
+enum b2_dtype { B2_U8 = 0, B2_F32 = 1, B2_BF16 = 2 };
+enum b2_order { B2_RGB = 0, B2_BGR = 1 };
+
+/* Message for the last failure on the calling thread ("" if none). */
+B2_API const char* b2_last_error(void);
+B2_API int b2_abi_version(void);
+
+/* Create/attach the primary context of `device`.
+ * Replaces spdl::cuda::init_cuda (src/libspdl/cuda/utils.cpp:25-37). */
+B2_API int b2_init(int device);
+B2_API int b2_device_count(int* count);
+
+/* Wait for `stream` on `device`.
+ * Replaces spdl::cuda::synchronize_stream (src/libspdl/cuda/utils.cpp:39-43). */
+B2_API int b2_stream_synchronize(int device, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Colour conversion, reference signature.
+ *
+ * Drop-in for spdl::cuda::detail::nv12_to_planar_rgb / nv12_to_planar_bgr
+ * (src/libspdl/cuda/detail/color_conversion.cu:155-193; the function-pointer type
+ * Nv2Converter at src/libspdl/cuda/color_conversion.cpp:24-25).  Same argument
+ * order and meaning: `src` holds num_frames packed NV12 frames of
+ * (height + height/2) rows, rows `src_pitch` bytes apart, frames
+ * (height + height/2) * width bytes apart; `dst` receives planar u8
+ * [num_frames, 3, height, width], rows `dst_pitch` apart, planes
+ * height * dst_pitch apart, frames 3 * height * width apart.
+ * matrix_coefficients outside 1..10 means 1 (BT.709).  Runs on the current device.
+ * A trailing odd column or row is left untouched, as in the reference.
+ * ---------------------------------------------------------------------------------------- */
+B2_API int b2_nv12_to_planar_rgb(void* stream, const uint8_t* src, int src_pitch, uint8_t* dst,
+                          int dst_pitch, int width, int height, int num_frames,
+                          int matrix_coefficients);
+B2_API int b2_nv12_to_planar_bgr(void* stream, const uint8_t* src, int src_pitch, uint8_t* dst,
+                          int dst_pitch, int width, int height, int num_frames,
+                          int matrix_coefficients);
+
+/* ------------------------------------------------------------------------------------------
+ * Colour conversion, general form (same arithmetic, more layouts).
+ *
+ * Covers what the reference does in separate passes around its kernel: the
+ * planar->interleaved permute and the float()/255, (x-mean)/std, .to(bf16) that
+ * user code applies afterwards (examples/imagenet_classification.py:95-106), and
+ * planar-chroma (I420) input as produced by convert_frames for yuv420p
+ * (src/libspdl/core/detail/ffmpeg/conversion.cpp:218-260).
+ *
+ * out[slot] = value(channel(slot)) * scale[slot] + bias[slot] for float outputs
+ * (one fused multiply-add in fp32; bf16 rounds that to nearest even); u8 outputs
+ * ignore scale/bias.  slot order is R,G,B or B,G,R per `order`.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct b2_dense_args {
+  uint32_t struct_size;     /* sizeof(b2_dense_args), for forward compatibility            */
+  int32_t device;
+  const void* y;            /* luma of frame 0                                              */
+  const void* u;            /* NV12: interleaved UV plane of frame 0; I420: U plane         */
+  const void* v;            /* I420: V plane; NV12: ignored                                 */
+  /* Optional pointer table (device memory, num_frames entries each) for frames that do not
+   * sit at a fixed stride, e.g. decoder surfaces.  When y_table is non-null the kernel takes
+   * frame i's planes from y_table[i], u_table[i] (and v_table[i]) and ignores y/u/v and the
+   * frame strides. */
+  const void* const* y_table;
+  const void* const* u_table;
+  const void* const* v_table;
+  int64_t y_pitch, uv_pitch;              /* bytes between rows                             */
+  int64_t y_frame_stride, uv_frame_stride; /* bytes between frames                          */
+  int32_t src_format;       /* b2_src_format                                                */
+  int32_t width, height, num_frames;
+  int32_t matrix_coeff;     /* 1..10, else 1                                                */
+  int32_t full_range;       /* 0: limited range (the reference); 1: full range, no offset   */
+  void* dst;
+  int64_t dst_frame_stride; /* elements between frames; 0 = packed (3*height*width)         */
+  int32_t layout, dtype, order;
+  float scale[3], bias[3];
+} b2_dense_args;
+
+B2_API int b2_convert_dense(const b2_dense_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Fused convert -> bilinear resize -> crop -> scale/bias over a ragged batch.
+ *
+ * Stands in for the resize that follows decode in the reference -- NPP resize
+ * (src/libspdl/cuda/npp/detail/resize.cpp:37-116), the NVDEC crop/scale
+ * parameters (src/libspdl/cuda/nvdec/detail/utils.cpp:133-220) and the
+ * scale/crop filter strings (src/spdl/io/_preprocessing.py:122-254) -- fused
+ * with the colour conversion above and the normalise of user code.  Filter:
+ * bilinear, half-pixel centres, no antialias.  Each image has a descriptor; all
+ * images write an out_h x out_w result.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct b2_image_desc {
+  uint64_t y_off, u_off, v_off; /* byte offsets of the planes from `base`                   */
+  int32_t y_pitch, uv_pitch;
+  int32_t src_w, src_h;
+  int32_t crop_x, crop_y;       /* where output (0,0) sits in the resized grid              */
+  float scale_x, scale_y;       /* source size / resized size                               */
+  int32_t reserved[2];
+} b2_image_desc;                /* 64 bytes */
+
+typedef struct b2_resize_args {
+  uint32_t struct_size;
+  int32_t device;
+  const void* base;             /* device buffer holding every image                        */
+  const b2_image_desc* descs;   /* device table, num_images entries                         */
+  int32_t num_images, src_format;
+  int32_t out_w, out_h;
+  int32_t matrix_coeff, full_range;
+  int32_t layout, dtype, order;
+  int32_t max_src_w;            /* largest src_w in the table (sizes the staging tile)      */
+  void* dst;
+  int64_t dst_image_stride;     /* elements; 0 = packed                                     */
+  float scale[3], bias[3];
+} b2_resize_args;
+
+B2_API int b2_convert_resize(const b2_resize_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Frame batching.
+ *
+ * Replaces FrameBuffer::push (src/libspdl/cuda/nvdec/detail/buffer.cpp:31-74): copies
+ * `num_frames` pitched NV12 surfaces (device pointer table + pitch table, both in device
+ * memory) into one packed [num_frames, height*3/2, width] batch in a single launch, without
+ * the per-frame stream synchronisation.
+ * ---------------------------------------------------------------------------------------- */
+B2_API int b2_gather_surfaces(const void* const* surfaces, const int64_t* pitches, int num_frames,
+                       int width, int height, uint8_t* dst, int device, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Buffer transfer and storage.
+ *
+ * b2_transfer_h2d replaces transfer_buffer_impl (src/libspdl/cuda/transfer.cpp:37-66):
+ * pinned source -> asynchronous copy on `stream` followed by a stream synchronise;
+ * pageable source -> blocking copy.  b2_transfer_h2d_async is the same copy without the
+ * wait, for callers that overlap transfers.  b2_transfer_d2h replaces the device->host
+ * overload (src/libspdl/cuda/transfer.cpp:91-118): blocking.
+ * b2_alloc_pinned / b2_free_pinned replace alloc_pinned / dealloc_pinned
+ * (src/libspdl/cuda/storage.cpp:22-38); b2_device_alloc / b2_device_free are the default
+ * allocator of CUDAStorage (src/libspdl/cuda/storage.cpp:44-58).
+ * ---------------------------------------------------------------------------------------- */
+B2_API int b2_transfer_h2d(void* dst, const void* host_src, size_t nbytes, int src_is_pinned, int device,
+                    void* stream);
+B2_API int b2_transfer_h2d_async(void* dst, const void* host_src, size_t nbytes, int device,
+                          void* stream);
+B2_API int b2_transfer_d2h(void* host_dst, const void* src, size_t nbytes, int device);
+B2_API int b2_alloc_pinned(void** host_ptr, size_t nbytes);
+B2_API int b2_free_pinned(void* host_ptr);
+B2_API int b2_device_alloc(void** ptr, size_t nbytes, int device);
+B2_API int b2_device_free(void* ptr, int device);
+
+/* Per-frame checksum of a packed byte batch: out[i] = sum over j of
+ * (byte[i][j] + 1) * (1 + j mod 65521), as uint64.  `out` is device memory,
+ * num_frames entries, overwritten.  No counterpart in the reference; used to
+ * verify full-size results without copying them back. */
+B2_API int b2_frame_checksum(const uint8_t* src, int64_t frame_bytes, int num_frames, uint64_t* out,
+                      int device, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B2FRAMES_H_ */

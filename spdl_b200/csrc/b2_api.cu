@@ -1,0 +1,344 @@
+// extern "C" surface of libb2frames.so: argument validation, device selection, error messages.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "b2_common.cuh"
+
+namespace b2 {
+
+int launch_resize(const b2_resize_args& a, cudaStream_t stream);
+int launch_gather(const void* const* surfaces, const int64_t* pitches, int num_frames, int width,
+                  int height, uint8_t* dst, cudaStream_t stream);
+int launch_checksum(const uint8_t* src, int64_t frame_bytes, int num_frames, uint64_t* out,
+                    cudaStream_t stream);
+
+namespace {
+thread_local char g_err[512] = "";
+}
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+int fail_cuda(cudaError_t e, const char* what) {
+  snprintf(g_err, sizeof(g_err), "%s (%s: %s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+  return B2_ERR_CUDA;
+}
+void clear_error() { g_err[0] = 0; }
+
+DeviceGuard::DeviceGuard(int device) {
+  status_ = cudaGetDevice(&prev_);
+  if (status_ == cudaSuccess && prev_ != device) {
+    status_ = cudaSetDevice(device);
+    switched_ = status_ == cudaSuccess;
+  }
+}
+DeviceGuard::~DeviceGuard() {
+  if (switched_) cudaSetDevice(prev_);
+}
+
+// The reference table (src/libspdl/cuda/detail/color_conversion.cu:20-70), one row of five
+// numbers per matrix_coefficients value 1..10: luma gain, V->R, U->G, V->G, U->B.
+static const float kLimited[10][5] = {
+    {1.1644f, 1.8337f, -0.2181f, -0.5451f, 2.1606f},  // 1 BT.709
+    {1.1644f, 1.8337f, -0.2181f, -0.5451f, 2.1606f},  // 2 unspecified
+    {1.1644f, 1.8337f, -0.2181f, -0.5451f, 2.1606f},  // 3 reserved
+    {1.1644f, 1.6301f, -0.3864f, -0.8289f, 2.0726f},  // 4 FCC
+    {1.1644f, 1.6325f, -0.4007f, -0.8315f, 2.0633f},  // 5 BT.470
+    {1.1644f, 1.6325f, -0.4007f, -0.8315f, 2.0633f},  // 6 BT.601
+    {1.1644f, 1.8351f, -0.2639f, -0.5550f, 2.1262f},  // 7 SMPTE 240M
+    {1.1644f, 1.8337f, -0.2181f, -0.5451f, 2.1606f},  // 8 "YCgCo" (BT.709 numbers)
+    {1.1689f, 1.7237f, -0.1924f, -0.6679f, 2.1992f},  // 9 BT.2020
+    {1.1689f, 1.7237f, -0.1924f, -0.6679f, 2.1992f},  // 10 BT.2020 constant luminance
+};
+// Full-range companions (not in the reference): unit luma gain, no luma offset, chroma gains
+// 2(1-Kr), -2Kb(1-Kb)/Kg, -2Kr(1-Kr)/Kg, 2(1-Kb) of each standard, six decimals.
+static const float kFull[10][5] = {
+    {1.0f, 1.574800f, -0.187324f, -0.468124f, 1.855600f},
+    {1.0f, 1.574800f, -0.187324f, -0.468124f, 1.855600f},
+    {1.0f, 1.574800f, -0.187324f, -0.468124f, 1.855600f},
+    {1.0f, 1.400000f, -0.331864f, -0.711864f, 1.780000f},
+    {1.0f, 1.402000f, -0.344136f, -0.714136f, 1.772000f},
+    {1.0f, 1.402000f, -0.344136f, -0.714136f, 1.772000f},
+    {1.0f, 1.576000f, -0.226622f, -0.476622f, 1.826000f},
+    {1.0f, 1.574800f, -0.187324f, -0.468124f, 1.855600f},
+    {1.0f, 1.474600f, -0.164553f, -0.571353f, 1.881400f},
+    {1.0f, 1.474600f, -0.164553f, -0.571353f, 1.881400f},
+};
+
+ColorMat color_matrix(int k, int full_range) {
+  if (k <= 0 || k > 10) k = 1;  // color_conversion.cu:120-123
+  const float* r = full_range ? kFull[k - 1] : kLimited[k - 1];
+  ColorMat m;
+  m.g = r[0]; m.vr = r[1]; m.ug = r[2]; m.vg = r[3]; m.ub = r[4];
+  m.y_bias = 8388608.0f + (full_range ? 0.0f : 16.0f);
+  return m;
+}
+
+namespace {
+
+bool valid_enum(int v, int hi) { return v >= 0 && v <= hi; }
+
+int planar_entry(void* stream, const uint8_t* src, int src_pitch, uint8_t* dst, int dst_pitch,
+                 int width, int height, int num_frames, int coeff, int order) {
+  clear_error();
+  if (width < 0 || height < 0 || num_frames < 0)
+    return fail(B2_ERR_INVALID, "negative size: width %d, height %d, num_frames %d", width, height,
+                num_frames);
+  if (num_frames == 0 || width == 0 || height == 0) return B2_OK;
+  if (!src || !dst) return fail(B2_ERR_INVALID, "null %s pointer", src ? "dst" : "src");
+  if (src_pitch < width || dst_pitch < width)
+    return fail(B2_ERR_INVALID, "pitch smaller than width (%d, %d < %d)", src_pitch, dst_pitch,
+                width);
+  DenseLaunch L{};
+  L.y = src;
+  L.u = src + (long long)height * src_pitch;  // color_conversion.cu:117
+  L.y_pitch = L.uv_pitch = src_pitch;
+  // the reference strides frames by width, not by pitch (color_conversion.cu:106-107)
+  L.y_frame_stride = L.uv_frame_stride = (long long)(height + height / 2) * width;
+  L.src_format = B2_SRC_NV12;
+  L.width = width; L.height = height; L.num_frames = num_frames;
+  L.mat = color_matrix(coeff, 0);
+  L.dst = dst;
+  L.dst_row_pitch = dst_pitch;
+  L.dst_plane_stride = (long long)height * dst_pitch;   // color_conversion.cu:136
+  L.dst_frame_stride = 3LL * height * width;            // color_conversion.cu:107
+  L.layout = B2_NCHW; L.dtype = B2_U8; L.order = order;
+  for (int i = 0; i < 3; ++i) { L.sb.s[i] = 1.0f; L.sb.b[i] = 0.0f; }
+  return launch_dense(L, static_cast<cudaStream_t>(stream));
+}
+
+}  // namespace
+}  // namespace b2
+
+using namespace b2;
+
+extern "C" {
+
+B2_API const char* b2_last_error(void) { return g_err; }
+B2_API int b2_abi_version(void) { return B2_ABI_VERSION; }
+
+B2_API int b2_init(int device) {
+  clear_error();
+  DeviceGuard g(device);
+  B2_CUDA(g.status(), "selecting the device failed");
+  B2_CUDA(cudaFree(nullptr), "creating the primary context failed");
+  return B2_OK;
+}
+
+B2_API int b2_device_count(int* count) {
+  clear_error();
+  if (!count) return fail(B2_ERR_INVALID, "null count pointer");
+  B2_CUDA(cudaGetDeviceCount(count), "querying the device count failed");
+  return B2_OK;
+}
+
+B2_API int b2_stream_synchronize(int device, void* stream) {
+  clear_error();
+  DeviceGuard g(device);
+  B2_CUDA(g.status(), "selecting the device failed");
+  B2_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)),
+          "Failed to synchronize stream");
+  return B2_OK;
+}
+
+B2_API int b2_nv12_to_planar_rgb(void* stream, const uint8_t* src, int src_pitch, uint8_t* dst,
+                          int dst_pitch, int width, int height, int num_frames, int coeff) {
+  return planar_entry(stream, src, src_pitch, dst, dst_pitch, width, height, num_frames, coeff,
+                      B2_RGB);
+}
+B2_API int b2_nv12_to_planar_bgr(void* stream, const uint8_t* src, int src_pitch, uint8_t* dst,
+                          int dst_pitch, int width, int height, int num_frames, int coeff) {
+  return planar_entry(stream, src, src_pitch, dst, dst_pitch, width, height, num_frames, coeff,
+                      B2_BGR);
+}
+
+B2_API int b2_convert_dense(const b2_dense_args* a, void* stream) {
+  clear_error();
+  if (!a) return fail(B2_ERR_INVALID, "null argument struct");
+  if (a->struct_size != sizeof(b2_dense_args))
+    return fail(B2_ERR_INVALID, "b2_dense_args.struct_size is %u, this library expects %zu",
+                a->struct_size, sizeof(b2_dense_args));
+  if (!valid_enum(a->src_format, 1) || !valid_enum(a->layout, 1) || !valid_enum(a->dtype, 2) ||
+      !valid_enum(a->order, 1))
+    return fail(B2_ERR_INVALID, "unknown src_format/layout/dtype/order (%d, %d, %d, %d)",
+                a->src_format, a->layout, a->dtype, a->order);
+  if (a->width < 0 || a->height < 0 || a->num_frames < 0)
+    return fail(B2_ERR_INVALID, "negative size: width %d, height %d, num_frames %d", a->width,
+                a->height, a->num_frames);
+  if (a->num_frames == 0 || a->width == 0 || a->height == 0) return B2_OK;
+  const bool table = a->y_table != nullptr;
+  const bool i420 = a->src_format == B2_SRC_I420;
+  if (table) {
+    if (!a->u_table || (i420 && !a->v_table))
+      return fail(B2_ERR_INVALID, "y_table given without u_table%s", i420 ? "/v_table" : "");
+  } else if (!a->y || !a->u || (i420 && !a->v)) {
+    return fail(B2_ERR_INVALID, "null source plane pointer");
+  }
+  if (!a->dst) return fail(B2_ERR_INVALID, "null dst pointer");
+  // a trailing odd column is never converted, so its chroma is never read
+  const long long min_uv = i420 ? a->width / 2 : (a->width & ~1);
+  if (a->y_pitch < a->width || a->uv_pitch < min_uv)
+    return fail(B2_ERR_INVALID, "pitch smaller than the row (y_pitch %lld, uv_pitch %lld, width %d)",
+                (long long)a->y_pitch, (long long)a->uv_pitch, a->width);
+  const long long packed = 3LL * a->height * a->width;
+  if (a->dst_frame_stride != 0 && a->dst_frame_stride < packed)
+    return fail(B2_ERR_INVALID, "dst_frame_stride %lld is smaller than one frame (%lld elements)",
+                (long long)a->dst_frame_stride, packed);
+  DeviceGuard g(a->device);
+  B2_CUDA(g.status(), "selecting the device failed");
+  DenseLaunch L{};
+  L.y = static_cast<const uint8_t*>(a->y);
+  L.u = static_cast<const uint8_t*>(a->u);
+  L.v = static_cast<const uint8_t*>(a->v);
+  L.y_table = a->y_table; L.u_table = a->u_table; L.v_table = a->v_table;
+  L.y_pitch = a->y_pitch; L.uv_pitch = a->uv_pitch;
+  L.y_frame_stride = a->y_frame_stride; L.uv_frame_stride = a->uv_frame_stride;
+  L.src_format = a->src_format;
+  L.width = a->width; L.height = a->height; L.num_frames = a->num_frames;
+  L.mat = color_matrix(a->matrix_coeff, a->full_range);
+  L.dst = a->dst;
+  L.layout = a->layout; L.dtype = a->dtype; L.order = a->order;
+  L.dst_row_pitch = a->layout == B2_NCHW ? a->width : 3LL * a->width;
+  L.dst_plane_stride = (long long)a->height * a->width;
+  L.dst_frame_stride = a->dst_frame_stride ? a->dst_frame_stride : packed;
+  for (int i = 0; i < 3; ++i) { L.sb.s[i] = a->scale[i]; L.sb.b[i] = a->bias[i]; }
+  return launch_dense(L, static_cast<cudaStream_t>(stream));
+}
+
+B2_API int b2_convert_resize(const b2_resize_args* a, void* stream) {
+  clear_error();
+  if (!a) return fail(B2_ERR_INVALID, "null argument struct");
+  if (a->struct_size != sizeof(b2_resize_args))
+    return fail(B2_ERR_INVALID, "b2_resize_args.struct_size is %u, this library expects %zu",
+                a->struct_size, sizeof(b2_resize_args));
+  if (!valid_enum(a->src_format, 1) || !valid_enum(a->layout, 1) || !valid_enum(a->dtype, 2) ||
+      !valid_enum(a->order, 1))
+    return fail(B2_ERR_INVALID, "unknown src_format/layout/dtype/order (%d, %d, %d, %d)",
+                a->src_format, a->layout, a->dtype, a->order);
+  if (a->num_images < 0 || a->out_w < 0 || a->out_h < 0 || a->max_src_w < 0)
+    return fail(B2_ERR_INVALID, "negative size: num_images %d, out %dx%d, max_src_w %d",
+                a->num_images, a->out_w, a->out_h, a->max_src_w);
+  if (a->num_images == 0 || a->out_w == 0 || a->out_h == 0) return B2_OK;
+  if (!a->base || !a->descs || !a->dst)
+    return fail(B2_ERR_INVALID, "null base, descs or dst pointer");
+  if (a->max_src_w < 1) return fail(B2_ERR_INVALID, "max_src_w must be at least 1");
+  if (a->dst_image_stride != 0 && a->dst_image_stride < 3LL * a->out_w * a->out_h)
+    return fail(B2_ERR_INVALID, "dst_image_stride %lld is smaller than one image",
+                (long long)a->dst_image_stride);
+  DeviceGuard g(a->device);
+  B2_CUDA(g.status(), "selecting the device failed");
+  return launch_resize(*a, static_cast<cudaStream_t>(stream));
+}
+
+B2_API int b2_gather_surfaces(const void* const* surfaces, const int64_t* pitches, int num_frames,
+                       int width, int height, uint8_t* dst, int device, void* stream) {
+  clear_error();
+  if (num_frames < 0 || width < 0 || height < 0)
+    return fail(B2_ERR_INVALID, "negative size: num_frames %d, width %d, height %d", num_frames,
+                width, height);
+  if (num_frames == 0 || width == 0 || height == 0) return B2_OK;
+  if (!surfaces || !pitches || !dst) return fail(B2_ERR_INVALID, "null pointer argument");
+  if (height % 2) return fail(B2_ERR_INVALID, "NV12 height must be even. Found: %d", height);
+  DeviceGuard g(device);
+  B2_CUDA(g.status(), "selecting the device failed");
+  return launch_gather(surfaces, pitches, num_frames, width, height, dst,
+                       static_cast<cudaStream_t>(stream));
+}
+
+B2_API int b2_transfer_h2d(void* dst, const void* host_src, size_t nbytes, int src_is_pinned, int device,
+                    void* stream) {
+  clear_error();
+  if (nbytes == 0) return B2_OK;
+  if (!dst || !host_src) return fail(B2_ERR_INVALID, "null pointer argument");
+  DeviceGuard g(device);
+  B2_CUDA(g.status(), "selecting the device failed");
+  if (src_is_pinned) {
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    B2_CUDA(cudaMemcpyAsync(dst, host_src, nbytes, cudaMemcpyHostToDevice, s),
+            "Failed to initiate async memory copy from host to device.");
+    B2_CUDA(cudaStreamSynchronize(s), "Failed to synchronize the stream.");
+  } else {
+    B2_CUDA(cudaMemcpy(dst, host_src, nbytes, cudaMemcpyHostToDevice),
+            "Failed to copy data from host to device.");
+  }
+  return B2_OK;
+}
+
+B2_API int b2_transfer_h2d_async(void* dst, const void* host_src, size_t nbytes, int device,
+                          void* stream) {
+  clear_error();
+  if (nbytes == 0) return B2_OK;
+  if (!dst || !host_src) return fail(B2_ERR_INVALID, "null pointer argument");
+  DeviceGuard g(device);
+  B2_CUDA(g.status(), "selecting the device failed");
+  B2_CUDA(cudaMemcpyAsync(dst, host_src, nbytes, cudaMemcpyHostToDevice,
+                          static_cast<cudaStream_t>(stream)),
+          "Failed to initiate async memory copy from host to device.");
+  return B2_OK;
+}
+
+B2_API int b2_transfer_d2h(void* host_dst, const void* src, size_t nbytes, int device) {
+  clear_error();
+  if (nbytes == 0) return B2_OK;
+  if (!host_dst || !src) return fail(B2_ERR_INVALID, "null pointer argument");
+  DeviceGuard g(device);
+  B2_CUDA(g.status(), "selecting the device failed");
+  B2_CUDA(cudaMemcpy(host_dst, src, nbytes, cudaMemcpyDeviceToHost),
+          "Failed to copy data from device to host.");
+  return B2_OK;
+}
+
+B2_API int b2_alloc_pinned(void** host_ptr, size_t nbytes) {
+  clear_error();
+  if (!host_ptr) return fail(B2_ERR_INVALID, "null pointer argument");
+  if (nbytes == 0) return fail(B2_ERR_INVALID, "`size` must be greater than 0.");
+  B2_CUDA(cudaHostAlloc(host_ptr, nbytes, cudaHostAllocDefault),
+          "Failed to allocate pinned memory.");
+  return B2_OK;
+}
+
+B2_API int b2_free_pinned(void* host_ptr) {
+  clear_error();
+  if (!host_ptr) return B2_OK;
+  B2_CUDA(cudaFreeHost(host_ptr), "Failed to free pinned memory.");
+  return B2_OK;
+}
+
+B2_API int b2_device_alloc(void** ptr, size_t nbytes, int device) {
+  clear_error();
+  if (!ptr) return fail(B2_ERR_INVALID, "null pointer argument");
+  if (nbytes == 0) return fail(B2_ERR_INVALID, "`size` must be greater than 0.");
+  DeviceGuard g(device);
+  B2_CUDA(g.status(), "selecting the device failed");
+  B2_CUDA(cudaMalloc(ptr, nbytes), "Failed to allocate CUDA memory");
+  return B2_OK;
+}
+
+B2_API int b2_device_free(void* ptr, int device) {
+  clear_error();
+  if (!ptr) return B2_OK;
+  DeviceGuard g(device);
+  B2_CUDA(g.status(), "selecting the device failed");
+  B2_CUDA(cudaFree(ptr), "Failed to free CUDA memory");
+  return B2_OK;
+}
+
+B2_API int b2_frame_checksum(const uint8_t* src, int64_t frame_bytes, int num_frames, uint64_t* out,
+                      int device, void* stream) {
+  clear_error();
+  if (num_frames < 0 || frame_bytes < 0)
+    return fail(B2_ERR_INVALID, "negative size: num_frames %d, frame_bytes %lld", num_frames,
+                (long long)frame_bytes);
+  if (num_frames == 0) return B2_OK;
+  if (!out || (!src && frame_bytes)) return fail(B2_ERR_INVALID, "null pointer argument");
+  DeviceGuard g(device);
+  B2_CUDA(g.status(), "selecting the device failed");
+  return launch_checksum(src, frame_bytes, num_frames, out, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,168 @@
+// Shared pieces of the sm_100a frame kernels: error plumbing for the C ABI, the
+// colour-matrix table and the per-pixel arithmetic.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "b2frames.h"
+
+namespace b2 {
+
+// ---- host: status + thread-local message ----------------------------------------------------
+int fail(int code, const char* fmt, ...);
+int fail_cuda(cudaError_t e, const char* what);
+void clear_error();
+
+#define B2_CUDA(expr, what)                          \
+  do {                                               \
+    cudaError_t _e = (expr);                         \
+    if (_e != cudaSuccess) return ::b2::fail_cuda(_e, what); \
+  } while (0)
+
+// Makes `device` current for the scope and restores the previous one.
+class DeviceGuard {
+ public:
+  explicit DeviceGuard(int device);
+  ~DeviceGuard();
+  cudaError_t status() const { return status_; }
+
+ private:
+  int prev_ = -1;
+  bool switched_ = false;
+  cudaError_t status_ = cudaSuccess;
+};
+
+// ---- colour matrix ----------------------------------------------------------------------------
+// Every entry of the reference table (src/libspdl/cuda/detail/color_conversion.cu:20-70) has the
+// shape {g,0,vr},{g,ug,vg},{g,ub,0}; five numbers describe it.  y_bias is 2^23 + luma offset:
+// the kernels turn a byte b into the float 2^23+b with one byte-permute and subtract y_bias.
+struct ColorMat {
+  float g, vr, ug, vg, ub;
+  float y_bias;
+};
+ColorMat color_matrix(int matrix_coeff, int full_range);
+
+struct ScaleBias {
+  float s[3], b[3];
+};
+
+#ifdef __CUDACC__
+
+constexpr float kTwo23 = 8388608.0f;
+constexpr float kQuantMagic = 12582912.0f;  // 1.5 * 2^23: ulp is 1 on both sides of zero offset
+
+// float(2^23 + byte k of w): one PRMT, no integer->float conversion instruction.
+__device__ __forceinline__ float biased_byte(uint32_t w, int k) {
+  return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u + k));
+}
+
+// The reference evaluates  m0*fy + m1*fu + m2*fv  per channel in fp32
+// (color_conversion.cu:76-86); as nvcc compiles it the device computes
+//     fma(m0, fy, m1*fu) + m2*fv
+// -- the first product pair fused, the last add not.  With the table's zeros this is
+//     R = g*fy + vr*fv          G = fma(g, fy, ug*fu) + vg*fv          B = fma(g, fy, ub*fu)
+// and the four chroma products are shared by the 2x2 quad that shares the chroma sample.
+struct Chroma {
+  float vr, ug, vg, ub;  // vr*fv, ug*fu, vg*fv, ub*fu, each rounded once
+};
+// bu, bv: 2^23 + U, 2^23 + V
+__device__ __forceinline__ Chroma chroma_of(const ColorMat& m, float bu, float bv) {
+  const float fu = __fsub_rn(bu, kTwo23 + 128.0f);
+  const float fv = __fsub_rn(bv, kTwo23 + 128.0f);
+  Chroma c;
+  c.vr = __fmul_rn(m.vr, fv);
+  c.ug = __fmul_rn(m.ug, fu);
+  c.vg = __fmul_rn(m.vg, fv);
+  c.ub = __fmul_rn(m.ub, fu);
+  return c;
+}
+
+// One pixel: the three channel values as fp32, bit-for-bit what the reference kernel holds
+// before its clamp.  `by` is 2^23 + Y.
+__device__ __forceinline__ void pixel_f32(const ColorMat& m, float by, const Chroma& c, float& r,
+                                          float& g, float& b) {
+  const float fy = __fsub_rn(by, m.y_bias);
+  r = __fadd_rn(__fmul_rn(m.g, fy), c.vr);
+  g = __fadd_rn(__fmaf_rn(m.g, fy, c.ug), c.vg);
+  b = __fmaf_rn(m.g, fy, c.ub);
+}
+
+// Truncate-and-clamp of two channel values at once (color_conversion.cu:72-74):
+// x<0 -> 0, x>255 -> 255, else (uint8)x.  Adding 1.5*2^23 with round-toward-zero leaves
+// floor(x) in the low 16 mantissa bits as a signed halfword; one packed min-with-relu clamps
+// both halfwords.  Returns {lo: q(a), hi: q(b)} as two 16-bit lanes holding 0..255.
+__device__ __forceinline__ uint32_t quant2(float a, float b) {
+  const uint32_t qa = __float_as_uint(__fadd_rz(a, kQuantMagic));
+  const uint32_t qb = __float_as_uint(__fadd_rz(b, kQuantMagic));
+  return __vimin_s16x2_relu(__byte_perm(qa, qb, 0x5410u), 0x00FF00FFu);
+}
+// Four bytes from two quant2 results: {p.lo, p.hi, q.lo, q.hi}.
+__device__ __forceinline__ uint32_t bytes4(uint32_t p, uint32_t q) {
+  return __byte_perm(p, q, 0x6420u);
+}
+// The float value (0..255, exact) of 16-bit lane k of a quant2 result.
+__device__ __forceinline__ float lane_f32(uint32_t p, int k) {
+  return __fsub_rn(__uint_as_float(__byte_perm(p, 0x4B000000u, 0x7540u + 2 * k)), kTwo23);
+}
+
+// One pixel straight to three integers (scalar path of the generic kernels).
+__device__ __forceinline__ void pixel_u8(const ColorMat& m, int y, int u, int v, int& r, int& g,
+                                         int& b) {
+  Chroma c = chroma_of(m, kTwo23 + (float)u, kTwo23 + (float)v);
+  float fr, fg, fb;
+  pixel_f32(m, kTwo23 + (float)y, c, fr, fg, fb);
+  const uint32_t rg = quant2(fr, fg), bb = quant2(fb, fb);
+  r = rg & 0xFFFF;
+  g = rg >> 16;
+  b = bb & 0xFFFF;
+}
+
+template <typename T>
+__device__ __forceinline__ T finish(float v, float s, float b);
+template <>
+__device__ __forceinline__ float finish<float>(float v, float s, float b) {
+  return __fmaf_rn(v, s, b);
+}
+template <>
+__device__ __forceinline__ __nv_bfloat16 finish<__nv_bfloat16>(float v, float s, float b) {
+  return __float2bfloat16_rn(__fmaf_rn(v, s, b));
+}
+template <>
+__device__ __forceinline__ uint8_t finish<uint8_t>(float v, float, float) {
+  return (uint8_t)(int)v;
+}
+
+template <int DTYPE>
+struct OutT;
+template <>
+struct OutT<B2_U8> { using type = uint8_t; };
+template <>
+struct OutT<B2_F32> { using type = float; };
+template <>
+struct OutT<B2_BF16> { using type = __nv_bfloat16; };
+
+#endif  // __CUDACC__
+
+// ---- launchers shared between translation units ------------------------------------------------
+struct DenseLaunch {
+  const uint8_t* y;
+  const uint8_t* u;
+  const uint8_t* v;
+  const void* const* y_table;
+  const void* const* u_table;
+  const void* const* v_table;
+  int64_t y_pitch, uv_pitch, y_frame_stride, uv_frame_stride;
+  int src_format, width, height, num_frames;
+  ColorMat mat;
+  void* dst;
+  int64_t dst_row_pitch;     // elements (NCHW: between rows of a plane; NHWC: between rows)
+  int64_t dst_plane_stride;  // elements (NCHW only)
+  int64_t dst_frame_stride;  // elements
+  int layout, dtype, order;
+  ScaleBias sb;
+};
+int launch_dense(const DenseLaunch& L, cudaStream_t stream);
+
+}  // namespace b2

@@ -1,0 +1,392 @@
+// Dense colour conversion: every pixel of every frame, no resampling.
+//
+// Two kernel families.
+//   dense_vec_kernel   the fast path.  One thread owns a 2-row x PX-pixel block (PX = 16 bytes
+//                      of output per channel: 16 px for u8, 8 for bf16, 4 for fp32), so the two
+//                      rows share one chroma load, every global load is one 4/8/16-byte vector
+//                      and every global store is a 16-byte vector.  Planar output is stored
+//                      straight from registers (a warp writes 512 contiguous bytes per
+//                      instruction).  Interleaved output (48 bytes per thread per row) is staged
+//                      in shared memory by the warp and leaves as one bulk asynchronous copy
+//                      (cp.async.bulk shared->global) per row segment.
+//   dense_quad_kernel  the any-shape path: one thread per 2x2 quad with byte accesses.  Taken
+//                      when a pointer, pitch or the width breaks the vector path's alignment.
+//
+// The kernels are HBM-bound: 1.5 bytes read and 3*sizeof(T) written per pixel.
+#include "b2_common.cuh"
+
+namespace b2 {
+namespace {
+
+struct DenseParams {
+  const uint8_t* y;
+  const uint8_t* u;
+  const uint8_t* v;
+  const void* const* y_table;
+  const void* const* u_table;
+  const void* const* v_table;
+  long long y_pitch, uv_pitch, y_frame_stride, uv_frame_stride;
+  int width, height;  // height here is the even part of the frame height
+  ColorMat mat;
+  void* dst;
+  long long dst_row_pitch, dst_plane_stride, dst_frame_stride;  // elements
+  ScaleBias sb;
+};
+
+template <int NB>
+struct Vec;
+template <>
+struct Vec<16> { using type = uint4; };
+template <>
+struct Vec<8> { using type = uint2; };
+template <>
+struct Vec<4> { using type = uint32_t; };
+template <>
+struct Vec<2> { using type = uint16_t; };
+
+// Load NB bytes into ceil(NB/4) words.  Streaming (read-once) cache hint.
+template <int NB>
+__device__ __forceinline__ void load_bytes(const uint8_t* p, uint32_t* w) {
+  if constexpr (NB == 16) {
+    uint4 t = __ldcs(reinterpret_cast<const uint4*>(p));
+    w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w;
+  } else if constexpr (NB == 8) {
+    uint2 t = __ldcs(reinterpret_cast<const uint2*>(p));
+    w[0] = t.x; w[1] = t.y;
+  } else if constexpr (NB == 4) {
+    w[0] = __ldcs(reinterpret_cast<const uint32_t*>(p));
+  } else {
+    w[0] = __ldcs(reinterpret_cast<const uint16_t*>(p));
+  }
+}
+template <int NB>
+__device__ __forceinline__ void load_bytes_any(const uint8_t* p, uint32_t* w, bool aligned) {
+  if (aligned) {
+    load_bytes<NB>(p, w);
+  } else {
+#pragma unroll
+    for (int i = 0; i < (NB + 3) / 4; ++i) w[i] = 0;
+#pragma unroll
+    for (int i = 0; i < NB; ++i) w[i >> 2] |= (uint32_t)__ldcs(p + i) << (8 * (i & 3));
+  }
+}
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+constexpr int kDenseThreads = 128;
+
+template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE>
+__global__ void __launch_bounds__(kDenseThreads) dense_vec_kernel(const DenseParams p) {
+  using T = typename OutT<DTYPE>::type;
+  constexpr int PX = 16 / (int)sizeof(T);  // pixels per thread per row
+  constexpr int NW = PX / 4;               // luma words per row
+  constexpr int UVB = FMT == B2_SRC_NV12 ? PX : PX / 2;  // chroma bytes per plane row segment
+  constexpr int UVW = (UVB + 3) / 4;
+
+  const int cx = blockIdx.x * blockDim.x + threadIdx.x;
+  const int rp = blockIdx.y * blockDim.y + threadIdx.y;
+  const int n = blockIdx.z;
+  const int x0 = cx * PX;
+  const bool active = x0 < p.width && 2 * rp < p.height;
+
+  uint32_t out[2][12];  // 48 bytes per row, already in destination order
+
+  if (active) {
+    const uint8_t *yb, *ub, *vb = nullptr;
+    bool aligned = true;
+    if constexpr (TABLE) {
+      yb = static_cast<const uint8_t*>(p.y_table[n]);
+      ub = static_cast<const uint8_t*>(p.u_table[n]);
+      if constexpr (FMT == B2_SRC_I420) vb = static_cast<const uint8_t*>(p.v_table[n]);
+      aligned = (((uintptr_t)yb | (uintptr_t)ub | (uintptr_t)vb) & 15) == 0;
+    } else {
+      yb = p.y + (long long)n * p.y_frame_stride;
+      ub = p.u + (long long)n * p.uv_frame_stride;
+      if constexpr (FMT == B2_SRC_I420) vb = p.v + (long long)n * p.uv_frame_stride;
+    }
+    uint32_t yw[2][NW], uw[UVW], vw[UVW];
+    const uint8_t* y0p = yb + (long long)(2 * rp) * p.y_pitch + x0;
+    const uint8_t* up = ub + (long long)rp * p.uv_pitch + (FMT == B2_SRC_NV12 ? x0 : x0 / 2);
+    if constexpr (TABLE) {
+      load_bytes_any<PX>(y0p, yw[0], aligned);
+      load_bytes_any<PX>(y0p + p.y_pitch, yw[1], aligned);
+      load_bytes_any<UVB>(up, uw, aligned);
+      if constexpr (FMT == B2_SRC_I420)
+        load_bytes_any<UVB>(vb + (long long)rp * p.uv_pitch + x0 / 2, vw, aligned);
+    } else {
+      load_bytes<PX>(y0p, yw[0]);
+      load_bytes<PX>(y0p + p.y_pitch, yw[1]);
+      load_bytes<UVB>(up, uw);
+      if constexpr (FMT == B2_SRC_I420)
+        load_bytes<UVB>(vb + (long long)rp * p.uv_pitch + x0 / 2, vw);
+    }
+    (void)vw;
+
+    const ColorMat m = p.mat;
+#pragma unroll
+    for (int j = 0; j < NW; ++j) {
+      // chroma of the two 2x2 quads under luma word j
+      Chroma c[2];
+      if constexpr (FMT == B2_SRC_NV12) {
+        c[0] = chroma_of(m, biased_byte(uw[j], 0), biased_byte(uw[j], 1));
+        c[1] = chroma_of(m, biased_byte(uw[j], 2), biased_byte(uw[j], 3));
+      } else {
+        const int w = j >> 1, b = (j & 1) * 2;
+        c[0] = chroma_of(m, biased_byte(uw[w], b), biased_byte(vw[w], b));
+        c[1] = chroma_of(m, biased_byte(uw[w], b + 1), biased_byte(vw[w], b + 1));
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        float ch[3][4];  // [output slot][pixel]
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float cr, cg, cb;
+          pixel_f32(m, biased_byte(yw[r][j], k), c[k >> 1], cr, cg, cb);
+          ch[BGR ? 2 : 0][k] = cr;
+          ch[1][k] = cg;
+          ch[BGR ? 0 : 2][k] = cb;
+        }
+        if constexpr (DTYPE == B2_U8) {
+          if constexpr (LAYOUT == B2_NCHW) {
+#pragma unroll
+            for (int s = 0; s < 3; ++s)
+              out[r][4 * s + j] = bytes4(quant2(ch[s][0], ch[s][1]), quant2(ch[s][2], ch[s][3]));
+          } else {
+            out[r][3 * j + 0] = bytes4(quant2(ch[0][0], ch[1][0]), quant2(ch[2][0], ch[0][1]));
+            out[r][3 * j + 1] = bytes4(quant2(ch[1][1], ch[2][1]), quant2(ch[0][2], ch[1][2]));
+            out[r][3 * j + 2] = bytes4(quant2(ch[2][2], ch[0][3]), quant2(ch[1][3], ch[2][3]));
+          }
+        } else {
+          float f[3][4];
+#pragma unroll
+          for (int s = 0; s < 3; ++s) {
+            const uint32_t q01 = quant2(ch[s][0], ch[s][1]), q23 = quant2(ch[s][2], ch[s][3]);
+            f[s][0] = __fmaf_rn(lane_f32(q01, 0), p.sb.s[s], p.sb.b[s]);
+            f[s][1] = __fmaf_rn(lane_f32(q01, 1), p.sb.s[s], p.sb.b[s]);
+            f[s][2] = __fmaf_rn(lane_f32(q23, 0), p.sb.s[s], p.sb.b[s]);
+            f[s][3] = __fmaf_rn(lane_f32(q23, 1), p.sb.s[s], p.sb.b[s]);
+          }
+          if constexpr (DTYPE == B2_F32) {  // NW == 1
+#pragma unroll
+            for (int s = 0; s < 3; ++s)
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                out[r][LAYOUT == B2_NCHW ? 4 * s + k : 3 * k + s] = __float_as_uint(f[s][k]);
+          } else {  // bf16, NW == 2: 8 pixels, two per word
+            if constexpr (LAYOUT == B2_NCHW) {
+#pragma unroll
+              for (int s = 0; s < 3; ++s)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                  __nv_bfloat162 t = __floats2bfloat162_rn(f[s][2 * h], f[s][2 * h + 1]);
+                  out[r][4 * s + 2 * j + h] = *reinterpret_cast<uint32_t*>(&t);
+                }
+            } else {
+              // 12 values of this luma word in memory order: p0(s0 s1 s2) p1(...) ...
+#pragma unroll
+              for (int w = 0; w < 6; ++w) {
+                const int e0 = 2 * w, e1 = 2 * w + 1;
+                __nv_bfloat162 t = __floats2bfloat162_rn(f[e0 % 3][e0 / 3], f[e1 % 3][e1 / 3]);
+                out[r][6 * j + w] = *reinterpret_cast<uint32_t*>(&t);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  T* dst = static_cast<T*>(p.dst) + (long long)n * p.dst_frame_stride;
+  if constexpr (LAYOUT == B2_NCHW) {
+    if (active) {
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int s = 0; s < 3; ++s) {
+          T* q = dst + s * p.dst_plane_stride + (long long)(2 * rp + r) * p.dst_row_pitch + x0;
+          __stcs(reinterpret_cast<uint4*>(q),
+                 make_uint4(out[r][4 * s], out[r][4 * s + 1], out[r][4 * s + 2], out[r][4 * s + 3]));
+        }
+    }
+  } else {
+    // Interleaved: the warp's 32 x 48 bytes per row are contiguous in the destination.  Stage
+    // them in shared memory and hand each row segment to the bulk-copy engine.
+    extern __shared__ __align__(128) unsigned char stage_raw[];
+    const int lane = threadIdx.x & 31;
+    const int warp = (threadIdx.y * blockDim.x + threadIdx.x) >> 5;
+    unsigned char* ws = stage_raw + warp * (2 * 32 * 48);
+    if (active) {
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int i = 0; i < 3; ++i)
+          *reinterpret_cast<uint4*>(ws + r * 1536 + lane * 48 + i * 16) =
+              make_uint4(out[r][4 * i], out[r][4 * i + 1], out[r][4 * i + 2], out[r][4 * i + 3]);
+    }
+    // make the generic-proxy writes visible to the async proxy, then let lane 0 issue the copies
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0 && 2 * rp < p.height) {
+      const int wx0 = (cx - lane) * PX;  // first pixel of the warp's segment (lane 0's cx)
+      int px_in_seg = p.width - wx0;
+      if (px_in_seg > 32 * PX) px_in_seg = 32 * PX;
+      if (px_in_seg > 0) {
+        const uint32_t bytes = (uint32_t)px_in_seg * 3u * (uint32_t)sizeof(T);
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          T* q = dst + (long long)(2 * rp + r) * p.dst_row_pitch + (long long)wx0 * 3;
+          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(q),
+                       "r"(smem_addr(ws + r * 1536)), "r"(bytes)
+                       : "memory");
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        // the staging buffer must outlive the engine's reads of it
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      }
+    }
+  }
+}
+
+// Any-shape path: one thread per 2x2 quad (color_conversion.cu:98-137 has the same ownership).
+template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE>
+__global__ void __launch_bounds__(256) dense_quad_kernel(const DenseParams p) {
+  using T = typename OutT<DTYPE>::type;
+  const int x = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  const int y = (blockIdx.y * blockDim.y + threadIdx.y) * 2;
+  const int n = blockIdx.z;
+  if (x + 1 >= p.width || y + 1 >= p.height) return;
+  const uint8_t *yb, *ub, *vb = nullptr;
+  if constexpr (TABLE) {
+    yb = static_cast<const uint8_t*>(p.y_table[n]);
+    ub = static_cast<const uint8_t*>(p.u_table[n]);
+    if constexpr (FMT == B2_SRC_I420) vb = static_cast<const uint8_t*>(p.v_table[n]);
+  } else {
+    yb = p.y + (long long)n * p.y_frame_stride;
+    ub = p.u + (long long)n * p.uv_frame_stride;
+    if constexpr (FMT == B2_SRC_I420) vb = p.v + (long long)n * p.uv_frame_stride;
+  }
+  int cu, cv;
+  if constexpr (FMT == B2_SRC_NV12) {
+    const uint8_t* q = ub + (long long)(y >> 1) * p.uv_pitch + x;
+    cu = q[0];
+    cv = q[1];
+  } else {
+    cu = ub[(long long)(y >> 1) * p.uv_pitch + (x >> 1)];
+    cv = vb[(long long)(y >> 1) * p.uv_pitch + (x >> 1)];
+  }
+  T* dst = static_cast<T*>(p.dst) + (long long)n * p.dst_frame_stride;
+#pragma unroll
+  for (int r = 0; r < 2; ++r)
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      int c[3];
+      pixel_u8(p.mat, yb[(long long)(y + r) * p.y_pitch + x + k], cu, cv, c[BGR ? 2 : 0], c[1],
+               c[BGR ? 0 : 2]);
+#pragma unroll
+      for (int s = 0; s < 3; ++s) {
+        const long long idx =
+            LAYOUT == B2_NCHW
+                ? s * p.dst_plane_stride + (long long)(y + r) * p.dst_row_pitch + x + k
+                : (long long)(y + r) * p.dst_row_pitch + (long long)(x + k) * 3 + s;
+        dst[idx] = finish<T>((float)c[s], p.sb.s[s], p.sb.b[s]);
+      }
+    }
+}
+
+template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE>
+int launch_t(const DenseLaunch& L, const DenseParams& p, bool vec, cudaStream_t stream) {
+  using T = typename OutT<DTYPE>::type;
+  constexpr int PX = 16 / (int)sizeof(T);
+  const int He = L.height & ~1;
+  // gridDim.z is limited to 65535 frames per launch
+  for (int n0 = 0; n0 < L.num_frames; n0 += 65535) {
+    const int nn = L.num_frames - n0 < 65535 ? L.num_frames - n0 : 65535;
+    DenseParams q = p;
+    if (TABLE) {
+      q.y_table = p.y_table + n0;
+      q.u_table = p.u_table + n0;
+      if (p.v_table) q.v_table = p.v_table + n0;
+    } else {
+      q.y = p.y + (long long)n0 * p.y_frame_stride;
+      q.u = p.u + (long long)n0 * p.uv_frame_stride;
+      if (p.v) q.v = p.v + (long long)n0 * p.uv_frame_stride;
+    }
+    q.dst = static_cast<T*>(p.dst) + (long long)n0 * p.dst_frame_stride;
+    if (vec) {
+      const int chunks = (L.width + PX - 1) / PX;
+      int bx = ((chunks + 31) / 32) * 32;
+      if (bx > kDenseThreads) bx = kDenseThreads;
+      const int by = kDenseThreads / bx;
+      dim3 block(bx, by), grid((chunks + bx - 1) / bx, (He / 2 + by - 1) / by, nn);
+      const size_t smem = LAYOUT == B2_NHWC ? (size_t)(kDenseThreads / 32) * 2 * 32 * 48 : 0;
+      dense_vec_kernel<FMT, LAYOUT, DTYPE, BGR, TABLE><<<grid, block, smem, stream>>>(q);
+    } else {
+      dim3 block(32, 8), grid((L.width / 2 + 31) / 32, (He / 2 + 7) / 8, nn);
+      if (grid.x == 0 || grid.y == 0) continue;
+      dense_quad_kernel<FMT, LAYOUT, DTYPE, BGR, TABLE><<<grid, block, 0, stream>>>(q);
+    }
+    B2_CUDA(cudaPeekAtLastError(), "launch of the dense conversion kernel failed");
+  }
+  return B2_OK;
+}
+
+template <int FMT, int LAYOUT, int DTYPE>
+int launch_fld(const DenseLaunch& L, const DenseParams& p, bool vec, cudaStream_t s) {
+  const bool bgr = L.order == B2_BGR, table = L.y_table != nullptr;
+  if (bgr) return table ? launch_t<FMT, LAYOUT, DTYPE, true, true>(L, p, vec, s)
+                        : launch_t<FMT, LAYOUT, DTYPE, true, false>(L, p, vec, s);
+  return table ? launch_t<FMT, LAYOUT, DTYPE, false, true>(L, p, vec, s)
+               : launch_t<FMT, LAYOUT, DTYPE, false, false>(L, p, vec, s);
+}
+template <int FMT, int LAYOUT>
+int launch_fl(const DenseLaunch& L, const DenseParams& p, bool vec, cudaStream_t s) {
+  switch (L.dtype) {
+    case B2_U8: return launch_fld<FMT, LAYOUT, B2_U8>(L, p, vec, s);
+    case B2_F32: return launch_fld<FMT, LAYOUT, B2_F32>(L, p, vec, s);
+    default: return launch_fld<FMT, LAYOUT, B2_BF16>(L, p, vec, s);
+  }
+}
+
+inline bool mult(long long v, long long m) { return v % m == 0; }
+
+}  // namespace
+
+int launch_dense(const DenseLaunch& L, cudaStream_t stream) {
+  if (L.num_frames == 0 || L.width < 2 || L.height < 2) return B2_OK;
+  DenseParams p{};
+  p.y = L.y; p.u = L.u; p.v = L.v;
+  p.y_table = L.y_table; p.u_table = L.u_table; p.v_table = L.v_table;
+  p.y_pitch = L.y_pitch; p.uv_pitch = L.uv_pitch;
+  p.y_frame_stride = L.y_frame_stride; p.uv_frame_stride = L.uv_frame_stride;
+  p.width = L.width; p.height = L.height & ~1;
+  p.mat = L.mat;
+  p.dst = L.dst;
+  p.dst_row_pitch = L.dst_row_pitch;
+  p.dst_plane_stride = L.dst_plane_stride;
+  p.dst_frame_stride = L.dst_frame_stride;
+  p.sb = L.sb;
+
+  // Can every access of the vector path be a naturally aligned 4/8/16-byte vector?
+  const int esz = L.dtype == B2_U8 ? 1 : (L.dtype == B2_F32 ? 4 : 2);
+  const int px = 16 / esz;
+  const int uvb = L.src_format == B2_SRC_NV12 ? px : px / 2;
+  const bool table = L.y_table != nullptr;
+  bool vec = mult(L.width, px) && mult(L.y_pitch, px) && mult(L.uv_pitch, uvb) &&
+             mult((long long)(uintptr_t)L.dst, 16) && mult(L.dst_row_pitch * esz, 16) &&
+             mult(L.dst_frame_stride * esz, 16);
+  if (L.layout == B2_NCHW) vec = vec && mult(L.dst_plane_stride * esz, 16);
+  if (!table) {
+    vec = vec && mult((long long)(uintptr_t)L.y, px) && mult((long long)(uintptr_t)L.u, uvb) &&
+          mult(L.y_frame_stride, px) && mult(L.uv_frame_stride, uvb);
+    if (L.src_format == B2_SRC_I420) vec = vec && mult((long long)(uintptr_t)L.v, uvb);
+  }
+  if (L.src_format == B2_SRC_NV12)
+    return L.layout == B2_NCHW ? launch_fl<B2_SRC_NV12, B2_NCHW>(L, p, vec, stream)
+                               : launch_fl<B2_SRC_NV12, B2_NHWC>(L, p, vec, stream);
+  return L.layout == B2_NCHW ? launch_fl<B2_SRC_I420, B2_NCHW>(L, p, vec, stream)
+                             : launch_fl<B2_SRC_I420, B2_NHWC>(L, p, vec, stream);
+}
+
+}  // namespace b2

@@ -1,0 +1,452 @@
+"""The ``spdl.io`` functions of the post-decode frame path, backed by ``libb2frames.so``.
+
+Reference counterparts (paths within facebookresearch/spdl):
+
+* ``nv12_to_rgb`` / ``nv12_to_bgr``      ``src/spdl/io/_core.py:1201-1267`` ->
+  ``src/spdl/io/lib/cuda/color_conversion.cpp:23-76`` ->
+  ``src/libspdl/cuda/color_conversion.cpp:29-97``
+* ``transfer_buffer``                     ``src/spdl/io/_core.py:1168-1183`` ->
+  ``src/spdl/io/lib/cuda/transfer.cpp:55-95`` -> ``src/libspdl/cuda/transfer.cpp:37-89``
+* ``transfer_buffer_cpu``                 ``src/spdl/io/_core.py:1186-1195`` ->
+  ``src/libspdl/cuda/transfer.cpp:91-118``
+* ``FrameBatcher``                        ``src/libspdl/cuda/nvdec/detail/buffer.cpp:18-92``
+
+``convert_nv12`` and ``convert_resize`` have no single counterpart: they fuse the conversion
+with the permute / float / normalise / resize steps that reference users run as separate passes
+(``examples/imagenet_classification.py:95-106``).
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Any, Sequence
+
+import numpy as np
+
+from .. import _lib
+from .._lib import BF16, BGR, F32, I420, NCHW, NHWC, NV12, RGB, U8
+from ._types import CPUBuffer, CUDABuffer, CUDAConfig, cuda_buffer
+
+__all__ = [
+    "nv12_to_rgb", "nv12_to_bgr", "convert_nv12", "convert_resize", "make_image_descs",
+    "transfer_buffer", "transfer_buffer_cpu", "synchronize_stream", "FrameBatcher",
+    "frame_checksum", "DESC_DTYPE",
+]
+
+#: numpy view of ``b2_image_desc`` (64 bytes)
+DESC_DTYPE = np.dtype(
+    [("y_off", "<u8"), ("u_off", "<u8"), ("v_off", "<u8"), ("y_pitch", "<i4"), ("uv_pitch", "<i4"),
+     ("src_w", "<i4"), ("src_h", "<i4"), ("crop_x", "<i4"), ("crop_y", "<i4"),
+     ("scale_x", "<f4"), ("scale_y", "<f4"), ("reserved", "<i4", (2,))]
+)
+
+_LAYOUTS = {"NCHW": NCHW, "NHWC": NHWC, NCHW: NCHW, NHWC: NHWC}
+_DTYPES = {"uint8": U8, "u8": U8, "float32": F32, "fp32": F32, "f32": F32, "bfloat16": BF16,
+           "bf16": BF16}
+_ORDERS = {"rgb": RGB, "bgr": BGR}
+_FORMATS = {"nv12": NV12, "i420": I420, "yuv420p": I420}
+_OUT_ELEM = {U8: ("u", 1), F32: ("f", 4), BF16: ("u", 2)}  # bf16 is exposed as 2-byte words
+
+
+def _cai(obj: Any) -> tuple[int, tuple[int, ...], str]:
+    """(pointer, shape, typestr) of a C-contiguous CUDA array."""
+    iface = getattr(obj, "__cuda_array_interface__", None)
+    if iface is None:
+        raise TypeError(
+            f"Expected an object with __cuda_array_interface__ (CUDABuffer, torch CUDA tensor); "
+            f"found {type(obj).__name__}.")
+    shape = tuple(int(s) for s in iface["shape"])
+    strides = iface.get("strides")
+    if strides is not None:
+        item = int(iface["typestr"][2:])
+        expect, acc = [], item
+        for s in reversed(shape):
+            expect.append(acc)
+            acc *= s
+        if tuple(strides) != tuple(reversed(expect)) and all(s > 1 for s in shape):
+            raise RuntimeError("The input CUDA array must be C-contiguous.")
+    return int(iface["data"][0]), shape, iface["typestr"]
+
+
+def _device_of(obj: Any, cfg: CUDAConfig) -> None:
+    dev = getattr(obj, "device_index", None)
+    if dev is None:
+        d = getattr(obj, "device", None)
+        dev = getattr(d, "index", None)
+    if dev is not None and dev != cfg.device_index:
+        raise RuntimeError(
+            f"The buffer is on device {dev} but device_config targets {cfg.device_index}.")
+
+
+def _scale_bias(mean, std) -> tuple[np.ndarray, np.ndarray]:
+    """``scale = 1/(255*std)``, ``bias = -mean/std`` per output channel slot, in fp32, so that
+    ``v*scale + bias == (v/255 - mean)/std``.  With neither given the float output is ``v``."""
+    if mean is None and std is None:
+        return np.ones(3, np.float32), np.zeros(3, np.float32)
+    mean = np.asarray((0.0, 0.0, 0.0) if mean is None else mean, np.float64).reshape(3)
+    std = np.asarray((1 / 255.0,) * 3 if std is None else std, np.float64).reshape(3)
+    if np.any(std == 0):
+        raise RuntimeError("std must be non-zero.")
+    return (1.0 / (255.0 * std)).astype(np.float32), (-mean / std).astype(np.float32)
+
+
+def synchronize_stream(device_config: CUDAConfig) -> None:
+    """Block until the stream of ``device_config`` is idle."""
+    _lib.check(_lib.lib().b2_stream_synchronize(device_config.device_index,
+                                                device_config.stream))
+
+
+# ---- colour conversion: the reference entry points -------------------------------------------
+
+
+def _nv12_planar(buffers: Any, device_config: CUDAConfig, coeff: int, sync: bool,
+                 bgr: bool) -> CUDABuffer:
+    ptr, shape, typestr = _cai(buffers)
+    if len(shape) != 3:
+        raise RuntimeError(
+            f"Expected 3D buffer [num_frames, h*1.5, width]. Found: {len(shape)}D")
+    if typestr[1:] != "u1":
+        raise RuntimeError(f"Expected uint8 buffer. Found: {typestr}")
+    n, h2, w = shape
+    if h2 % 3:
+        raise RuntimeError(
+            f"The height of NV12 image (h*1.5) must be divisible by 3. Found: {h2}")
+    _device_of(buffers, device_config)
+    h = h2 // 3 * 2
+    out = cuda_buffer((n, 3, h, w), device_config)
+    L = _lib.lib()
+    # The reference launcher runs on the calling thread's current device.
+    args = _lib.DenseArgs()
+    args.struct_size = ctypes.sizeof(_lib.DenseArgs)
+    args.device = device_config.device_index
+    args.y, args.u = ptr, ptr + h * w
+    args.y_pitch = args.uv_pitch = w
+    args.y_frame_stride = args.uv_frame_stride = h2 * w
+    args.src_format, args.width, args.height, args.num_frames = NV12, w, h, n
+    args.matrix_coeff, args.full_range = int(coeff), 0
+    args.dst, args.dst_frame_stride = out.data_ptr, 0
+    args.layout, args.dtype, args.order = NCHW, U8, BGR if bgr else RGB
+    args.scale = (ctypes.c_float * 3)(1, 1, 1)
+    args.bias = (ctypes.c_float * 3)(0, 0, 0)
+    _lib.check(L.b2_convert_dense(ctypes.byref(args), device_config.stream))
+    out._owner = buffers  # keep the source alive until the consumer lets go of the result
+    if sync:
+        synchronize_stream(device_config)
+    return out
+
+
+def nv12_to_rgb(buffers: Any, *, device_config: CUDAConfig, coeff: int = 1,
+                sync: bool = False) -> CUDABuffer:
+    """Convert a batch of NV12 images ``[num_frames, H*1.5, W]`` to planar RGB
+    ``(num_frames, 3, H, W)``.
+
+    ``coeff`` selects the matrix (1 BT709 default, 4 FCC, 5 BT470, 6 BT601, 7 SMPTE240M,
+    8 YCgCo, 9 BT2020, 10 BT2020C; anything else is silently 1).  The kernel runs on
+    ``device_config.stream``; with ``sync=True`` the call waits for it.
+    """
+    return _nv12_planar(buffers, device_config, coeff, sync, bgr=False)
+
+
+def nv12_to_bgr(buffers: Any, *, device_config: CUDAConfig, coeff: int = 1,
+                sync: bool = False) -> CUDABuffer:
+    """Same as :func:`nv12_to_rgb`, but the order of the colour channels is BGR."""
+    return _nv12_planar(buffers, device_config, coeff, sync, bgr=True)
+
+
+# ---- colour conversion: general dense form ----------------------------------------------------
+
+
+def convert_nv12(buffers: Any, *, device_config: CUDAConfig, coeff: int = 1,
+                 full_range: bool = False, src_format: str = "nv12", layout: str = "NCHW",
+                 dtype: str = "uint8", order: str = "rgb", mean=None, std=None,
+                 sync: bool = False) -> CUDABuffer:
+    """Convert ``[N, H*1.5, W]`` NV12 or I420 frames in one pass to ``NCHW``/``NHWC``
+    ``uint8``/``float32``/``bfloat16`` RGB or BGR, optionally normalised.
+
+    For float outputs the value is ``(v/255 - mean)/std`` per output channel when ``mean``/
+    ``std`` are given (0..1 units, in output channel order), else the plain 0..255 value.
+    ``bfloat16`` results are exposed as 2-byte words (``|u2``); view them as ``torch.bfloat16``.
+    I420 input is the layout ``convert_frames`` produces for ``yuv420p``: Y rows, then the U
+    plane and the V plane as contiguous ``H/2 x W/2`` blocks.
+    """
+    ptr, shape, typestr = _cai(buffers)
+    if len(shape) != 3:
+        raise RuntimeError(
+            f"Expected 3D buffer [num_frames, h*1.5, width]. Found: {len(shape)}D")
+    if typestr[1:] != "u1":
+        raise RuntimeError(f"Expected uint8 buffer. Found: {typestr}")
+    n, h2, w = shape
+    if h2 % 3:
+        raise RuntimeError(
+            f"The height of NV12 image (h*1.5) must be divisible by 3. Found: {h2}")
+    try:
+        fmt, lay, dt, od = (_FORMATS[src_format.lower()], _LAYOUTS[layout], _DTYPES[dtype],
+                            _ORDERS[order.lower()])
+    except KeyError as e:
+        raise RuntimeError(f"Unsupported option: {e}") from None
+    h = h2 // 3 * 2
+    if fmt == I420 and w % 2:
+        # the U and V blocks are [H/2, W/2] planes only when W is even
+        raise RuntimeError(f"I420 width must be even. Found: {w}")
+    _device_of(buffers, device_config)
+    ec, depth = _OUT_ELEM[dt]
+    oshape = (n, 3, h, w) if lay == NCHW else (n, h, w, 3)
+    out = cuda_buffer(oshape, device_config, ec, depth)
+    scale, bias = _scale_bias(mean, std)
+    a = _lib.DenseArgs()
+    a.struct_size = ctypes.sizeof(_lib.DenseArgs)
+    a.device = device_config.device_index
+    a.y = ptr
+    if fmt == NV12:
+        a.u, a.uv_pitch = ptr + h * w, w
+    else:
+        a.u, a.v, a.uv_pitch = ptr + h * w, ptr + h * w + (h // 2) * (w // 2), w // 2
+    a.y_pitch = w
+    a.y_frame_stride = a.uv_frame_stride = h2 * w
+    a.src_format, a.width, a.height, a.num_frames = fmt, w, h, n
+    a.matrix_coeff, a.full_range = int(coeff), int(bool(full_range))
+    a.dst, a.dst_frame_stride = out.data_ptr, 0
+    a.layout, a.dtype, a.order = lay, dt, od
+    a.scale = (ctypes.c_float * 3)(*scale.tolist())
+    a.bias = (ctypes.c_float * 3)(*bias.tolist())
+    _lib.check(_lib.lib().b2_convert_dense(ctypes.byref(a), device_config.stream))
+    out._owner = buffers
+    if sync:
+        synchronize_stream(device_config)
+    return out
+
+
+# ---- fused resize ------------------------------------------------------------------------------
+
+
+def make_image_descs(widths: Sequence[int], heights: Sequence[int], *, src_format: str = "nv12",
+                     offsets: Sequence[int] | None = None, resize: tuple[int, int] | None = None,
+                     resize_shorter: int | None = None, crop: tuple[int, int] | None = None,
+                     out_size: tuple[int, int] | None = None) -> tuple[np.ndarray, tuple[int, int]]:
+    """Build the descriptor table of a (possibly ragged) packed batch.
+
+    Images are packed back to back (``offsets[i]`` = byte offset of image ``i``; computed when
+    omitted), each as Y rows then chroma (NV12: interleaved UV rows; I420: U block, V block).
+    Geometry: ``resize=(w, h)`` stretches every image to that size; ``resize_shorter=s`` scales
+    the shorter side to ``s`` and the longer to ``int(s * long / short)``; then
+    ``crop=(w, h)`` takes the centre window with offset ``int(round((dim - crop) / 2))``.
+    Returns ``(descs, (out_w, out_h))``.
+    """
+    w = np.asarray(widths, np.int64)
+    h = np.asarray(heights, np.int64)
+    if w.shape != h.shape or w.ndim != 1:
+        raise RuntimeError("widths and heights must be 1-D and of equal length")
+    if np.any(w < 1) or np.any(h < 1):
+        raise RuntimeError("image sizes must be positive")
+    fmt = _FORMATS[src_format.lower()]
+    n = len(w)
+    cw, chh = (w + 1) // 2, (h + 1) // 2
+    frame_bytes = w * h + 2 * cw * chh
+    if offsets is None:
+        off = np.concatenate([[0], np.cumsum(frame_bytes)[:-1]]) if n else np.zeros(0, np.int64)
+    else:
+        off = np.asarray(offsets, np.int64)
+    if resize is not None and resize_shorter is not None:
+        raise RuntimeError("give either resize or resize_shorter")
+    if resize is not None:
+        rw = np.full(n, int(resize[0]), np.int64)
+        rh = np.full(n, int(resize[1]), np.int64)
+    elif resize_shorter is not None:
+        s = int(resize_shorter)
+        rw = np.where(w <= h, s, (s * w) // h)
+        rh = np.where(w <= h, (s * h) // w, s)
+    else:
+        rw, rh = w.copy(), h.copy()
+    if crop is not None:
+        ow, oh = int(crop[0]), int(crop[1])
+        if np.any(rw < ow) or np.any(rh < oh):
+            raise RuntimeError("crop window larger than the resized image")
+        cx = np.rint((rw - ow) / 2.0).astype(np.int64)
+        cy = np.rint((rh - oh) / 2.0).astype(np.int64)
+    else:
+        if n and (np.any(rw != rw[0]) or np.any(rh != rh[0])):
+            raise RuntimeError("without crop every image must resize to the same size")
+        ow, oh = (int(rw[0]), int(rh[0])) if n else (0, 0)
+        cx = cy = np.zeros(n, np.int64)
+    if out_size is not None and tuple(out_size) != (ow, oh):
+        raise RuntimeError(f"out_size {out_size} does not match the geometry {(ow, oh)}")
+    d = np.zeros(n, DESC_DTYPE)
+    d["y_off"] = off
+    d["u_off"] = off + w * h
+    if fmt == NV12:
+        d["uv_pitch"] = 2 * cw
+    else:
+        d["v_off"] = off + w * h + cw * chh
+        d["uv_pitch"] = cw
+    d["y_pitch"], d["src_w"], d["src_h"] = w, w, h
+    d["crop_x"], d["crop_y"] = cx, cy
+    d["scale_x"] = w.astype(np.float32) / rw.astype(np.float32)
+    d["scale_y"] = h.astype(np.float32) / rh.astype(np.float32)
+    return d, (ow, oh)
+
+
+def convert_resize(base: Any, descs: Any, *, out_size: tuple[int, int], max_src_w: int,
+                   device_config: CUDAConfig, src_format: str = "nv12", coeff: int = 1,
+                   full_range: bool = False, layout: str = "NCHW", dtype: str = "uint8",
+                   order: str = "rgb", mean=None, std=None, sync: bool = False) -> CUDABuffer:
+    """Fused colour conversion, bilinear resize, crop and normalise over a packed batch.
+
+    ``base`` is a device byte buffer holding every image, ``descs`` a device copy of the table
+    from :func:`make_image_descs` (``[N]`` of ``DESC_DTYPE``, i.e. ``N*64`` bytes), ``out_size``
+    is ``(out_w, out_h)`` and ``max_src_w`` the widest source image in the table.
+    Returns ``[N,3,out_h,out_w]`` (``NCHW``) or ``[N,out_h,out_w,3]``.
+    """
+    bptr, _, _ = _cai(base)
+    dptr, dshape, dtypestr = _cai(descs)
+    nbytes = int(np.prod(dshape, dtype=np.int64)) * int(dtypestr[2:])
+    if nbytes % 64:
+        raise RuntimeError("descs must be a whole number of 64-byte descriptors")
+    n = nbytes // 64
+    try:
+        fmt, lay, dt, od = (_FORMATS[src_format.lower()], _LAYOUTS[layout], _DTYPES[dtype],
+                            _ORDERS[order.lower()])
+    except KeyError as e:
+        raise RuntimeError(f"Unsupported option: {e}") from None
+    ow, oh = int(out_size[0]), int(out_size[1])
+    _device_of(base, device_config)
+    ec, depth = _OUT_ELEM[dt]
+    oshape = (n, 3, oh, ow) if lay == NCHW else (n, oh, ow, 3)
+    out = cuda_buffer(oshape, device_config, ec, depth)
+    scale, bias = _scale_bias(mean, std)
+    a = _lib.ResizeArgs()
+    a.struct_size = ctypes.sizeof(_lib.ResizeArgs)
+    a.device = device_config.device_index
+    a.base, a.descs = bptr, dptr
+    a.num_images, a.src_format, a.out_w, a.out_h = n, fmt, ow, oh
+    a.matrix_coeff, a.full_range = int(coeff), int(bool(full_range))
+    a.layout, a.dtype, a.order = lay, dt, od
+    a.max_src_w = int(max_src_w)
+    a.dst, a.dst_image_stride = out.data_ptr, 0
+    a.scale = (ctypes.c_float * 3)(*scale.tolist())
+    a.bias = (ctypes.c_float * 3)(*bias.tolist())
+    _lib.check(_lib.lib().b2_convert_resize(ctypes.byref(a), device_config.stream))
+    out._owner = (base, descs)
+    if sync:
+        synchronize_stream(device_config)
+    return out
+
+
+# ---- transfer ----------------------------------------------------------------------------------
+
+_NP_CLASS = {"u": "u", "i": "i", "f": "f", "b": "u"}
+
+
+def transfer_buffer(buffer: Any, *, device_config: CUDAConfig) -> CUDABuffer:
+    """Move host data to the GPU; shape and element type are preserved.
+
+    Accepts a :class:`CPUBuffer`, a NumPy array or a CPU torch tensor (non-contiguous inputs are
+    made contiguous first).  Pinned sources are copied asynchronously on
+    ``device_config.stream`` and the stream is then synchronised; pageable sources use a blocking
+    copy -- in both cases the data is on the device when the call returns.
+    """
+    keep: Any = buffer
+    if isinstance(buffer, CPUBuffer):
+        ptr, shape, ec, depth = buffer.data_ptr, buffer.shape, buffer.elem_class, buffer.depth
+        pinned = buffer.is_pinned()
+    else:
+        pinned = False
+        if hasattr(buffer, "is_cuda") and hasattr(buffer, "numpy"):  # torch tensor
+            if buffer.is_cuda:
+                raise RuntimeError("transfer_buffer expects a CPU tensor.")
+            pinned = bool(buffer.is_pinned()) and buffer.is_contiguous()
+            arr = buffer.contiguous().numpy()
+        else:
+            arr = np.ascontiguousarray(buffer)
+        if arr.dtype.kind not in _NP_CLASS:
+            raise RuntimeError(f"Unsupported dtype: {arr.dtype}")
+        keep = arr
+        ptr, shape = arr.ctypes.data, arr.shape
+        ec, depth = _NP_CLASS[arr.dtype.kind], arr.dtype.itemsize
+    out = cuda_buffer(shape, device_config, ec, depth)
+    _lib.check(_lib.lib().b2_transfer_h2d(out.data_ptr, ptr, out.nbytes, int(pinned),
+                                          device_config.device_index, device_config.stream))
+    del keep
+    return out
+
+
+def transfer_buffer_cpu(buffer: Any) -> CPUBuffer:
+    """Move a CUDA array (anything with ``__cuda_array_interface__``) to host memory."""
+    ptr, shape, typestr = _cai(buffer)
+    ec, depth = typestr[1], int(typestr[2:])
+    dev = getattr(buffer, "device_index", None)
+    if dev is None:
+        dev = getattr(getattr(buffer, "device", None), "index", 0) or 0
+    out = CPUBuffer(shape, _NP_CLASS.get(ec, "u"), depth)
+    _lib.check(_lib.lib().b2_transfer_d2h(out.data_ptr, ptr, out.nbytes, dev))
+    return out
+
+
+# ---- frame batching ----------------------------------------------------------------------------
+
+
+class FrameBatcher:
+    """Batches pitched NV12 decoder surfaces into packed ``[num_frames, H*3/2, W]`` buffers.
+
+    Same observable behaviour as the reference's ``FrameBuffer`` -- ``push`` a surface, full
+    batches queue up, ``flush`` emits a short last batch whose ``shape[0]`` is the number of
+    frames pushed -- but surfaces are only recorded on ``push``; one gather kernel copies the
+    whole batch when it completes, with no per-frame stream synchronisation.  Surfaces must stay
+    valid until their batch has been emitted.
+    """
+
+    def __init__(self, num_frames: int, width: int, height: int, device_config: CUDAConfig):
+        if num_frames < 1:
+            raise RuntimeError("num_frames must be positive")
+        if width < 1 or height < 1 or height % 2:
+            raise RuntimeError(f"Invalid NV12 frame size: {width}x{height}")
+        self._n, self._w, self._h, self._cfg = int(num_frames), int(width), int(height), \
+            device_config
+        self._pending: list[tuple[int, int]] = []
+        self._queue: list[CUDABuffer] = []
+
+    def empty(self) -> bool:
+        return not self._queue
+
+    def push(self, surface_ptr: int, pitch: int) -> None:
+        if pitch < self._w:
+            raise RuntimeError(f"pitch {pitch} is smaller than the width {self._w}")
+        self._pending.append((int(surface_ptr), int(pitch)))
+        if len(self._pending) == self._n:
+            self._emit()
+
+    def flush(self) -> None:
+        if self._pending:
+            self._emit()
+
+    def pop(self) -> CUDABuffer:
+        if not self._queue:
+            raise RuntimeError("There is no buffer available.")
+        return self._queue.pop(0)
+
+    def _emit(self) -> None:
+        k = len(self._pending)
+        h2 = self._h + self._h // 2
+        out = cuda_buffer((k, h2, self._w), self._cfg)
+        table = np.array([p for p, _ in self._pending] + [q for _, q in self._pending], np.int64)
+        dtab = transfer_buffer(table, device_config=self._cfg)
+        _lib.check(_lib.lib().b2_gather_surfaces(
+            dtab.data_ptr, dtab.data_ptr + 8 * k, k, self._w, self._h, out.data_ptr,
+            self._cfg.device_index, self._cfg.stream))
+        out._owner = dtab
+        self._pending = []
+        self._queue.append(out)
+
+
+def frame_checksum(buffer: Any, *, device_config: CUDAConfig) -> np.ndarray:
+    """Per-frame 64-bit checksum of a CUDA array, first dimension = frames (blocking)."""
+    ptr, shape, typestr = _cai(buffer)
+    n = shape[0] if shape else 0
+    frame_bytes = int(np.prod(shape[1:], dtype=np.int64)) * int(typestr[2:]) if n else 0
+    if n == 0:
+        return np.zeros(0, np.uint64)
+    out = cuda_buffer((n,), device_config, "u", 8)
+    _lib.check(_lib.lib().b2_frame_checksum(ptr, frame_bytes, n, out.data_ptr,
+                                            device_config.device_index, device_config.stream))
+    synchronize_stream(device_config)
+    host = transfer_buffer_cpu(out)
+    return np.array(host, copy=True).reshape(n)
