@@ -1,0 +1,375 @@
+"""Benchmark of the post-decode frame path: 1080p NV12 -> interleaved RGB, frames/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" converts one batch of 64 synthetic 1920x1080 NV12 frames (BT.709 limited range) to
+interleaved RGB u8 with a single kernel launch.  Inputs are seeded synthetic frames with the
+workload's value distributions (Y uniform in [16,235], UV uniform in [16,240]); no dataset is
+involved.  For N > 1 launch with ``torch.distributed.run``; every rank converts its own 64
+frames per step on its own GPU (weak scaling, no collective on the data path).
+
+Prints one JSON line (rank 0).  ``value`` is frames/s with inputs resident in HBM; ``e2e`` is the
+same metric through the public API from pinned host memory; ``roofline`` relates the kernel to
+the measured HBM copy bandwidth; ``cpu_baseline`` times the reference's CPU arithmetic on a
+bounded sample on this machine's cores.  ``--impl reference`` times only that CPU path.
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+N_FRAMES, W, H = 64, 1920, 1080
+FRAME_IN = W * H * 3 // 2
+FRAME_OUT = W * H * 3
+ALGO_BYTES_PER_FRAME = FRAME_IN + FRAME_OUT  # 9,331,200
+METRIC = "1080p NV12->RGB frames/s"
+WORKLOAD = "64 x 1920x1080 NV12 -> interleaved RGB u8 (NHWC), BT.709 limited range"
+ROTATE = 4  # distinct input batches cycled through, so no step finds its input in L2
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dense kernel on this workload,
+# from the ncu capture summarised in profiles/ (None until a capture exists).
+NCU_TRAFFIC_BYTES_PER_LAUNCH: int | None = None
+
+
+def measured_peak() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict | None:
+        rows = [l.split(", ") for l in self.lines if l and l[0].isdigit()]
+        rows = [r for r in rows if len(r) >= 6]
+        if not rows:
+            return None
+        sm = sorted(int(r[0]) for r in rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].strip() == "Active" for r in rows)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": int(rows[0][1]), "samples": len(rows),
+                "reasons": reasons}
+
+
+# ---- the reference's CPU path -------------------------------------------------------------------
+
+
+def cpu_cores() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def make_cpu_runner(frames: int):
+    """Returns (run_once, kind, description) converting ``frames`` 1080p I420 frames to rgb24 into
+    one contiguous buffer with all host cores."""
+    from oracle import swscale_ref
+    from tests import synth
+
+    cores = cpu_cores()
+    batch = synth.i420_batch_gradient(min(frames, 8), W, H, config=1)
+    reps = -(-frames // batch.shape[0])
+    batch = np.concatenate([batch] * reps)[:frames]
+    out = np.empty((frames, H, W, 3), np.uint8)
+    if swscale_ref.available():
+        conv = swscale_ref.BatchConverter(W, H, cores)
+        conv(batch[:cores], out[:cores])  # first call builds swscale's tables
+        return (lambda: conv(batch, out)), "reference", (
+            f"libswscale (the library the reference's CPU path converts with), yuv420p->rgb24 "
+            f"BT.709 limited->full into one contiguous buffer, {frames} frames 1920x1080 per step, "
+            f"one SwsContext per thread")
+    import oracle
+
+    flat = batch.reshape(-1)
+    h2 = H * 3 // 2
+
+    def run():
+        oracle.convert_dense(batch, flat[H * W:], flat[H * W + (H // 2) * (W // 2):], width=W,
+                             height=H, num_frames=frames, y_pitch=W, uv_pitch=W // 2,
+                             y_frame_stride=h2 * W, uv_frame_stride=h2 * W,
+                             src_format=oracle.I420, layout=oracle.NHWC, out=out)
+
+    return run, "port", (f"C restatement of the reference kernel arithmetic with OpenMP (swscale "
+                         f"unavailable on this box), {frames} frames 1920x1080 per step")
+
+
+def time_cpu(frames: int, steps: int, warmup: int, budget_s: float = 60.0) -> dict:
+    """Time ``steps`` steps of the CPU path.  A step is at most ``frames`` frames; it is cut down
+    (never below 8) so that all steps together take about ``budget_s`` seconds."""
+    probe, _, _ = make_cpu_runner(8)
+    probe()
+    t0 = time.perf_counter()
+    probe()
+    rate = 8 / (time.perf_counter() - t0)
+    frames = int(max(8, min(frames, budget_s * rate / max(steps, 1))))
+    run, kind, desc = make_cpu_runner(frames)
+    for _ in range(warmup):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        run()
+    dt = time.perf_counter() - t0
+    return {"value": frames * steps / dt, "unit": "frames/s", "cores": cpu_cores(), "kind": kind,
+            "sample": desc, "ms_per_step": 1e3 * dt / steps, "frames_per_step": frames}
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    r = time_cpu(N_FRAMES, args.steps, max(args.warmup, 1))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": r["value"], "unit": "frames/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "frames_per_step": r["frames_per_step"],
+                   "note": "CPU path takes yuv420p (what FFmpeg decoders emit) instead of NV12; "
+                           "a step is a bounded sample of the 64-frame batch"},
+        "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": r["value"], "unit": "frames/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---- our arm ------------------------------------------------------------------------------------
+
+
+def synth_batch_on_device(torch, device, seed: int):
+    g = torch.Generator(device=device).manual_seed(seed)
+    src = torch.empty((N_FRAMES, H * 3 // 2, W), dtype=torch.uint8, device=device)
+    src[:, :H] = torch.randint(16, 236, (N_FRAMES, H, W), dtype=torch.uint8, device=device,
+                               generator=g)
+    src[:, H:] = torch.randint(16, 241, (N_FRAMES, H // 2, W), dtype=torch.uint8, device=device,
+                               generator=g)
+    return src
+
+
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    import spdl_b200.io as io
+    from spdl_b200 import _lib
+    from spdl_b200.sharding import ShardWorker, gather_stats, rank_info
+
+    info = rank_info()
+    multi = info.world_size > 1
+    if multi:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", info.local_rank))
+    worker = ShardWorker(info)
+    dev, stream, cfg = worker.device, worker.stream, worker.config
+    L = _lib.lib()
+    K, Wm = args.steps, max(args.warmup, 3)
+
+    inputs = [synth_batch_on_device(torch, dev, 2000 + 17 * info.rank + i) for i in range(ROTATE)]
+    outputs = [torch.empty((N_FRAMES, H, W, 3), dtype=torch.uint8, device=dev) for _ in range(2)]
+    torch.cuda.synchronize(dev)
+
+    def dense_args(src, dst):
+        a = _lib.DenseArgs()
+        a.struct_size = ctypes.sizeof(_lib.DenseArgs)
+        a.device = info.local_rank
+        a.y, a.u = src.data_ptr(), src.data_ptr() + H * W
+        a.y_pitch = a.uv_pitch = W
+        a.y_frame_stride = a.uv_frame_stride = FRAME_IN
+        a.src_format, a.width, a.height, a.num_frames = _lib.NV12, W, H, N_FRAMES
+        a.matrix_coeff, a.full_range = 1, 0
+        a.dst, a.dst_frame_stride = dst.data_ptr(), 0
+        a.layout, a.dtype, a.order = _lib.NHWC, _lib.U8, _lib.RGB
+        a.scale = (ctypes.c_float * 3)(1, 1, 1)
+        a.bias = (ctypes.c_float * 3)(0, 0, 0)
+        return a
+
+    calls = [dense_args(inputs[i % ROTATE], outputs[i % 2]) for i in range(ROTATE * 2)]
+    launches = 0
+
+    def step(i):
+        nonlocal launches
+        _lib.check(L.b2_convert_dense(ctypes.byref(calls[i % len(calls)]), cfg.stream))
+        launches += 1
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if multi:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    # -- kernel-resident timing: K steps, CUDA events on the launching stream ---------------------
+    for i in range(Wm):
+        step(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches = 0
+    with ClockSampler(info.local_rank) as clocks:
+        e0.record(stream)
+        for i in range(K):
+            step(i)
+        e1.record(stream)
+        barrier()
+    ms_total = e0.elapsed_time(e1)
+    timed_launches = launches
+
+    # -- end to end through the public API: pinned host NV12 -> H2D -> convert -> checksum -> D2H -
+    host = [io.CPUBuffer((N_FRAMES, H * 3 // 2, W), "u", 1,
+                         io.cpu_storage(N_FRAMES * FRAME_IN, pin_memory=True)) for _ in range(2)]
+    for hb, src in zip(host, inputs):
+        _lib.check(L.b2_transfer_d2h(hb.data_ptr, src.data_ptr(), hb.nbytes, info.local_rank))
+
+    def e2e_step(i):
+        d = io.transfer_buffer(host[i % 2], device_config=cfg)
+        rgb = io.convert_nv12(d, device_config=cfg, layout="NHWC")
+        return io.frame_checksum(rgb, device_config=cfg)
+
+    with torch.cuda.stream(stream):
+        for i in range(Wm):
+            sums = e2e_step(i)
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(K):
+            sums = e2e_step(i)
+        torch.cuda.synchronize(dev)
+        e2e_s = time.perf_counter() - t0
+    assert sums.shape == (N_FRAMES,)
+
+    # -- max over ranks ----------------------------------------------------------------------------
+    per_rank = gather_stats([ms_total, e2e_s], device=dev)
+    ms_max = max(r[0] for r in per_rank)
+    e2e_max = max(r[1] for r in per_rank)
+    total_frames = N_FRAMES * K * info.world_size
+
+    if info.rank == 0:
+        peak, peak_kind = measured_peak()
+        ms_launch = ms_total / K
+        achieved = N_FRAMES * ALGO_BYTES_PER_FRAME / (ms_launch * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": total_frames / (ms_max * 1e-3), "unit": "frames/s",
+            "n_gpus": info.world_size, "steps": K, "warmup": Wm, "ms_per_step": ms_max / K,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "frames_per_step_per_gpu": N_FRAMES,
+                       "l2": f"inputs (199 MB per batch) exceed L2 and rotate over {ROTATE} "
+                             f"batches",
+                       "sharding": "each rank converts its own frames; no data-path collective"},
+            "e2e": {"value": total_frames / e2e_max, "unit": "frames/s",
+                    "h2d_bytes_per_step": N_FRAMES * FRAME_IN, "d2h_bytes_per_step": N_FRAMES * 8,
+                    "note": "pinned NV12 -> transfer_buffer -> convert_nv12 -> frame_checksum -> "
+                            "host, per step, host-timed"},
+            "gpu_launches": timed_launches,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                         "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)"
+                         if peak_kind == "measured" else "fallback 6650 GB/s",
+                         "algorithmic_bytes_per_launch": N_FRAMES * ALGO_BYTES_PER_FRAME,
+                         "kernel": "dense_vec_kernel<NV12,NHWC,u8>", "ms_per_launch": ms_launch},
+            "clocks": clocks.summary(),
+        }
+        if info.world_size == 1:
+            line["cpu_baseline"] = {k: v for k, v in time_cpu(N_FRAMES, 5, 1, 15.0).items()
+                                    if k not in ("ms_per_step", "frames_per_step")}
+            ref = reference_kernel_fps(torch, inputs[0], cfg)
+            if ref is not None:
+                line["reference_gpu_kernel"] = ref
+        print(json.dumps(line), flush=True)
+    if multi:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def reference_kernel_fps(torch, src, cfg) -> dict | None:
+    """The reference's own kernel (planar RGB, compiled unmodified for sm_100a) on the same input,
+    as the GPU-side kernel to beat.  Informational; absent when oracle/_ref was not built."""
+    import oracle
+
+    ref = oracle.ref_kernel()
+    if ref is None:
+        return None
+    dst = torch.empty((N_FRAMES, 3, H, W), dtype=torch.uint8, device=src.device)
+    stream = torch.cuda.current_stream(src.device)
+
+    def run():
+        ref.ref_nv12_to_planar_rgb(stream.cuda_stream, src.data_ptr(), W, dst.data_ptr(), W, W, H,
+                                   N_FRAMES, 1)
+
+    for _ in range(3):
+        run()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record(stream)
+    for _ in range(20):
+        run()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 20
+    return {"value": N_FRAMES / (ms * 1e-3), "unit": "frames/s", "layout": "planar RGB u8",
+            "gb_per_s": N_FRAMES * ALGO_BYTES_PER_FRAME / (ms * 1e-3) / 1e9}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

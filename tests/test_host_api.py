@@ -1,0 +1,259 @@
+"""Host-side logic that needs no GPU: configuration, storage, frame batching on the CPU,
+descriptor tables, the library's exported symbols and the transfer helper's traversal."""
+
+import ctypes
+import dataclasses
+import re
+from collections import namedtuple
+from pathlib import Path
+from unittest import mock
+
+import numpy as np
+import pytest
+
+import spdl_b200.io as io
+from spdl_b200 import _build, _lib
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def test_library_exports_every_declared_symbol():
+    """Every function include/b2frames.h declares is exported by the built library (no compute
+    call is made)."""
+    _build.build()
+    header = (ROOT / "include" / "b2frames.h").read_text()
+    declared = set(re.findall(r"B2_API\s+[\w\s\*]+?\b(b2_\w+)\s*\(", header))
+    assert declared == set(_lib.EXPORTS)
+    handle = ctypes.CDLL(str(_lib.LIB_PATH))
+    for name in declared:
+        assert hasattr(handle, name), name
+    assert _lib.lib().b2_abi_version() == 1
+    assert _lib.lib().b2_last_error() == b""
+
+
+def test_struct_layouts_match_header_sizes():
+    assert ctypes.sizeof(_lib.ImageDesc) == 64 == io.DESC_DTYPE.itemsize
+    # field order of the ctypes mirrors follows the header; offsets that matter to the kernels
+    assert _lib.DenseArgs.y.offset == 8 and _lib.DenseArgs.y_pitch.offset == 56
+    assert _lib.ResizeArgs.base.offset == 8 and _lib.ResizeArgs.dst.offset == 64
+
+
+def test_status_and_message_without_a_gpu():
+    L = _lib.lib()
+    assert L.b2_convert_dense(None, None) != 0
+    assert b"null" in L.b2_last_error()
+    a = _lib.DenseArgs()
+    a.struct_size = 4
+    assert L.b2_convert_dense(ctypes.byref(a), None) == 1
+    assert b"struct_size" in L.b2_last_error()
+    a.struct_size = ctypes.sizeof(_lib.DenseArgs)
+    a.layout = 7
+    assert L.b2_convert_dense(ctypes.byref(a), None) == 1
+    a.layout = 0
+    a.width = -1
+    assert L.b2_convert_dense(ctypes.byref(a), None) == 1
+    a.width, a.height, a.num_frames = 16, 8, 0
+    assert L.b2_convert_dense(ctypes.byref(a), None) == 0  # nothing to do
+    assert L.b2_last_error() == b""
+    with pytest.raises(RuntimeError, match="struct_size"):
+        a.struct_size = 3
+        _lib.check(L.b2_convert_dense(ctypes.byref(a), None))
+    assert L.b2_nv12_to_planar_rgb(None, None, 8, None, 8, 8, 4, 0, 1) == 0
+    assert L.b2_nv12_to_planar_rgb(None, None, 8, None, 8, 8, 4, 1, 1) == 1
+    assert L.b2_gather_surfaces(None, None, 1, 8, 3, None, 0, None) == 1
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "nope.so")
+    with pytest.raises(RuntimeError, match="no fallback"):
+        _lib.lib()
+
+
+def test_cuda_config():
+    cfg = io.cuda_config(device_index=1)
+    assert (cfg.device_index, cfg.stream, cfg.allocator) == (1, 0x2, None)
+    cfg = io.cuda_config(0, stream=0, allocator=(lambda s, d, st: 0, lambda p: None))
+    assert cfg.stream == 0 and callable(cfg.allocator[0])
+    with pytest.raises(TypeError):
+        io.cuda_config("0")
+    with pytest.raises(TypeError):
+        io.cuda_config(0, allocator=(1, 2))
+    with pytest.raises(dataclasses.FrozenInstanceError):
+        cfg.stream = 5
+
+
+def test_cpu_storage_errors():
+    # tests/cuda/pin_memory_test.py:69-75 of the reference
+    with pytest.raises(RuntimeError):
+        io.cpu_storage(0, pin_memory=False)
+    with pytest.raises(TypeError):
+        io.cpu_storage(-1, pin_memory=False)
+    s = io.cpu_storage(128, pin_memory=False)
+    assert s.size == 128 and not s.is_pinned() and s.as_array().shape == (128,)
+
+
+def _yuv420(n, w, h, pad=3):
+    rng = np.random.default_rng(0)
+    return io.Frames("yuv420p", w, h, [[rng.integers(0, 256, (h, w + pad), dtype=np.uint8),
+                                        rng.integers(0, 256, (h // 2, w // 2 + pad), dtype=np.uint8),
+                                        rng.integers(0, 256, (h // 2, w // 2 + pad), dtype=np.uint8)]
+                                       for _ in range(n)])
+
+
+def test_convert_frames_shapes():
+    f = _yuv420(5, 16, 8)
+    b = io.convert_frames(f)
+    assert b.shape == (5, 1, 12, 16)
+    a = io.to_numpy(b)
+    assert (a[3, 0, :8] == f.planes[3][0][:, :16]).all()
+    assert (a[3, 0, 8:].reshape(-1)[:32].reshape(4, 8) == f.planes[3][1][:, :8]).all()
+    assert (a[3, 0, 8:].reshape(-1)[32:].reshape(4, 8) == f.planes[3][2][:, :8]).all()
+    assert io.convert_frames([f, f]).shape == (2, 5, 1, 12, 16)
+
+    rng = np.random.default_rng(1)
+    rgb = io.Frames("rgb24", 8, 4, [[rng.integers(0, 256, (4, 30), dtype=np.uint8)] for _ in range(3)])
+    assert io.convert_frames(rgb).shape == (3, 4, 8, 3)
+    img = io.Frames("rgb24", 8, 4, rgb.planes[:1], media="image")
+    assert io.convert_frames(img).shape == (4, 8, 3)
+    assert io.convert_frames([img, img]).shape == (2, 4, 8, 3)
+    p444 = io.Frames("yuv444p", 8, 4, [[rng.integers(0, 256, (4, 8), dtype=np.uint8)] * 3])
+    assert io.convert_frames(p444).shape == (1, 3, 4, 8)
+    nv = io.Frames("nv12", 8, 4, [[rng.integers(0, 256, (4, 8), dtype=np.uint8),
+                                   rng.integers(0, 256, (2, 8), dtype=np.uint8)]])
+    assert io.convert_frames(nv).shape == (1, 1, 6, 8)
+    p422 = io.Frames("yuv422p", 8, 4, [[rng.integers(0, 256, (4, 8), dtype=np.uint8),
+                                        rng.integers(0, 256, (4, 4), dtype=np.uint8),
+                                        rng.integers(0, 256, (4, 4), dtype=np.uint8)]])
+    assert io.convert_frames(p422).shape == (1, 1, 8, 8)
+    gray = io.Frames("gray8", 8, 4, [[rng.integers(0, 256, (4, 8), dtype=np.uint8)]])
+    assert io.convert_frames(gray).shape == (1, 4, 8, 1)
+
+
+def test_convert_frames_rgb24_round_trip():
+    # tests/io/reference_frames_test.py:120-135 of the reference: (5,128,128,3) survives bit-exactly
+    src = np.random.default_rng(2).integers(0, 256, (5, 128, 128, 3), dtype=np.uint8)
+    f = io.Frames("rgb24", 128, 128, [[src[i].reshape(128, 384)] for i in range(5)])
+    assert (io.to_numpy(io.convert_frames(f)) == src).all()
+
+
+def test_convert_frames_errors():
+    a, b = _yuv420(2, 16, 8), _yuv420(2, 32, 8)
+    with pytest.raises(RuntimeError):
+        io.convert_frames([a, b])
+    with pytest.raises(RuntimeError):
+        io.convert_frames([])
+    with pytest.raises(RuntimeError):
+        io.convert_frames(a, storage=io.cpu_storage(10, pin_memory=False))
+    with pytest.raises(RuntimeError):
+        io.convert_frames(io.Frames("yuv420p", 15, 8, a.planes))
+    with pytest.raises(RuntimeError):
+        io.convert_frames(io.Frames("p010", 16, 8, a.planes))
+
+
+def test_buffer_keeps_storage_alive():
+    b = io.convert_frames(_yuv420(1, 16, 8))
+    arr = io.to_numpy(b)
+    want = arr.copy()
+    del b
+    assert (arr == want).all()
+
+
+def test_make_image_descs_geometry():
+    d, out = io.make_image_descs([640, 480, 256], [480, 640, 256], src_format="i420",
+                                 resize_shorter=256, crop=(224, 224))
+    assert out == (224, 224)
+    # shorter side 256, longer int(256*long/short) = 341; centre offsets round((dim-224)/2)
+    assert [int(x) for x in d["crop_x"]] == [round((341 - 224) / 2), 16, 16]
+    assert [int(x) for x in d["crop_y"]] == [16, round((341 - 224) / 2), 16]
+    assert np.float32(d["scale_x"][0]) == np.float32(640) / np.float32(341)
+    assert np.float32(d["scale_y"][2]) == np.float32(1.0)
+    assert [int(x) for x in d["y_off"]] == [0, 460800, 921600]
+    assert int(d["u_off"][1]) == 460800 + 480 * 640
+    assert int(d["v_off"][1]) == 460800 + 480 * 640 + 240 * 320
+    assert int(d["uv_pitch"][0]) == 320
+    d, out = io.make_image_descs([1280], [720], resize=(256, 256))
+    assert out == (256, 256) and int(d["uv_pitch"][0]) == 1280 and int(d["v_off"][0]) == 0
+    with pytest.raises(RuntimeError):
+        io.make_image_descs([100], [100], resize=(50, 50), crop=(64, 64))
+    with pytest.raises(RuntimeError):
+        io.make_image_descs([100, 200], [100, 200])
+    with pytest.raises(RuntimeError):
+        io.make_image_descs([100], [100], resize=(50, 50), resize_shorter=10)
+
+
+def test_build_flags():
+    from spdl_b200.io import utils
+
+    assert utils.built_with_cuda() is True
+    assert utils.built_with_nvcodec() is False and utils.built_with_nvjpeg() is False
+
+
+# ---- transfer_tensor: traversal and call order with torch.cuda mocked (no GPU needed) -----------
+
+Pair = namedtuple("Pair", ["a", "b"])
+
+
+@dataclasses.dataclass
+class Sample:
+    x: object
+    tag: str
+    derived: object = dataclasses.field(init=False, default=None)
+
+
+def test_recursive_apply_over_containers():
+    from spdl_b200.io._transfer import _recursive_apply
+
+    fn = lambda v: v * 2 if isinstance(v, int) else v  # noqa: E731
+    s = Sample(3, "t")
+    s.derived = 5
+    out = _recursive_apply(fn, {"l": [1, (2, "s")], "p": Pair(4, [5]), "d": s})
+    assert out["l"] == [2, (4, "s")]
+    assert out["p"] == Pair(8, [10]) and isinstance(out["p"], Pair)
+    assert out["d"].x == 6 and out["d"].tag == "t" and out["d"].derived == 10
+
+
+def test_transfer_tensor_call_order_mocked():
+    import torch
+
+    from spdl_b200.io import _transfer
+
+    events = []
+    stream = mock.MagicMock()
+    stream.synchronize.side_effect = lambda: events.append("sync")
+
+    class FakeCtx:
+        def __enter__(self):
+            events.append("enter")
+
+        def __exit__(self, *a):
+            events.append("exit")
+
+    cpu = torch.arange(6)
+    pinned, moved = mock.MagicMock(), object()
+    pinned.to.side_effect = lambda dev, non_blocking: (events.append(("to", non_blocking)), moved)[1]
+    with mock.patch.object(torch.cuda, "Stream", return_value=stream), \
+            mock.patch.object(torch.cuda, "stream", return_value=FakeCtx()), \
+            mock.patch.object(torch.cuda, "device_count", return_value=1), \
+            mock.patch.object(torch.Tensor, "pin_memory", return_value=pinned):
+        _transfer._THREAD_LOCAL.__dict__.pop("transfer", None)
+        out = _transfer.transfer_tensor([cpu, "keep"], num_caches=2)
+        assert out == [moved, "keep"]
+        assert events == ["enter", ("to", True), "exit", "sync"]
+        tr = _transfer._THREAD_LOCAL.transfer
+        assert tr._batch_cache == [None, out]
+        _transfer.transfer_tensor(cpu)
+        assert tr._batch_cache[0] is out
+    _transfer._THREAD_LOCAL.__dict__.pop("transfer", None)
+
+
+def test_transfer_tensor_rejects_bad_local_rank(monkeypatch):
+    import torch
+
+    from spdl_b200.io import _transfer
+
+    monkeypatch.setenv("LOCAL_RANK", "3")
+    _transfer._THREAD_LOCAL.__dict__.pop("transfer", None)
+    with mock.patch.object(torch.cuda, "device_count", return_value=1):
+        with pytest.raises(RuntimeError):
+            _transfer.transfer_tensor(torch.zeros(1))

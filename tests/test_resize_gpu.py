@@ -1,0 +1,158 @@
+"""Parity of the fused convert -> resize -> crop -> normalise kernel with the oracle."""
+
+import numpy as np
+import pytest
+
+import oracle
+from tests import synth
+
+pytestmark = pytest.mark.gpu
+
+MEAN, STD = (0.485, 0.456, 0.406), (0.229, 0.224, 0.225)
+_O_DT = {"uint8": oracle.U8, "float32": oracle.F32, "bfloat16": oracle.BF16}
+
+
+def _dev(a):
+    import torch
+
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def _run(cfg, data, descs, out_size, fmt, layout, dtype, order="rgb", coeff=1, full_range=False,
+         mean=None, std=None):
+    import spdl_b200.io as io
+
+    max_w = int(descs["src_w"].max())
+    buf = io.convert_resize(_dev(data), _dev(descs.view(np.uint8)), out_size=out_size,
+                            max_src_w=max_w, device_config=cfg, src_format=fmt, coeff=coeff,
+                            full_range=full_range, layout=layout, dtype=dtype, order=order,
+                            mean=mean, std=std, sync=True)
+    got = io.to_torch(buf).cpu().numpy()
+    want = oracle.convert_resize(
+        data, descs, out_w=out_size[0], out_h=out_size[1],
+        src_format=oracle.NV12 if fmt == "nv12" else oracle.I420, coeff=coeff,
+        full_range=full_range, layout=oracle.NCHW if layout == "NCHW" else oracle.NHWC,
+        dtype=_O_DT[dtype], order=oracle.RGB if order == "rgb" else oracle.BGR,
+        sb=oracle.scale_bias(mean, std) if mean is not None else None)
+    return got, want
+
+
+def _compare(got, want, dtype):
+    assert got.shape == want.shape
+    if dtype == "uint8":
+        # same fp32 operations in the same order: bit-exact
+        assert (got == want).all()
+    elif dtype == "float32":
+        np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5)
+    else:
+        a = oracle.bf16_to_f32(got.view(np.uint16))
+        b = oracle.bf16_to_f32(want)
+        # identical up to one bf16 ulp where the fp32 values straddle a rounding boundary
+        np.testing.assert_allclose(a, b, rtol=2 ** -7, atol=1e-6)
+        assert (got.view(np.uint16) == want).mean() > 0.999
+
+
+@pytest.mark.parametrize("src,dst", [((64, 48), (24, 20)), ((320, 240), (160, 120)),
+                                     ((40, 30), (40, 30)), ((30, 20), (50, 44)),
+                                     ((1280, 720), (256, 256)), ((98, 50), (33, 17))])
+@pytest.mark.parametrize("fmt", ["nv12", "i420"])
+@pytest.mark.parametrize("layout,dtype", [("NCHW", "uint8"), ("NHWC", "uint8"),
+                                          ("NCHW", "float32"), ("NHWC", "bfloat16")])
+def test_uniform_resize(cuda_cfg, src, dst, fmt, layout, dtype):
+    import spdl_b200.io as io
+
+    w, h = src
+    n = 3
+    nv = synth.nv12_batch(n, w, h, config=9, index=w)
+    descs, out = io.make_image_descs([w] * n, [h] * n, src_format=fmt, resize=dst)
+    norm = dict(mean=MEAN, std=STD) if dtype != "uint8" else {}
+    got, want = _run(cuda_cfg, nv.reshape(-1), descs, out, fmt, layout, dtype, **norm)
+    _compare(got, want, dtype)
+
+
+def test_crop_equals_slice_of_uncropped(cuda_cfg):
+    """tests/cuda/nvdec_video_decoding_test.py:257-284 of the reference checks the same property
+    for the decoder's crop."""
+    import spdl_b200.io as io
+
+    w, h = 320, 240
+    nv = synth.nv12_batch(2, w, h, config=9, index=8)
+    full_d, fo = io.make_image_descs([w, w], [h, h], resize=(200, 150))
+    crop_d, co = io.make_image_descs([w, w], [h, h], resize=(200, 150), crop=(64, 48))
+    full, _ = _run(cuda_cfg, nv.reshape(-1), full_d, fo, "nv12", "NCHW", "uint8")
+    crop, want = _run(cuda_cfg, nv.reshape(-1), crop_d, co, "nv12", "NCHW", "uint8")
+    cx, cy = int(crop_d["crop_x"][0]), int(crop_d["crop_y"][0])
+    assert (crop == full[:, :, cy:cy + 48, cx:cx + 64]).all()
+    assert (crop == want).all()
+
+
+@pytest.mark.parametrize("dtype", ["uint8", "float32"])
+def test_ragged_i420_shorter_side_centre_crop(cuda_cfg, dtype):
+    """Ragged batch: per-image sizes and offsets, shorter side to 64, centre crop 56x56,
+    full-range BT.601 (JPEG-style)."""
+    import spdl_b200.io as io
+
+    data, ws, hs, offs = synth.ragged_i420(24, lo=64, hi=200, config=5, index=1)
+    descs, out = io.make_image_descs(ws, hs, src_format="i420", offsets=offs, resize_shorter=64,
+                                     crop=(56, 56))
+    assert out == (56, 56)
+    norm = dict(mean=MEAN, std=STD) if dtype != "uint8" else {}
+    got, want = _run(cuda_cfg, data, descs, out, "i420", "NCHW", dtype, coeff=6, full_range=True,
+                     **norm)
+    _compare(got, want, dtype)
+
+
+def test_odd_sizes_and_upscale(cuda_cfg):
+    import spdl_b200.io as io
+
+    data, ws, hs, offs = synth.ragged_i420(6, lo=20, hi=60, config=5, index=2)
+    ws, hs = ws + 1, hs - 1  # odd sizes: chroma planes are ceil(w/2) x ceil(h/2)
+    sizes = ws * hs + 2 * ((ws + 1) // 2) * ((hs + 1) // 2)
+    offs = np.concatenate([[0], np.cumsum(sizes)[:-1]])
+    data = np.random.default_rng(3).integers(0, 256, int(sizes.sum()), dtype=np.uint8)
+    descs, out = io.make_image_descs(ws, hs, src_format="i420", offsets=offs, resize=(80, 72))
+    got, want = _run(cuda_cfg, data, descs, out, "i420", "NHWC", "uint8", order="bgr")
+    _compare(got, want, "uint8")
+
+
+def test_clip_stacking_layout(cuda_cfg):
+    """Clips stack as N x T x C x H x W: frames of clip n are images n*T .. n*T+T-1."""
+    import spdl_b200.io as io
+
+    clips, t, w, h = 2, 4, 128, 72
+    frames = np.concatenate([synth.nv12_clip(t, w, h, config=4, index=i) for i in range(clips)])
+    descs, out = io.make_image_descs([w] * clips * t, [h] * clips * t, resize=(32, 32))
+    got, want = _run(cuda_cfg, frames.reshape(-1), descs, out, "nv12", "NCHW", "uint8", coeff=6)
+    assert (got == want).all()
+    stacked = got.reshape(clips, t, 3, 32, 32)
+    assert (stacked[1, 2] == want[1 * t + 2]).all()
+
+
+def test_4k_to_224_bf16(cuda_cfg):
+    """One 3840x2160 frame -> 224x224 bf16 NCHW normalised (the large-downscale workload)."""
+    import spdl_b200.io as io
+
+    w, h = 3840, 2160
+    nv = synth.nv12_batch(1, w, h, config=3)
+    descs, out = io.make_image_descs([w], [h], resize=(224, 224))
+    got, want = _run(cuda_cfg, nv.reshape(-1), descs, out, "nv12", "NCHW", "bfloat16", order="bgr",
+                     mean=MEAN[::-1], std=STD[::-1])
+    _compare(got, want, "bfloat16")
+
+
+def test_validation(cuda_cfg):
+    import torch
+
+    import spdl_b200.io as io
+
+    base = torch.zeros(1024, dtype=torch.uint8, device="cuda")
+    bad = torch.zeros(65, dtype=torch.uint8, device="cuda")
+    with pytest.raises(RuntimeError):
+        io.convert_resize(base, bad, out_size=(8, 8), max_src_w=16, device_config=cuda_cfg)
+    d, o = io.make_image_descs([16], [16], resize=(8, 8))
+    with pytest.raises(RuntimeError):  # staging limit
+        io.convert_resize(base, _dev(d.view(np.uint8)), out_size=o, max_src_w=1 << 20,
+                          device_config=cuda_cfg)
+    with pytest.raises(RuntimeError):
+        io.convert_resize(base, _dev(d.view(np.uint8)), out_size=o, max_src_w=16,
+                          device_config=cuda_cfg, layout="CHWN")

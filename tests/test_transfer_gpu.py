@@ -1,0 +1,226 @@
+"""Buffer transfer, storage, allocator accounting and array-interface contracts on a GPU.
+
+Modelled on the reference's tests/cuda/buffer_transfer_test.py, tests/cuda/pin_memory_test.py,
+tests/cuda/transfer_test.py and tests/io/buffer_conversion_refcount_test.py.
+"""
+
+import gc
+import sys
+
+import numpy as np
+import pytest
+
+import oracle
+from tests import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _frames(n=4, w=32, h=16):
+    import spdl_b200.io as io
+
+    rng = np.random.default_rng(0)
+    planes = [[rng.integers(0, 256, (h, w * 3 + 5), dtype=np.uint8)] for _ in range(n)]
+    return io.Frames("rgb24", w, h, planes), planes
+
+
+def test_h2d_of_converted_frames_equals_cpu(cuda_cfg):
+    import spdl_b200.io as io
+
+    frames, planes = _frames()
+    cpu = io.convert_frames(frames)
+    dev = io.transfer_buffer(cpu, device_config=cuda_cfg)
+    t = io.to_torch(dev)
+    assert t.is_cuda and tuple(t.shape) == (4, 16, 32, 3)
+    assert (t.cpu().numpy() == io.to_numpy(cpu)).all()
+    assert (io.to_numpy(cpu)[2] == planes[2][0][:, :96].reshape(16, 32, 3)).all()
+
+
+def test_custom_allocator_is_called_and_deleter_runs_on_gc():
+    import torch
+
+    import spdl_b200.io as io
+
+    calls = {"alloc": 0, "free": 0}
+
+    def alloc(size, device, stream):
+        calls["alloc"] += 1
+        assert device == 0 and size > 0
+        return torch.cuda.caching_allocator_alloc(size, device, stream)
+
+    def free(ptr):
+        calls["free"] += 1
+        torch.cuda.caching_allocator_delete(ptr)
+
+    cfg = io.cuda_config(0, stream=torch.cuda.current_stream().cuda_stream,
+                         allocator=(alloc, free))
+    buf = io.transfer_buffer(np.arange(100, dtype=np.int32), device_config=cfg)
+    assert calls == {"alloc": 1, "free": 0}
+    nv = torch.zeros((2, 6, 8), dtype=torch.uint8, device="cuda")
+    out = io.nv12_to_rgb(nv, device_config=cfg, sync=True)
+    assert calls == {"alloc": 2, "free": 0}
+    del buf
+    gc.collect()
+    assert calls["free"] == 1
+    t = io.to_torch(out)
+    del out
+    gc.collect()
+    assert calls["free"] == 1  # the tensor keeps the buffer alive
+    del t
+    gc.collect()
+    assert calls["free"] == 2
+
+
+def test_allocator_that_raises_propagates():
+    import spdl_b200.io as io
+
+    def alloc(size, device, stream):
+        raise MemoryError("no memory today")
+
+    cfg = io.cuda_config(0, allocator=(alloc, lambda p: None))
+    with pytest.raises(MemoryError):
+        io.transfer_buffer(np.zeros(4, np.uint8), device_config=cfg)
+
+
+@pytest.mark.parametrize("dtype", [np.uint8, np.int32, np.int64, np.float32])
+def test_array_round_trip(cuda_cfg, dtype):
+    import torch
+
+    import spdl_b200.io as io
+
+    a = (np.arange(2 * 3 * 5) * 7 % 251).astype(dtype).reshape(2, 3, 5)
+    for src in (a, torch.from_numpy(a)):
+        dev = io.transfer_buffer(src, device_config=cuda_cfg)
+        assert dev.device_index == 0
+        iface = dev.__cuda_array_interface__
+        assert iface["version"] == 2 and iface["shape"] == (2, 3, 5)
+        assert iface["strides"] is None and iface["data"][1] is False
+        assert iface["stream"] == cuda_cfg.stream
+        assert iface["typestr"] == f"|{np.dtype(dtype).kind}{np.dtype(dtype).itemsize}"
+        t = io.to_torch(dev)
+        assert t.data_ptr() == iface["data"][0]
+        assert t.dtype == torch.from_numpy(a).dtype
+        assert (t.cpu().numpy() == a).all()
+        back = io.to_numpy(io.transfer_buffer_cpu(dev))
+        assert back.dtype == a.dtype and (back == a).all()
+
+
+def test_non_contiguous_inputs(cuda_cfg):
+    import torch
+
+    import spdl_b200.io as io
+
+    a = np.arange(4 * 6 * 8, dtype=np.int32).reshape(4, 6, 8)
+    for view in (a[:, ::2], a.transpose(2, 0, 1), a[1:3, 1:5, ::3]):
+        dev = io.transfer_buffer(view, device_config=cuda_cfg)
+        assert (io.to_torch(dev).cpu().numpy() == view).all()
+        dev = io.transfer_buffer(torch.from_numpy(a)[:, ::2], device_config=cuda_cfg)
+        assert (io.to_torch(dev).cpu().numpy() == a[:, ::2]).all()
+
+
+def test_many_transfers(cuda_cfg):
+    import spdl_b200.io as io
+
+    a = np.random.default_rng(1).integers(0, 255, (64, 64), dtype=np.uint8)
+    for _ in range(100):
+        assert (io.to_torch(io.transfer_buffer(a, device_config=cuda_cfg)).cpu().numpy() == a).all()
+
+
+@pytest.mark.parametrize("pin", [True, False])
+def test_storage_convert_transfer_on_torch_stream(pin):
+    import torch
+
+    import spdl_b200.io as io
+
+    frames, _ = _frames(3, 40, 20)
+    want = io.to_numpy(io.convert_frames(frames)).copy()
+    storage = io.cpu_storage(3 * 20 * 40 * 3, pin_memory=pin)
+    cpu = io.convert_frames(frames, storage=storage)
+    assert cpu.is_pinned() == pin
+    stream = torch.cuda.Stream(device=0)
+    cfg = io.cuda_config(0, stream=stream.cuda_stream)
+    dev = io.transfer_buffer(cpu, device_config=cfg)
+    assert (io.to_torch(dev).cpu().numpy() == want).all()
+    with pytest.raises(RuntimeError):
+        io.convert_frames(frames, storage=io.cpu_storage(100, pin_memory=pin))
+
+
+def test_buffer_outlives_its_variable(cuda_cfg):
+    import spdl_b200.io as io
+
+    a = np.arange(64, dtype=np.int64)
+    dev = io.transfer_buffer(a, device_config=cuda_cfg)
+    before = sys.getrefcount(dev)
+    t = io.to_torch(dev)
+    assert sys.getrefcount(dev) == before + 1
+    del dev
+    gc.collect()
+    assert (t.cpu().numpy() == a).all()
+
+
+def test_zero_element_buffers(cuda_cfg):
+    import spdl_b200.io as io
+
+    with pytest.raises(RuntimeError):
+        io.transfer_buffer(np.zeros((0, 3), np.uint8), device_config=cuda_cfg)
+
+    class Empty:
+        device_index = 0
+        __cuda_array_interface__ = {"version": 2, "shape": (0, 4), "typestr": "|u1",
+                                    "data": (0, False), "strides": None}
+
+    with pytest.raises(ValueError):
+        io.to_torch(Empty())
+
+
+def test_transfer_tensor_large(cuda_cfg):
+    """tests/cuda/transfer_test.py of the reference, at a smaller but still multi-MB size."""
+    import torch
+
+    import spdl_b200.io as io
+
+    x = torch.randint(0, 256, (4, 3, 1152, 1332), dtype=torch.uint8)
+    out = io.transfer_tensor({"a": x, "b": [x[:1], "label"]})
+    assert out["a"].is_cuda and torch.equal(out["a"].cpu(), x)
+    assert out["b"][1] == "label" and torch.equal(out["b"][0].cpu(), x[:1])
+
+
+def test_frame_batcher_matches_gather_oracle(cuda_cfg):
+    """Pitched surfaces -> packed batches of 3, with a short last batch, then conversion."""
+    import torch
+
+    import spdl_b200.io as io
+
+    w, h, pitch, total = 100, 36, 256, 8
+    h2 = h * 3 // 2
+    rng = np.random.default_rng(9)
+    host = [rng.integers(0, 256, (h2, pitch), dtype=np.uint8) for _ in range(total)]
+    dev = [torch.from_numpy(s).cuda() for s in host]
+    fb = io.FrameBatcher(3, w, h, cuda_cfg)
+    assert fb.empty()
+    with pytest.raises(RuntimeError):
+        fb.pop()
+    for d in dev:
+        fb.push(d.data_ptr(), pitch)
+    fb.flush()
+    shapes, got = [], []
+    while not fb.empty():
+        b = fb.pop()
+        shapes.append(b.shape)
+        got.append(io.to_torch(b).cpu().numpy())
+    assert shapes == [(3, h2, w), (3, h2, w), (2, h2, w)]
+    want = oracle.gather_frames(host, w, h)
+    assert (np.concatenate(got) == want).all()
+    rgb = io.nv12_to_rgb(torch.from_numpy(np.concatenate(got)).cuda(), device_config=cuda_cfg,
+                         sync=True)
+    assert (io.to_torch(rgb).cpu().numpy() == oracle.nv12_to_planar(want)).all()
+
+
+def test_checksum_kernel_matches_oracle(cuda_cfg):
+    import torch
+
+    import spdl_b200.io as io
+
+    a = np.random.default_rng(4).integers(0, 256, (5, 70001), dtype=np.uint8)
+    got = io.frame_checksum(torch.from_numpy(a).cuda(), device_config=cuda_cfg)
+    assert [int(x) for x in got] == [oracle.checksum(a[i]) for i in range(5)]
