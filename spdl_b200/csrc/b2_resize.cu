@@ -91,6 +91,11 @@ __global__ void __launch_bounds__(kResizeThreads) resize_kernel(const ResizePara
   const int cxlo = FMT == B2_SRC_NV12 ? (xlo & ~1) : (xlo >> 1);
   const int cxhi = FMT == B2_SRC_NV12 ? (((xhi - 1) & ~1) + 2) : (((xhi - 1) >> 1) + 1);
 
+  // A descriptor wider than the caller's max_src_w would overrun the staging rows: such an image
+  // is skipped (its output is left untouched) rather than allowed to write out of bounds.
+  if (xhi - xlo + 15 > p.span_cap || cxhi - cxlo + 15 > p.span_cap || d.src_w < 1 || d.src_h < 1)
+    return;
+
   // Shared layout per output row: [y0 | y1 | c0a | c1a | (I420: c0b | c1b)], span_cap bytes each.
   constexpr int kPlanes = FMT == B2_SRC_NV12 ? 4 : 6;
   const int rows_here = min(kRows, p.out_h - oy0);
