@@ -76,6 +76,7 @@ ColorMat color_matrix(int k, int full_range) {
   ColorMat m;
   m.g = r[0]; m.vr = r[1]; m.ug = r[2]; m.vg = r[3]; m.ub = r[4];
   m.y_bias = 8388608.0f + (full_range ? 0.0f : 16.0f);
+  m.neg_zero = -0.0f;
   return m;
 }
 

@@ -41,6 +41,7 @@ class DeviceGuard {
 struct ColorMat {
   float g, vr, ug, vg, ub;
   float y_bias;
+  float neg_zero;  // always -0.0f; a run-time value so that the compiler cannot fold it away
 };
 ColorMat color_matrix(int matrix_coeff, int full_range);
 
@@ -87,6 +88,77 @@ __device__ __forceinline__ void pixel_f32(const ColorMat& m, float by, const Chr
   r = __fadd_rn(__fmul_rn(m.g, fy), c.vr);
   g = __fadd_rn(__fmaf_rn(m.g, fy, c.ug), c.vg);
   b = __fmaf_rn(m.g, fy, c.ub);
+}
+
+// ---- the same arithmetic, two pixels per instruction -------------------------------------------
+// sm_100 has packed fp32 instructions (add/fma on two fp32 lanes of a 64-bit register pair), each
+// lane IEEE-rounded exactly like the scalar instruction.  The vector kernel pairs pixel k of a
+// luma word with pixel k+2: lane x then belongs to the first 2x2 quad under the word, lane y to
+// the second, so chroma terms pair up the same way and nothing has to be duplicated.
+//
+// ptxas contracts a packed multiply with a following packed add into one packed fma even when
+// both carry an explicit rounding mode (observed on CUDA 12.9: a mul.rn.f32x2 -> add.rn.f32x2
+// chain differs from the scalar chain in 16 % of all 2^24 inputs while each single packed
+// instruction is exact).  That would change which products are rounded, so every product that
+// feeds an add is written as fma(a, b, nz) with nz = -0.0 read from the kernel parameters: adding
+// -0.0 is an exact identity, the compiler cannot know the value, and an fma result cannot be
+// contracted into a later add.
+__device__ __forceinline__ unsigned long long pack2(float2 v) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(v.x), "f"(v.y));
+  return r;
+}
+__device__ __forceinline__ float2 unpack2(unsigned long long v) {
+  float2 r;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(v));
+  return r;
+}
+__device__ __forceinline__ float2 x2_add(float2 a, float2 b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(pack2(a)), "l"(pack2(b)));
+  return unpack2(d);
+}
+__device__ __forceinline__ float2 x2_add_rz(float2 a, float2 b) {
+  unsigned long long d;
+  asm("add.rz.f32x2 %0, %1, %2;" : "=l"(d) : "l"(pack2(a)), "l"(pack2(b)));
+  return unpack2(d);
+}
+__device__ __forceinline__ float2 x2_fma(float2 a, float2 b, float2 c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(pack2(a)), "l"(pack2(b)), "l"(pack2(c)));
+  return unpack2(d);
+}
+__device__ __forceinline__ float2 dup2(float a) { return make_float2(a, a); }
+
+struct Chroma2 {
+  float2 vr, ug, vg, ub;  // lane x: first quad, lane y: second quad
+};
+// bu, bv: {2^23 + U, 2^23 + V} of the two quads
+__device__ __forceinline__ Chroma2 chroma2_of(const ColorMat& m, float2 bu, float2 bv) {
+  const float2 nz = dup2(m.neg_zero), off = dup2(-(kTwo23 + 128.0f));
+  const float2 fu = x2_add(bu, off), fv = x2_add(bv, off);
+  Chroma2 c;
+  c.vr = x2_fma(dup2(m.vr), fv, nz);
+  c.ug = x2_fma(dup2(m.ug), fu, nz);
+  c.vg = x2_fma(dup2(m.vg), fv, nz);
+  c.ub = x2_fma(dup2(m.ub), fu, nz);
+  return c;
+}
+// Two pixels (one per quad): by = {2^23 + Y, 2^23 + Y'}.  Results are the channel values plus
+// 1.5*2^23 rounded toward zero, i.e. floor(x) sits in the low 16 mantissa bits (see quant2).
+__device__ __forceinline__ void pixel2_bits(const ColorMat& m, float2 by, const Chroma2& c,
+                                            float2& r, float2& g, float2& b) {
+  const float2 g2 = dup2(m.g), magic = dup2(kQuantMagic);
+  const float2 fy = x2_add(by, dup2(-m.y_bias));
+  const float2 ly = x2_fma(g2, fy, dup2(m.neg_zero));
+  r = x2_add_rz(x2_add(ly, c.vr), magic);
+  g = x2_add_rz(x2_add(x2_fma(g2, fy, c.ug), c.vg), magic);
+  b = x2_add_rz(x2_fma(g2, fy, c.ub), magic);
+}
+// Clamp two magic-added values (as produced by pixel2_bits) to 0..255 in two 16-bit lanes.
+__device__ __forceinline__ uint32_t clamp2_bits(float a, float b) {
+  return __vimin_s16x2_relu(__byte_perm(__float_as_uint(a), __float_as_uint(b), 0x5410u),
+                            0x00FF00FFu);
 }
 
 // Truncate-and-clamp of two channel values at once (color_conversion.cu:72-74):

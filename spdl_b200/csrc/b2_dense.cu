@@ -76,9 +76,11 @@ __device__ __forceinline__ uint32_t smem_addr(const void* p) {
 }
 
 constexpr int kDenseThreads = 128;
+// 12 resident CTAs (48 warps) per SM: measured best; caps the kernel at 40 registers per thread.
+constexpr int kDenseMinBlocks = 12;
 
 template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE>
-__global__ void __launch_bounds__(kDenseThreads) dense_vec_kernel(const DenseParams p) {
+__global__ void __launch_bounds__(kDenseThreads, kDenseMinBlocks) dense_vec_kernel(const DenseParams p) {
   using T = typename OutT<DTYPE>::type;
   constexpr int PX = 16 / (int)sizeof(T);  // pixels per thread per row
   constexpr int NW = PX / 4;               // luma words per row
@@ -127,42 +129,44 @@ __global__ void __launch_bounds__(kDenseThreads) dense_vec_kernel(const DensePar
     const ColorMat m = p.mat;
 #pragma unroll
     for (int j = 0; j < NW; ++j) {
-      // chroma of the two 2x2 quads under luma word j
-      Chroma c[2];
+      // chroma of the two 2x2 quads under luma word j: lane x = first quad, lane y = second
+      Chroma2 c;
       if constexpr (FMT == B2_SRC_NV12) {
-        c[0] = chroma_of(m, biased_byte(uw[j], 0), biased_byte(uw[j], 1));
-        c[1] = chroma_of(m, biased_byte(uw[j], 2), biased_byte(uw[j], 3));
+        c = chroma2_of(m, make_float2(biased_byte(uw[j], 0), biased_byte(uw[j], 2)),
+                       make_float2(biased_byte(uw[j], 1), biased_byte(uw[j], 3)));
       } else {
         const int w = j >> 1, b = (j & 1) * 2;
-        c[0] = chroma_of(m, biased_byte(uw[w], b), biased_byte(vw[w], b));
-        c[1] = chroma_of(m, biased_byte(uw[w], b + 1), biased_byte(vw[w], b + 1));
+        c = chroma2_of(m, make_float2(biased_byte(uw[w], b), biased_byte(uw[w], b + 1)),
+                       make_float2(biased_byte(vw[w], b), biased_byte(vw[w], b + 1)));
       }
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
-        float ch[3][4];  // [output slot][pixel]
+        // ch[slot][pixel]: channel value + 1.5*2^23, truncated (floor in the low mantissa bits)
+        float ch[3][4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          float cr, cg, cb;
-          pixel_f32(m, biased_byte(yw[r][j], k), c[k >> 1], cr, cg, cb);
-          ch[BGR ? 2 : 0][k] = cr;
-          ch[1][k] = cg;
-          ch[BGR ? 0 : 2][k] = cb;
+        for (int k = 0; k < 2; ++k) {  // pixels k and k+2 share one packed instruction stream
+          float2 cr, cg, cb;
+          pixel2_bits(m, make_float2(biased_byte(yw[r][j], k), biased_byte(yw[r][j], k + 2)), c, cr,
+                      cg, cb);
+          ch[BGR ? 2 : 0][k] = cr.x; ch[BGR ? 2 : 0][k + 2] = cr.y;
+          ch[1][k] = cg.x;           ch[1][k + 2] = cg.y;
+          ch[BGR ? 0 : 2][k] = cb.x; ch[BGR ? 0 : 2][k + 2] = cb.y;
         }
         if constexpr (DTYPE == B2_U8) {
           if constexpr (LAYOUT == B2_NCHW) {
 #pragma unroll
             for (int s = 0; s < 3; ++s)
-              out[r][4 * s + j] = bytes4(quant2(ch[s][0], ch[s][1]), quant2(ch[s][2], ch[s][3]));
+              out[r][4 * s + j] = bytes4(clamp2_bits(ch[s][0], ch[s][1]), clamp2_bits(ch[s][2], ch[s][3]));
           } else {
-            out[r][3 * j + 0] = bytes4(quant2(ch[0][0], ch[1][0]), quant2(ch[2][0], ch[0][1]));
-            out[r][3 * j + 1] = bytes4(quant2(ch[1][1], ch[2][1]), quant2(ch[0][2], ch[1][2]));
-            out[r][3 * j + 2] = bytes4(quant2(ch[2][2], ch[0][3]), quant2(ch[1][3], ch[2][3]));
+            out[r][3 * j + 0] = bytes4(clamp2_bits(ch[0][0], ch[1][0]), clamp2_bits(ch[2][0], ch[0][1]));
+            out[r][3 * j + 1] = bytes4(clamp2_bits(ch[1][1], ch[2][1]), clamp2_bits(ch[0][2], ch[1][2]));
+            out[r][3 * j + 2] = bytes4(clamp2_bits(ch[2][2], ch[0][3]), clamp2_bits(ch[1][3], ch[2][3]));
           }
         } else {
           float f[3][4];
 #pragma unroll
           for (int s = 0; s < 3; ++s) {
-            const uint32_t q01 = quant2(ch[s][0], ch[s][1]), q23 = quant2(ch[s][2], ch[s][3]);
+            const uint32_t q01 = clamp2_bits(ch[s][0], ch[s][1]), q23 = clamp2_bits(ch[s][2], ch[s][3]);
             f[s][0] = __fmaf_rn(lane_f32(q01, 0), p.sb.s[s], p.sb.b[s]);
             f[s][1] = __fmaf_rn(lane_f32(q01, 1), p.sb.s[s], p.sb.b[s]);
             f[s][2] = __fmaf_rn(lane_f32(q23, 0), p.sb.s[s], p.sb.b[s]);
