@@ -41,8 +41,8 @@ ROTATE = 4  # distinct input batches cycled through, so no step finds its input 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dense kernel on this workload,
 # from the ncu capture summarised in profiles/dense_nhwc_u8_1080p_x64.md
-# (199,146,752 read + 338,714,112 written; part of the 398 MB output is still in L2 at kernel end).
-NCU_TRAFFIC_BYTES_PER_LAUNCH: int | None = 537_860_864
+# (199,083,264 read + 362,917,632 written; part of the 398 MB output is still in L2 at kernel end).
+NCU_TRAFFIC_BYTES_PER_LAUNCH: int | None = 562_000_896
 
 
 def measured_peak() -> tuple[float, str]:
@@ -69,7 +69,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -369,7 +369,7 @@ def reference_kernel_fps(torch, src, cfg) -> dict | None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--kernel-only", action="store_true",
