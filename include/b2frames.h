@@ -44,7 +44,14 @@ enum b2_status {
   B2_ERR_LIMIT = 3    /* a size is beyond a stated maximum                                   */
 };
 
-enum b2_src_format { B2_SRC_NV12 = 0, B2_SRC_I420 = 1 };
+/* B2_SRC_RGB_PLANAR / B2_SRC_RGB_INTERLEAVED: already-decoded 8-bit RGB as a JPEG decoder emits
+ * it (src/libspdl/cuda/nvjpeg/decoding.cpp:56-95); accepted by b2_convert_resize only. */
+enum b2_src_format {
+  B2_SRC_NV12 = 0,
+  B2_SRC_I420 = 1,
+  B2_SRC_RGB_PLANAR = 2,
+  B2_SRC_RGB_INTERLEAVED = 3
+};
 enum b2_layout { B2_NCHW = 0, B2_NHWC = 1 };
 enum b2_dtype { B2_U8 = 0, B2_F32 = 1, B2_BF16 = 2 };
 enum b2_order { B2_RGB = 0, B2_BGR = 1 };
@@ -134,6 +141,9 @@ B2_API int b2_convert_dense(const b2_dense_args* args, void* stream);
  * bilinear, half-pixel centres, no antialias.  Each image has a descriptor; all
  * images write an out_h x out_w result.
  * ---------------------------------------------------------------------------------------- */
+/* Planes per source format: NV12 = Y, interleaved UV (v_off unused); I420 = Y, U, V;
+ * RGB planar = three full-size planes in y_off, u_off, v_off (y_pitch for the first, uv_pitch
+ * for the other two); RGB interleaved = one plane of 3-byte pixels in y_off / y_pitch. */
 typedef struct b2_image_desc {
   uint64_t y_off, u_off, v_off; /* byte offsets of the planes from `base`                   */
   int32_t y_pitch, uv_pitch;

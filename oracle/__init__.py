@@ -24,7 +24,7 @@ import numpy as np
 _HERE = Path(__file__).resolve().parent
 _LIB: ctypes.CDLL | None = None
 
-NV12, I420 = 0, 1
+NV12, I420, RGBP, RGBI = 0, 1, 2, 3
 NCHW, NHWC = 0, 1
 U8, F32, BF16 = 0, 1, 2
 RGB, BGR = 0, 1

@@ -33,7 +33,9 @@
 
 #define ORC_EXPORT __attribute__((visibility("default")))
 
-enum { ORC_NV12 = 0, ORC_I420 = 1 };
+/* ORC_RGBP / ORC_RGBI: already-decoded RGB (planar / interleaved), as a JPEG decoder emits
+ * it (src/libspdl/cuda/nvjpeg/decoding.cpp:56-95); only the resize path takes them. */
+enum { ORC_NV12 = 0, ORC_I420 = 1, ORC_RGBP = 2, ORC_RGBI = 3 };
 enum { ORC_NCHW = 0, ORC_NHWC = 1 };
 enum { ORC_U8 = 0, ORC_F32 = 1, ORC_BF16 = 2 };
 enum { ORC_RGB = 0, ORC_BGR = 1 };
@@ -296,6 +298,17 @@ static inline void orc_axis(float scale, int g, int n_in, int* i0, int* i1, floa
         for (int j = 0; j < 2; ++j)                                                             \
           for (int i = 0; i < 2; ++i) {                                                         \
             int sx = xs[i], sy = ys[j];                                                         \
+            if (a->src_format == ORC_RGBP) {                                                    \
+              tap[j][i][0] = a->base[d->y_off + (uint64_t)sy * d->y_pitch + sx];                \
+              tap[j][i][1] = a->base[d->u_off + (uint64_t)sy * d->uv_pitch + sx];               \
+              tap[j][i][2] = a->base[d->v_off + (uint64_t)sy * d->uv_pitch + sx];               \
+              continue;                                                                         \
+            }                                                                                   \
+            if (a->src_format == ORC_RGBI) {                                                    \
+              const uint8_t* q = a->base + d->y_off + (uint64_t)sy * d->y_pitch + 3 * sx;       \
+              tap[j][i][0] = q[0]; tap[j][i][1] = q[1]; tap[j][i][2] = q[2];                    \
+              continue;                                                                         \
+            }                                                                                   \
             int Y = a->base[d->y_off + (uint64_t)sy * d->y_pitch + sx];                         \
             int cu, cv;                                                                         \
             if (a->src_format == ORC_I420) {                                                    \

@@ -217,7 +217,7 @@ B2_API int b2_convert_resize(const b2_resize_args* a, void* stream) {
   if (a->struct_size != sizeof(b2_resize_args))
     return fail(B2_ERR_INVALID, "b2_resize_args.struct_size is %u, this library expects %zu",
                 a->struct_size, sizeof(b2_resize_args));
-  if (!valid_enum(a->src_format, 1) || !valid_enum(a->layout, 1) || !valid_enum(a->dtype, 2) ||
+  if (!valid_enum(a->src_format, 3) || !valid_enum(a->layout, 1) || !valid_enum(a->dtype, 2) ||
       !valid_enum(a->order, 1))
     return fail(B2_ERR_INVALID, "unknown src_format/layout/dtype/order (%d, %d, %d, %d)",
                 a->src_format, a->layout, a->dtype, a->order);

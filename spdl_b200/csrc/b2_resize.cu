@@ -7,11 +7,17 @@
 //   top = fma(wx1, t01, wx0*t00); bot = fma(wx1, t11, wx0*t10); val = fma(wy1, bot, wy0*top)
 //   u8 output: floor(val + 0.5) clamped to 0..255; float outputs: fma(val, scale, bias).
 //
-// One CTA produces kRows output rows of one image.  For each output row it needs two luma rows
-// and one or two chroma rows; the CTA copies exactly the spans of those rows that its outputs
-// touch into shared memory with 16-byte coalesced loads, then every thread interpolates one
-// output pixel at a time from shared memory.  Global traffic is therefore whole 16-byte
-// segments of the touched rows and nothing else.
+// One CTA produces kRows output rows of one image.
+//   Stage:   for each output row the CTA needs two luma rows and one or two chroma rows (two
+//            planes for I420).  Warp 0 works out the distinct row spans (rows shared between
+//            neighbouring output rows are fetched once), and each lane hands its span to the
+//            bulk-copy engine (cp.async.bulk global -> shared, completion on one mbarrier).  The
+//            spans are widened to 16-byte boundaries; global traffic is whole 16-byte segments
+//            of touched rows and nothing else.
+//   Compute: each thread owns four consecutive output pixels of one row.  The two source rows of
+//            a tap column ride in the two lanes of the packed fp32 instructions, so one
+//            instruction stream converts both rows of a column and the horizontal blend of both
+//            rows; 16-byte (fp32), 8-byte (bf16) or 4-byte (u8) stores per channel.
 #include "b2_common.cuh"
 
 namespace b2 {
@@ -25,151 +31,301 @@ struct ResizeParams {
   void* dst;
   long long dst_image_stride;
   ScaleBias sb;
-  int span_cap;  // bytes reserved per staged row
+  int span_cap;   // bytes reserved per staged row span (multiple of 16)
+  int vec_store;  // 1: out_w % 4 == 0 and the destination is 16-byte aligned
 };
 
-constexpr int kRows = 4;        // output rows per CTA
+constexpr int kRows = 4;  // output rows per CTA
 constexpr int kResizeThreads = 256;
+constexpr int kMaxSpans = kRows * 6;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
 
 struct Axis {
   int i0, i1;
   float w1;
 };
-__device__ __forceinline__ Axis axis_of(float scale, int g, int n_in) {
-  float s = fmaxf(__fmaf_rn(scale, (float)g + 0.5f, -0.5f), 0.0f);
-  int a = (int)s;
-  a = min(a, n_in - 1);
+// g: output coordinate in the resized grid, already as float.  No conversion instructions:
+// floor() is an add of 2^23 with round-toward-zero (0 <= s < 2^22 here).
+__device__ __forceinline__ Axis axis_of(float scale, float g, int n_in) {
+  const float s = fmaxf(__fmaf_rn(scale, __fadd_rn(g, 0.5f), -0.5f), 0.0f);
+  const float t = __fadd_rz(s, kTwo23);
+  int a = (int)(__float_as_uint(t) & 0x7FFFFFu);
+  float fa = __fsub_rn(t, kTwo23);
+  if (a > n_in - 1) {  // cannot happen for in-grid coordinates; keeps every access in bounds
+    a = n_in - 1;
+    fa = (float)a;
+  }
   Axis r;
   r.i0 = a;
   r.i1 = min(a + 1, n_in - 1);
-  r.w1 = __fsub_rn(s, (float)a);
+  r.w1 = __fsub_rn(s, fa);
   return r;
 }
 
-// Copy bytes [lo, hi) of a source row into shared memory at s[0 .. hi-lo).  The global range is
-// widened to 16-byte boundaries when the row pointer allows it; `shift` tells the caller where
-// byte `lo` landed.
-__device__ __forceinline__ int stage_span(const uint8_t* row, int lo, int hi, unsigned char* s,
-                                          int tid, int nthreads) {
-  const uintptr_t a = (uintptr_t)(row + lo);
-  const int head = (int)(a & 15);
-  const uint8_t* g = row + lo - head;  // 16-byte aligned
-  const int total = hi - lo + head;
-  const int nvec = (total + 15) >> 4;
-  // Rows start 16-byte aligned relative to the allocation in every layout this library
-  // produces; reading up to 15 bytes past `hi` could leave the allocation, so the last
-  // partial vector is fetched bytewise.
-  const int full = total >> 4;
-  for (int i = tid; i < full; i += nthreads)
-    reinterpret_cast<uint4*>(s)[i] = __ldg(reinterpret_cast<const uint4*>(g) + i);
-  if (full < nvec) {
-    const int rem = total - (full << 4);
-    for (int i = tid; i < rem; i += nthreads) s[(full << 4) + i] = __ldg(g + (full << 4) + i);
-  }
-  return head;
+__device__ __forceinline__ float biased(uint32_t b) { return __uint_as_float(0x4B000000u | b); }
+
+// {row0, row1} channel values after the truncating clamp, as exact floats 0..255.
+__device__ __forceinline__ float2 clamp_to_float2(float2 bits) {
+  const uint32_t c = clamp2_bits(bits.x, bits.y);
+  return x2_add(make_float2(__uint_as_float(__byte_perm(c, 0x4B000000u, 0x7540u)),
+                            __uint_as_float(__byte_perm(c, 0x4B000000u, 0x7542u))),
+                dup2(-kTwo23));
+}
+__device__ __forceinline__ float2 x2_mul(float2 a, float2 b) {
+  unsigned long long d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(pack2(a)), "l"(pack2(b)));
+  return unpack2(d);
 }
 
 template <int FMT, int LAYOUT, int DTYPE, bool BGR>
 __global__ void __launch_bounds__(kResizeThreads) resize_kernel(const ResizeParams p) {
   using T = typename OutT<DTYPE>::type;
-  extern __shared__ __align__(16) unsigned char smem[];
+  constexpr bool kYuv = FMT == B2_SRC_NV12 || FMT == B2_SRC_I420;
+  constexpr int kPlanes = FMT == B2_SRC_NV12 ? 4 : (FMT == B2_SRC_RGB_INTERLEAVED ? 2 : 6);
+  extern __shared__ __align__(128) unsigned char smem[];
   __shared__ b2_image_desc sd;
-  __shared__ int s_head[kRows][6];
+  __shared__ int s_off[kMaxSpans];
+  __shared__ __align__(8) unsigned long long bar;
 
   const int n = blockIdx.y;
   const int oy0 = blockIdx.x * kRows;
   const int tid = threadIdx.x;
-  if (tid < 16) reinterpret_cast<uint32_t*>(&sd)[tid] =
-      __ldg(reinterpret_cast<const uint32_t*>(p.descs + n) + tid);
-  __syncthreads();
-  const b2_image_desc d = sd;
-
-  // Horizontal extent of source pixels touched by this image's output columns.
-  const Axis ax_first = axis_of(d.scale_x, d.crop_x, d.src_w);
-  const Axis ax_last = axis_of(d.scale_x, d.crop_x + p.out_w - 1, d.src_w);
-  const int xlo = ax_first.i0, xhi = ax_last.i1 + 1;  // [xlo, xhi)
-  const int cxlo = FMT == B2_SRC_NV12 ? (xlo & ~1) : (xlo >> 1);
-  const int cxhi = FMT == B2_SRC_NV12 ? (((xhi - 1) & ~1) + 2) : (((xhi - 1) >> 1) + 1);
-
-  // A descriptor wider than the caller's max_src_w would overrun the staging rows: such an image
-  // is skipped (its output is left untouched) rather than allowed to write out of bounds.
-  if (xhi - xlo + 15 > p.span_cap || cxhi - cxlo + 15 > p.span_cap || d.src_w < 1 || d.src_h < 1)
-    return;
-
-  // Shared layout per output row: [y0 | y1 | c0a | c1a | (I420: c0b | c1b)], span_cap bytes each.
-  constexpr int kPlanes = FMT == B2_SRC_NV12 ? 4 : 6;
-  const int rows_here = min(kRows, p.out_h - oy0);
-  for (int r = 0; r < rows_here; ++r) {
-    const Axis ay = axis_of(d.scale_y, d.crop_y + oy0 + r, d.src_h);
-    unsigned char* sr = smem + (size_t)r * kPlanes * p.span_cap;
-    const uint8_t* yb = p.base + d.y_off;
-    int h;
-    h = stage_span(yb + (size_t)ay.i0 * d.y_pitch, xlo, xhi, sr, tid, kResizeThreads);
-    if (tid == 0) s_head[r][0] = h;
-    h = stage_span(yb + (size_t)ay.i1 * d.y_pitch, xlo, xhi, sr + p.span_cap, tid, kResizeThreads);
-    if (tid == 0) s_head[r][1] = h;
-    const uint8_t* ub = p.base + d.u_off;
-    h = stage_span(ub + (size_t)(ay.i0 >> 1) * d.uv_pitch, cxlo, cxhi, sr + 2 * p.span_cap, tid,
-                   kResizeThreads);
-    if (tid == 0) s_head[r][2] = h;
-    h = stage_span(ub + (size_t)(ay.i1 >> 1) * d.uv_pitch, cxlo, cxhi, sr + 3 * p.span_cap, tid,
-                   kResizeThreads);
-    if (tid == 0) s_head[r][3] = h;
-    if constexpr (FMT == B2_SRC_I420) {
-      const uint8_t* vb = p.base + d.v_off;
-      h = stage_span(vb + (size_t)(ay.i0 >> 1) * d.uv_pitch, cxlo, cxhi, sr + 4 * p.span_cap, tid,
-                     kResizeThreads);
-      if (tid == 0) s_head[r][4] = h;
-      h = stage_span(vb + (size_t)(ay.i1 >> 1) * d.uv_pitch, cxlo, cxhi, sr + 5 * p.span_cap, tid,
-                     kResizeThreads);
-      if (tid == 0) s_head[r][5] = h;
-    }
+  if (tid < 16)
+    reinterpret_cast<uint32_t*>(&sd)[tid] =
+        __ldg(reinterpret_cast<const uint32_t*>(p.descs + n) + tid);
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar)));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  const b2_image_desc d = sd;
+  if (d.src_w < 1 || d.src_h < 1) return;
+
+  // Horizontal extent of source pixels touched by this image's output columns.
+  const Axis ax_first = axis_of(d.scale_x, (float)d.crop_x, d.src_w);
+  const Axis ax_last = axis_of(d.scale_x, (float)(d.crop_x + p.out_w - 1), d.src_w);
+  const int xlo = ax_first.i0, xhi = ax_last.i1 + 1;  // source columns [xlo, xhi)
+  // byte range of the first plane's rows, and of the other planes' rows
+  const int blo = FMT == B2_SRC_RGB_INTERLEAVED ? 3 * xlo : xlo;
+  const int bhi = FMT == B2_SRC_RGB_INTERLEAVED ? 3 * xhi : xhi;
+  const int cxlo = FMT == B2_SRC_NV12 ? (xlo & ~1) : (FMT == B2_SRC_I420 ? (xlo >> 1) : xlo);
+  const int cxhi = FMT == B2_SRC_NV12   ? (((xhi - 1) & ~1) + 2)
+                   : FMT == B2_SRC_I420 ? (((xhi - 1) >> 1) + 1)
+                                        : xhi;
+  // A descriptor wider than the caller's max_src_w would overrun the staging rows: such an image
+  // is skipped (its output is left untouched) rather than allowed to write out of bounds.
+  if (bhi - blo + 15 > p.span_cap || cxhi - cxlo + 15 > p.span_cap) return;
+
+  const int rows_here = min(kRows, p.out_h - oy0);
+  if (tid < 32) {
+    const int lane = tid;
+    const int nspans = rows_here * kPlanes;
+    const bool active = lane < nspans;
+    const int r = lane / kPlanes, pl = lane - r * kPlanes;
+    long long key = -1 - lane;  // unique for idle lanes
+    const uint8_t* src = nullptr;
+    int lo = 0, bytes = 0, head = 0;
+    if (active) {
+      const Axis ay = axis_of(d.scale_y, (float)(d.crop_y + oy0 + r), d.src_h);
+      const int yrow = (pl & 1) ? ay.i1 : ay.i0;
+      if (pl < 2) {
+        key = yrow;
+        src = p.base + d.y_off + (size_t)yrow * d.y_pitch;
+        lo = blo;
+        bytes = bhi - blo;
+      } else {
+        const int plane = pl < 4 ? 1 : 2;       // second / third plane
+        const int prow = kYuv ? yrow >> 1 : yrow;  // chroma planes are half height
+        key = ((long long)plane << 32) | (uint32_t)prow;
+        src = p.base + (plane == 1 ? d.u_off : d.v_off) + (size_t)prow * d.uv_pitch;
+        lo = cxlo;
+        bytes = cxhi - cxlo;
+      }
+      head = (int)((uintptr_t)(src + lo) & 15);
+      bytes = (bytes + head + 15) & ~15;
+    }
+    // the first lane holding a given (plane, source row) fetches it; the others alias its slot
+    const unsigned same = __match_any_sync(0xffffffffu, key);
+    const int owner = __ffs(same) - 1;
+    const bool fetch = active && owner == lane;
+    if (active) s_off[lane] = owner * p.span_cap + head;
+    const unsigned total = __reduce_add_sync(0xffffffffu, fetch ? (unsigned)bytes : 0u);
+    if (lane == 0)
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&bar)),
+                   "r"(total)
+                   : "memory");
+    __syncwarp();
+    if (fetch)
+      // An aligned 16-byte segment that holds at least one valid byte lies inside the allocation
+      // (allocations start and end on coarser boundaries), so widening never leaves it.
+      asm volatile(
+          "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+              smem_u32(smem + (size_t)lane * p.span_cap)),
+          "l"(src + lo - head), "r"(bytes), "r"(smem_u32(&bar))
+          : "memory");
+  }
+  __syncthreads();  // s_off is visible
+  {
+    // Wait for the copies, with a limit: a wait that runs out abandons the tile.
+    uint32_t done = 0;
+    for (int spin = 0; spin < (1 << 20) && !done; ++spin)
+      asm volatile(
+          "{ .reg .pred P; mbarrier.try_wait.parity.shared::cta.b64 P, [%1], 0; "
+          "selp.u32 %0, 1, 0, P; }"
+          : "=r"(done)
+          : "r"(smem_u32(&bar))
+          : "memory");
+    if (!done) return;
+  }
 
   const ColorMat m = p.mat;
   T* dst = static_cast<T*>(p.dst) + (long long)n * p.dst_image_stride;
-  const int total = rows_here * p.out_w;
-  for (int i = tid; i < total; i += kResizeThreads) {
-    const int r = i / p.out_w, ox = i - r * p.out_w;
+  const int groups = (p.out_w + 3) >> 2;
+  const int total = rows_here * groups;
+  for (int gi = tid; gi < total; gi += kResizeThreads) {
+    const int r = gi / groups, ox0 = (gi - r * groups) * 4;
     const int oy = oy0 + r;
-    const Axis ay = axis_of(d.scale_y, d.crop_y + oy, d.src_h);
-    const Axis ax = axis_of(d.scale_x, d.crop_x + ox, d.src_w);
-    const unsigned char* sr = smem + (size_t)r * kPlanes * p.span_cap;
-    const float wx1 = ax.w1, wx0 = __fsub_rn(1.0f, wx1);
+    const Axis ay = axis_of(d.scale_y, (float)(d.crop_y + oy), d.src_h);
     const float wy1 = ay.w1, wy0 = __fsub_rn(1.0f, wy1);
-    int tap[2][2][3];
+    const int* so = s_off + r * kPlanes;
+    const unsigned char* y0p = smem + so[0] - blo;
+    const unsigned char* y1p = smem + so[1] - blo;
+    const unsigned char* u0p = kPlanes > 2 ? smem + so[2] - cxlo : nullptr;
+    const unsigned char* u1p = kPlanes > 2 ? smem + so[3] - cxlo : nullptr;
+    const unsigned char* v0p = kPlanes > 4 ? smem + so[4] - cxlo : nullptr;
+    const unsigned char* v1p = kPlanes > 4 ? smem + so[5] - cxlo : nullptr;
+    float val[4][3];  // [pixel][output slot]
+    const float gx0 = (float)(d.crop_x + ox0);
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const unsigned char* ys = sr + j * p.span_cap + s_head[r][j];
-      const unsigned char* us = sr + (2 + j) * p.span_cap + s_head[r][2 + j];
-      const unsigned char* vs =
-          FMT == B2_SRC_I420 ? sr + (4 + j) * p.span_cap + s_head[r][4 + j] : nullptr;
+    for (int k = 0; k < 4; ++k) {
+      // pixels past the row end repeat the last column; they are never stored
+      const Axis ax = axis_of(d.scale_x, fminf(__fadd_rn(gx0, (float)k),
+                                               (float)(d.crop_x + p.out_w - 1)), d.src_w);
+      const float2 wx1 = dup2(ax.w1), wx0 = dup2(__fsub_rn(1.0f, ax.w1));
+      float2 t[2][3];  // [column x0/x1][channel], lanes = {row y0, row y1}, clamped 0..255
 #pragma unroll
-      for (int k = 0; k < 2; ++k) {
-        const int sx = k ? ax.i1 : ax.i0;
-        const int Y = ys[sx - xlo];
-        int cu, cv;
-        if constexpr (FMT == B2_SRC_NV12) {
-          cu = us[(sx & ~1) - cxlo];
-          cv = us[(sx & ~1) - cxlo + 1];
-        } else {
-          cu = us[(sx >> 1) - cxlo];
-          cv = vs[(sx >> 1) - cxlo];
+      for (int c = 0; c < 2; ++c) {
+        const int sx = c ? ax.i1 : ax.i0;
+        if constexpr (!kYuv) {
+          // already RGB: the taps are the bytes themselves
+          const float2 off = dup2(-kTwo23);
+          if constexpr (FMT == B2_SRC_RGB_PLANAR) {
+            t[c][0] = x2_add(make_float2(biased(y0p[sx]), biased(y1p[sx])), off);
+            t[c][1] = x2_add(make_float2(biased(u0p[sx]), biased(u1p[sx])), off);
+            t[c][2] = x2_add(make_float2(biased(v0p[sx]), biased(v1p[sx])), off);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 3; ++e)
+              t[c][e] = x2_add(make_float2(biased(y0p[3 * sx + e]), biased(y1p[3 * sx + e])), off);
+          }
+          continue;
         }
-        pixel_u8(m, Y, cu, cv, tap[j][k][0], tap[j][k][1], tap[j][k][2]);
+        float2 bu, bv;
+        if constexpr (FMT == B2_SRC_NV12) {
+          const int ci = sx & ~1;
+          bu = make_float2(biased(u0p[ci]), biased(u1p[ci]));
+          bv = make_float2(biased(u0p[ci + 1]), biased(u1p[ci + 1]));
+        } else {
+          const int ci = sx >> 1;
+          bu = make_float2(biased(u0p[ci]), biased(u1p[ci]));
+          bv = make_float2(biased(v0p[ci]), biased(v1p[ci]));
+        }
+        const Chroma2 ch = chroma2_of(m, bu, bv);
+        float2 cr, cg, cb;
+        pixel2_bits(m, make_float2(biased(y0p[sx]), biased(y1p[sx])), ch, cr, cg, cb);
+        t[c][0] = clamp_to_float2(cr);
+        t[c][1] = clamp_to_float2(cg);
+        t[c][2] = clamp_to_float2(cb);
+      }
+#pragma unroll
+      for (int s = 0; s < 3; ++s) {
+        const int c = BGR ? 2 - s : s;
+        // {top, bot} = fma(wx1, t?1, wx0 * t?0) for both rows at once
+        const float2 tb = x2_fma(wx1, t[1][c], x2_mul(wx0, t[0][c]));
+        val[k][s] = __fmaf_rn(wy1, tb.y, __fmul_rn(wy0, tb.x));
       }
     }
+
+    // ---- finish and store four pixels -------------------------------------------------------
+    const bool full4 = p.vec_store && ox0 + 4 <= p.out_w;
+    if constexpr (DTYPE == B2_U8) {
+      float q[4][3];  // floor(val + 0.5) in the low mantissa bits (see quant2)
 #pragma unroll
-    for (int s = 0; s < 3; ++s) {
-      const int c = BGR ? 2 - s : s;
-      const float top = __fmaf_rn(wx1, (float)tap[0][1][c], __fmul_rn(wx0, (float)tap[0][0][c]));
-      const float bot = __fmaf_rn(wx1, (float)tap[1][1][c], __fmul_rn(wx0, (float)tap[1][0][c]));
-      float val = __fmaf_rn(wy1, bot, __fmul_rn(wy0, top));
-      if constexpr (DTYPE == B2_U8) val = fminf(fmaxf(floorf(__fadd_rn(val, 0.5f)), 0.0f), 255.0f);
-      const long long idx = LAYOUT == B2_NCHW ? ((long long)s * p.out_h + oy) * p.out_w + ox
-                                              : ((long long)oy * p.out_w + ox) * 3 + s;
-      dst[idx] = finish<T>(val, p.sb.s[s], p.sb.b[s]);
+      for (int k = 0; k < 4; ++k)
+#pragma unroll
+        for (int s = 0; s < 3; ++s) q[k][s] = __fadd_rz(__fadd_rn(val[k][s], 0.5f), kQuantMagic);
+      if (full4) {
+        if constexpr (LAYOUT == B2_NCHW) {
+#pragma unroll
+          for (int s = 0; s < 3; ++s)
+            *reinterpret_cast<uint32_t*>(dst + ((long long)s * p.out_h + oy) * p.out_w + ox0) =
+                bytes4(clamp2_bits(q[0][s], q[1][s]), clamp2_bits(q[2][s], q[3][s]));
+        } else {
+          uint32_t* o = reinterpret_cast<uint32_t*>(dst + ((long long)oy * p.out_w + ox0) * 3);
+          o[0] = bytes4(clamp2_bits(q[0][0], q[0][1]), clamp2_bits(q[0][2], q[1][0]));
+          o[1] = bytes4(clamp2_bits(q[1][1], q[1][2]), clamp2_bits(q[2][0], q[2][1]));
+          o[2] = bytes4(clamp2_bits(q[2][2], q[3][0]), clamp2_bits(q[3][1], q[3][2]));
+        }
+        continue;
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+#pragma unroll
+        for (int s = 0; s < 3; ++s) val[k][s] = (float)(clamp2_bits(q[k][s], q[k][s]) & 0xFFFFu);
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+#pragma unroll
+        for (int s = 0; s < 3; ++s) val[k][s] = __fmaf_rn(val[k][s], p.sb.s[s], p.sb.b[s]);
+      if (full4) {
+        if constexpr (DTYPE == B2_F32) {
+          if constexpr (LAYOUT == B2_NCHW) {
+#pragma unroll
+            for (int s = 0; s < 3; ++s)
+              *reinterpret_cast<float4*>(dst + ((long long)s * p.out_h + oy) * p.out_w + ox0) =
+                  make_float4(val[0][s], val[1][s], val[2][s], val[3][s]);
+          } else {
+            float4* o = reinterpret_cast<float4*>(dst + ((long long)oy * p.out_w + ox0) * 3);
+            o[0] = make_float4(val[0][0], val[0][1], val[0][2], val[1][0]);
+            o[1] = make_float4(val[1][1], val[1][2], val[2][0], val[2][1]);
+            o[2] = make_float4(val[2][2], val[3][0], val[3][1], val[3][2]);
+          }
+        } else {
+          auto b2w = [](float a, float b) {
+            __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+            return *reinterpret_cast<uint32_t*>(&t);
+          };
+          if constexpr (LAYOUT == B2_NCHW) {
+#pragma unroll
+            for (int s = 0; s < 3; ++s)
+              *reinterpret_cast<uint2*>(dst + ((long long)s * p.out_h + oy) * p.out_w + ox0) =
+                  make_uint2(b2w(val[0][s], val[1][s]), b2w(val[2][s], val[3][s]));
+          } else {
+            uint2* o = reinterpret_cast<uint2*>(dst + ((long long)oy * p.out_w + ox0) * 3);
+            o[0] = make_uint2(b2w(val[0][0], val[0][1]), b2w(val[0][2], val[1][0]));
+            o[1] = make_uint2(b2w(val[1][1], val[1][2]), b2w(val[2][0], val[2][1]));
+            o[2] = make_uint2(b2w(val[2][2], val[3][0]), b2w(val[3][1], val[3][2]));
+          }
+        }
+        continue;
+      }
+    }
+    // ragged end of a row, or a destination that is not 16-byte aligned: element stores
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (ox0 + k >= p.out_w) break;
+#pragma unroll
+      for (int s = 0; s < 3; ++s) {
+        const long long idx = LAYOUT == B2_NCHW
+                                  ? ((long long)s * p.out_h + oy) * p.out_w + ox0 + k
+                                  : ((long long)oy * p.out_w + ox0 + k) * 3 + s;
+        if constexpr (DTYPE == B2_U8) dst[idx] = (uint8_t)(int)val[k][s];
+        else if constexpr (DTYPE == B2_F32) dst[idx] = val[k][s];
+        else dst[idx] = __float2bfloat16_rn(val[k][s]);
+      }
     }
   }
 }
@@ -225,19 +381,32 @@ int launch_resize(const b2_resize_args& a, cudaStream_t stream) {
     p.sb.s[i] = a.scale[i];
     p.sb.b[i] = a.bias[i];
   }
-  // A staged row holds at most max_src_w bytes (interleaved chroma rows are as wide as luma rows)
-  // plus the 15 bytes of alignment head, rounded to 16.
-  p.span_cap = ((a.max_src_w + 2 + 15 + 15) / 16) * 16;
-  const int planes = a.src_format == B2_SRC_NV12 ? 4 : 6;
+  const int esz = a.dtype == B2_U8 ? 1 : (a.dtype == B2_F32 ? 4 : 2);
+  p.vec_store = a.out_w % 4 == 0 && (uintptr_t)a.dst % 16 == 0 &&
+                (p.dst_image_stride * esz) % 16 == 0;
+  // A staged span holds at most max_src_w + 1 bytes (interleaved chroma rows of an odd width)
+  // plus up to 15 bytes of alignment head, rounded up to whole 16-byte segments.
+  const int row_bytes = a.src_format == B2_SRC_RGB_INTERLEAVED ? 3 * a.max_src_w : a.max_src_w;
+  p.span_cap = ((row_bytes + 2 + 15 + 15) / 16) * 16;
+  const int planes = a.src_format == B2_SRC_NV12 ? 4 : (a.src_format == B2_SRC_RGB_INTERLEAVED ? 2 : 6);
   const size_t smem = (size_t)kRows * planes * p.span_cap;
   if (smem > 200 * 1024)
     return fail(B2_ERR_LIMIT, "max_src_w %d needs %zu bytes of staging; the limit is %d bytes",
                 a.max_src_w, smem, 200 * 1024);
-  if (a.src_format == B2_SRC_NV12)
-    return a.layout == B2_NCHW ? launch_fl<B2_SRC_NV12, B2_NCHW>(a, p, smem, stream)
-                               : launch_fl<B2_SRC_NV12, B2_NHWC>(a, p, smem, stream);
-  return a.layout == B2_NCHW ? launch_fl<B2_SRC_I420, B2_NCHW>(a, p, smem, stream)
-                             : launch_fl<B2_SRC_I420, B2_NHWC>(a, p, smem, stream);
+  switch (a.src_format) {
+    case B2_SRC_NV12:
+      return a.layout == B2_NCHW ? launch_fl<B2_SRC_NV12, B2_NCHW>(a, p, smem, stream)
+                                 : launch_fl<B2_SRC_NV12, B2_NHWC>(a, p, smem, stream);
+    case B2_SRC_I420:
+      return a.layout == B2_NCHW ? launch_fl<B2_SRC_I420, B2_NCHW>(a, p, smem, stream)
+                                 : launch_fl<B2_SRC_I420, B2_NHWC>(a, p, smem, stream);
+    case B2_SRC_RGB_PLANAR:
+      return a.layout == B2_NCHW ? launch_fl<B2_SRC_RGB_PLANAR, B2_NCHW>(a, p, smem, stream)
+                                 : launch_fl<B2_SRC_RGB_PLANAR, B2_NHWC>(a, p, smem, stream);
+    default:
+      return a.layout == B2_NCHW ? launch_fl<B2_SRC_RGB_INTERLEAVED, B2_NCHW>(a, p, smem, stream)
+                                 : launch_fl<B2_SRC_RGB_INTERLEAVED, B2_NHWC>(a, p, smem, stream);
+  }
 }
 
 }  // namespace b2

@@ -44,7 +44,9 @@ _LAYOUTS = {"NCHW": NCHW, "NHWC": NHWC, NCHW: NCHW, NHWC: NHWC}
 _DTYPES = {"uint8": U8, "u8": U8, "float32": F32, "fp32": F32, "f32": F32, "bfloat16": BF16,
            "bf16": BF16}
 _ORDERS = {"rgb": RGB, "bgr": BGR}
-_FORMATS = {"nv12": NV12, "i420": I420, "yuv420p": I420}
+RGB_PLANAR, RGB_INTERLEAVED = 2, 3
+_FORMATS = {"nv12": NV12, "i420": I420, "yuv420p": I420, "rgb_planar": RGB_PLANAR,
+            "rgb24": RGB_INTERLEAVED, "rgb_interleaved": RGB_INTERLEAVED}
 _OUT_ELEM = {U8: ("u", 1), F32: ("f", 4), BF16: ("u", 2)}  # bf16 is exposed as 2-byte words
 
 
@@ -226,7 +228,9 @@ def make_image_descs(widths: Sequence[int], heights: Sequence[int], *, src_forma
     """Build the descriptor table of a (possibly ragged) packed batch.
 
     Images are packed back to back (``offsets[i]`` = byte offset of image ``i``; computed when
-    omitted), each as Y rows then chroma (NV12: interleaved UV rows; I420: U block, V block).
+    omitted), each as Y rows then chroma (NV12: interleaved UV rows; I420: U block, V block), or,
+    for sources that are already RGB (``"rgb_planar"``: three planes, ``"rgb24"``: interleaved --
+    the layouts a JPEG decoder emits), as ``3*w*h`` bytes.
     Geometry: ``resize=(w, h)`` stretches every image to that size; ``resize_shorter=s`` scales
     the shorter side to ``s`` and the longer to ``int(s * long / short)``; then
     ``crop=(w, h)`` takes the centre window with offset ``int(round((dim - crop) / 2))``.
@@ -241,7 +245,7 @@ def make_image_descs(widths: Sequence[int], heights: Sequence[int], *, src_forma
     fmt = _FORMATS[src_format.lower()]
     n = len(w)
     cw, chh = (w + 1) // 2, (h + 1) // 2
-    frame_bytes = w * h + 2 * cw * chh
+    frame_bytes = 3 * w * h if fmt in (RGB_PLANAR, RGB_INTERLEAVED) else w * h + 2 * cw * chh
     if offsets is None:
         off = np.concatenate([[0], np.cumsum(frame_bytes)[:-1]]) if n else np.zeros(0, np.int64)
     else:
@@ -273,12 +277,19 @@ def make_image_descs(widths: Sequence[int], heights: Sequence[int], *, src_forma
     d = np.zeros(n, DESC_DTYPE)
     d["y_off"] = off
     d["u_off"] = off + w * h
+    d["y_pitch"] = w
     if fmt == NV12:
         d["uv_pitch"] = 2 * cw
-    else:
+    elif fmt == I420:
         d["v_off"] = off + w * h + cw * chh
         d["uv_pitch"] = cw
-    d["y_pitch"], d["src_w"], d["src_h"] = w, w, h
+    elif fmt == RGB_PLANAR:
+        d["v_off"] = off + 2 * w * h
+        d["uv_pitch"] = w
+    else:
+        d["u_off"] = 0
+        d["y_pitch"] = 3 * w
+    d["src_w"], d["src_h"] = w, h
     d["crop_x"], d["crop_y"] = cx, cy
     d["scale_x"] = w.astype(np.float32) / rw.astype(np.float32)
     d["scale_y"] = h.astype(np.float32) / rh.astype(np.float32)

@@ -156,3 +156,45 @@ def test_validation(cuda_cfg):
     with pytest.raises(RuntimeError):
         io.convert_resize(base, _dev(d.view(np.uint8)), out_size=o, max_src_w=16,
                           device_config=cuda_cfg, layout="CHWN")
+
+
+@pytest.mark.parametrize("fmt", ["rgb_planar", "rgb24"])
+@pytest.mark.parametrize("layout,dtype", [("NCHW", "uint8"), ("NHWC", "float32"),
+                                          ("NCHW", "bfloat16")])
+def test_rgb_sources_ragged(cuda_cfg, fmt, layout, dtype):
+    """Already-decoded RGB of different sizes (what a JPEG decoder hands over), planar or
+    interleaved -> shorter side 64, centre crop 48x48, normalise."""
+    import spdl_b200.io as io
+
+    rng = np.random.default_rng(21)
+    ws = rng.integers(50, 180, 9)
+    hs = rng.integers(50, 180, 9)
+    sizes = 3 * ws * hs
+    offs = np.concatenate([[0], np.cumsum(sizes)[:-1]])
+    data = rng.integers(0, 256, int(sizes.sum()), dtype=np.uint8)
+    descs, out = io.make_image_descs(ws, hs, src_format=fmt, offsets=offs, resize_shorter=64,
+                                     crop=(48, 48))
+    norm = dict(mean=MEAN, std=STD) if dtype != "uint8" else {}
+    max_w = int(descs["src_w"].max())
+    buf = io.convert_resize(_dev(data), _dev(descs.view(np.uint8)), out_size=out, max_src_w=max_w,
+                            device_config=cuda_cfg, src_format=fmt, layout=layout, dtype=dtype,
+                            order="bgr", sync=True, **norm)
+    got = io.to_torch(buf).cpu().numpy()
+    want = oracle.convert_resize(
+        data, descs, out_w=out[0], out_h=out[1],
+        src_format=oracle.RGBP if fmt == "rgb_planar" else oracle.RGBI,
+        layout=oracle.NCHW if layout == "NCHW" else oracle.NHWC, dtype=_O_DT[dtype],
+        order=oracle.BGR, sb=oracle.scale_bias(MEAN, STD) if norm else None)
+    _compare(got, want, dtype)
+
+
+def test_unaligned_output_width(cuda_cfg):
+    """out_w not a multiple of 4 takes the element-store path."""
+    import spdl_b200.io as io
+
+    w, h = 96, 64
+    nv = synth.nv12_batch(2, w, h, config=9, index=31)
+    descs, out = io.make_image_descs([w, w], [h, h], resize=(37, 23))
+    for layout, dtype in (("NCHW", "uint8"), ("NHWC", "uint8"), ("NHWC", "float32")):
+        got, want = _run(cuda_cfg, nv.reshape(-1), descs, out, "nv12", layout, dtype)
+        _compare(got, want, dtype)
