@@ -337,6 +337,133 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+# ---- the fused resize workloads (informational; the headline is the dense workload above) --------
+
+
+def _tap_bytes(w, h, rw, rh, cx, cy, ow, oh, fmt) -> tuple[int, int]:
+    """(tap-exact, row-granular) source bytes of one image: distinct luma taps plus distinct chroma
+    samples under them, and whole touched rows."""
+    def taps(n_in, n_out, off, keep):
+        d = np.arange(off, off + keep, dtype=np.float64)
+        s = np.maximum((d + 0.5) * (n_in / n_out) - 0.5, 0.0)
+        i0 = np.minimum(np.floor(s).astype(np.int64), n_in - 1)
+        return np.unique(np.concatenate([i0, np.minimum(i0 + 1, n_in - 1)]))
+
+    xs, ys = taps(w, rw, cx, ow), taps(h, rh, cy, oh)
+    ncx, ncy = len(np.unique(xs // 2)), len(np.unique(ys // 2))
+    exact = len(xs) * len(ys) + 2 * ncx * ncy
+    rows = len(ys) * w + ncy * (w if fmt == "nv12" else 2 * ((w + 1) // 2))
+    return exact, rows
+
+
+def run_resize_workload(args) -> None:
+    """``--workload c3|c4|c5``: one GPU, kernel-resident timing of the fused resize kernel on the
+    other benchmark configurations, with tap-exact and row-granular roofline figures."""
+    import torch
+
+    import spdl_b200.io as io
+    from spdl_b200 import _lib
+    from tests import synth
+
+    torch.cuda.init()
+    dev = torch.device("cuda", 0)
+    stream = torch.cuda.Stream(dev)
+    L = _lib.lib()
+    scale = float(args.scale)
+    mean, std = (0.485, 0.456, 0.406), (0.229, 0.224, 0.225)
+    if args.workload == "c3":
+        n, w, h = max(1, int(16 * scale)), 3840, 2160
+        ws, hs = [w] * n, [h] * n
+        descs, out = io.make_image_descs(ws, hs, resize=(224, 224))
+        spec = dict(fmt="nv12", layout=_lib.NCHW, dtype=_lib.BF16, esz=2, coeff=1, full=0, norm=True,
+                    name=f"{n} x 3840x2160 NV12 -> 224x224 bf16 NCHW, BT.709, normalised")
+        copies, nbytes = 8, n * w * h * 3 // 2
+    elif args.workload == "c4":
+        n, w, h = max(1, int(1024 * scale)), 1280, 720
+        ws, hs = [w] * n, [h] * n
+        descs, out = io.make_image_descs(ws, hs, resize=(256, 256))
+        spec = dict(fmt="nv12", layout=_lib.NCHW, dtype=_lib.U8, esz=1, coeff=6, full=0, norm=False,
+                    name=f"{n} frames ({n // 16} clips x 16) 1280x720 NV12 -> 256x256 u8 "
+                         f"N x T x C x H x W, BT.601")
+        copies, nbytes = 2, n * w * h * 3 // 2
+    else:
+        n = max(1, int(2048 * scale))
+        data, ws, hs, offs = synth.ragged_i420(n)
+        descs, out = io.make_image_descs(ws, hs, src_format="i420", offsets=offs,
+                                         resize_shorter=256, crop=(224, 224))
+        spec = dict(fmt="i420", layout=_lib.NCHW, dtype=_lib.F32, esz=4, coeff=6, full=1, norm=True,
+                    name=f"{n} ragged I420 images (256..1024) -> shorter side 256, centre crop "
+                         f"224x224 fp32 NCHW, full-range BT.601, normalised")
+        copies, nbytes = 2, int(data.nbytes)
+    with torch.cuda.stream(stream):
+        if args.workload == "c5":
+            first = torch.from_numpy(data).to(dev)
+            bases = [first] + [first.clone() for _ in range(copies - 1)]
+        else:
+            g = torch.Generator(device=dev).manual_seed(3000)
+            bases = [torch.randint(16, 236, (nbytes,), dtype=torch.uint8, device=dev, generator=g)
+                     for _ in range(copies)]
+        dd = torch.from_numpy(descs.view(np.uint8)).to(dev)
+        dst = torch.empty(n * 3 * out[0] * out[1] * spec["esz"], dtype=torch.uint8, device=dev)
+    sc, bi = io._core._scale_bias(mean if spec["norm"] else None, std if spec["norm"] else None)
+    calls = []
+    for b in bases:
+        a = _lib.ResizeArgs()
+        a.struct_size = ctypes.sizeof(_lib.ResizeArgs)
+        a.device, a.base, a.descs = 0, b.data_ptr(), dd.data_ptr()
+        a.num_images, a.src_format = n, io._core._FORMATS[spec["fmt"]]
+        a.out_w, a.out_h = out
+        a.matrix_coeff, a.full_range = spec["coeff"], spec["full"]
+        a.layout, a.dtype, a.order = spec["layout"], spec["dtype"], _lib.RGB
+        a.max_src_w, a.dst = int(max(ws)), dst.data_ptr()
+        a.scale = (ctypes.c_float * 3)(*sc.tolist())
+        a.bias = (ctypes.c_float * 3)(*bi.tolist())
+        calls.append(a)
+    K, Wm = args.steps, max(args.warmup, 3)
+    stream.synchronize()
+    for i in range(Wm):
+        _lib.check(L.b2_convert_resize(ctypes.byref(calls[i % copies]), stream.cuda_stream))
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(0) as clocks:
+        e0.record(stream)
+        for i in range(K):
+            _lib.check(L.b2_convert_resize(ctypes.byref(calls[i % copies]), stream.cuda_stream))
+        e1.record(stream)
+        torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / K
+    rw = np.rint(np.asarray(ws) / descs["scale_x"].astype(np.float64)).astype(np.int64)
+    rh = np.rint(np.asarray(hs) / descs["scale_y"].astype(np.float64)).astype(np.int64)
+    cache: dict = {}
+    exact = rows = 0
+    for i in range(n):
+        key = (int(ws[i]), int(hs[i]), int(rw[i]), int(rh[i]), int(descs["crop_x"][i]),
+               int(descs["crop_y"][i]))
+        if key not in cache:
+            cache[key] = _tap_bytes(*key, out[0], out[1], spec["fmt"])
+        exact += cache[key][0]
+        rows += cache[key][1]
+    out_bytes = n * 3 * out[0] * out[1] * spec["esz"]
+    peak, peak_kind = measured_peak()
+    line = {
+        "metric": "fused convert+resize images/s", "value": n / (ms * 1e-3), "unit": "images/s",
+        "n_gpus": 1, "steps": K, "warmup": Wm, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": {1: "u8", 2: "bf16", 4: "f32"}[spec["esz"]],
+        "data": "synthetic", "config": {"workload": spec["name"], "images_per_step": n,
+                                        "l2": f"{copies} input copies rotated"},
+        "gpu_launches": K,
+        "roofline": {"bound": "hbm", "unit": "GB/s", "peak": peak, "peak_source": peak_kind,
+                     "achieved": (exact + out_bytes) / (ms * 1e-3) / 1e9,
+                     "frac": (exact + out_bytes) / (ms * 1e-3) / 1e9 / peak,
+                     "algorithmic_bytes_per_launch": exact + out_bytes,
+                     "row_granular_bytes_per_launch": rows + out_bytes,
+                     "row_granular_gb_per_s": (rows + out_bytes) / (ms * 1e-3) / 1e9,
+                     "traffic": None, "kernel": "resize_kernel", "ms_per_launch": ms},
+        "clocks": clocks.summary(),
+    }
+    print(json.dumps(line), flush=True)
+
+
 def reference_kernel_fps(torch, src, cfg) -> dict | None:
     """The reference's own kernel (planar RGB, compiled unmodified for sm_100a) on the same input,
     as the GPU-side kernel to beat.  Informational; absent when oracle/_ref was not built."""
@@ -374,9 +501,16 @@ def main() -> None:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU legs (for profiler captures)")
+    ap.add_argument("--workload", choices=["c2", "c3", "c4", "c5"], default="c2",
+                    help="c2 = the headline dense workload; c3/c4/c5 = fused resize workloads "
+                         "(one GPU, informational)")
+    ap.add_argument("--scale", default="1.0",
+                    help="fraction of a resize workload's batch (for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload != "c2":
+        run_resize_workload(args)
     else:
         run_ours(args)
 
