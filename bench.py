@@ -210,6 +210,8 @@ def run_ours(args) -> None:
     multi = info.world_size > 1
     if multi:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout
         dist.init_process_group("nccl", device_id=torch.device("cuda", info.local_rank))
     worker = ShardWorker(info)
     dev, stream, cfg = worker.device, worker.stream, worker.config

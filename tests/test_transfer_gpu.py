@@ -224,3 +224,60 @@ def test_checksum_kernel_matches_oracle(cuda_cfg):
     a = np.random.default_rng(4).integers(0, 256, (5, 70001), dtype=np.uint8)
     got = io.frame_checksum(torch.from_numpy(a).cuda(), device_config=cuda_cfg)
     assert [int(x) for x in got] == [oracle.checksum(a[i]) for i in range(5)]
+
+
+def test_frame_stage_from_worker_threads():
+    """The pipeline stage: host yuv420p frames (as convert_frames lays them out) -> normalised
+    tensor, called concurrently from four threads; dense and resizing variants."""
+    import threading
+
+    import torch
+
+    import spdl_b200.io as io
+
+    mean, std = (0.485, 0.456, 0.406), (0.229, 0.224, 0.225)
+    n, w, h = 3, 64, 48
+    i420 = synth.i420_batch_gradient(n, w, h, config=1, index=2)
+    flat = i420.reshape(-1)
+    kw = dict(width=w, height=h, num_frames=n, y_pitch=w, uv_pitch=w // 2,
+              y_frame_stride=h * 3 // 2 * w, uv_frame_stride=h * 3 // 2 * w,
+              src_format=oracle.I420)
+    u, v = flat[h * w:], flat[h * w + (h // 2) * (w // 2):]
+    want_dense = oracle.convert_dense(i420, u, v, dtype=oracle.F32,
+                                      sb=oracle.scale_bias(mean, std), **kw)
+    descs, out = io.make_image_descs([w] * n, [h] * n, src_format="i420", resize_shorter=32,
+                                     crop=(24, 24))
+    want_small = oracle.convert_resize(flat, descs, out_w=24, out_h=24, src_format=oracle.I420,
+                                       dtype=oracle.BF16, sb=oracle.scale_bias(mean, std))
+    dense = io.FrameStage(mean=mean, std=std)
+    small = io.FrameStage(dtype="bfloat16", mean=mean, std=std, resize_shorter=32, crop=(24, 24))
+    # a CPUBuffer shaped like convert_frames' yuv420p output: [N, 1, H*1.5, W], pinned
+    frames = io.Frames("yuv420p", w, h, [[i420[i, :h], i420[i, h:].reshape(-1)[:(h // 2) * (w // 2)]
+                                          .reshape(h // 2, w // 2),
+                                          i420[i, h:].reshape(-1)[(h // 2) * (w // 2):]
+                                          .reshape(h // 2, w // 2)] for i in range(n)])
+    host = io.convert_frames(frames, storage=io.cpu_storage(i420.nbytes))
+    assert host.shape == (n, 1, h * 3 // 2, w)
+    errors = []
+
+    def work():
+        try:
+            for _ in range(5):
+                a = dense(host)
+                b = small(i420)
+                assert a.dtype == torch.float32 and tuple(a.shape) == (n, 3, h, w)
+                np.testing.assert_allclose(a.cpu().numpy(), want_dense, rtol=1e-6, atol=1e-6)
+                assert b.dtype == torch.bfloat16 and tuple(b.shape) == (n, 3, 24, 24)
+                got = b.view(torch.uint16).cpu().numpy()
+                assert (got == want_small).mean() > 0.999
+        except Exception as e:  # pragma: no cover
+            errors.append(e)
+
+    threads = [threading.Thread(target=work) for _ in range(4)]
+    [t.start() for t in threads]
+    [t.join() for t in threads]
+    assert not errors, errors
+    with pytest.raises(RuntimeError):
+        dense(np.zeros((2, 7, 8), np.uint8))
+    with pytest.raises(RuntimeError):
+        io.FrameStage(crop=(8, 8))
