@@ -37,6 +37,8 @@ struct ResizeParams {
 
 constexpr int kRows = 4;  // output rows per CTA
 constexpr int kResizeThreads = 256;
+// 6 resident CTAs (48 warps) per SM measured best; caps the kernel at 40 registers per thread.
+constexpr int kResizeMinBlocks = 6;
 constexpr int kMaxSpans = kRows * 6;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -81,7 +83,7 @@ __device__ __forceinline__ float2 x2_mul(float2 a, float2 b) {
 }
 
 template <int FMT, int LAYOUT, int DTYPE, bool BGR>
-__global__ void __launch_bounds__(kResizeThreads) resize_kernel(const ResizeParams p) {
+__global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kernel(const ResizeParams p) {
   using T = typename OutT<DTYPE>::type;
   constexpr bool kYuv = FMT == B2_SRC_NV12 || FMT == B2_SRC_I420;
   constexpr int kPlanes = FMT == B2_SRC_NV12 ? 4 : (FMT == B2_SRC_RGB_INTERLEAVED ? 2 : 6);
@@ -167,7 +169,31 @@ __global__ void __launch_bounds__(kResizeThreads) resize_kernel(const ResizePara
           "l"(src + lo - head), "r"(bytes), "r"(smem_u32(&bar))
           : "memory");
   }
-  __syncthreads();  // s_off is visible
+  // While the copies are in flight: one table entry per output column (the horizontal taps are
+  // the same for every row of the image).  {x0 | x1 << 16, c0 | c1 << 16, wx1, -}: byte offsets
+  // of the two tap columns in a staged first-plane row and in a staged second/third-plane row.
+  uint4* xtab = reinterpret_cast<uint4*>(smem + (size_t)kRows * kPlanes * p.span_cap);
+  const int tab_groups = (p.out_w + 3) >> 2;
+  for (int ox = tid; ox < p.out_w; ox += kResizeThreads) {
+    const Axis ax = axis_of(d.scale_x, (float)(d.crop_x + ox), d.src_w);
+    const int m3 = FMT == B2_SRC_RGB_INTERLEAVED ? 3 : 1;
+    const uint32_t x0 = (uint32_t)(m3 * (ax.i0 - xlo)), x1 = (uint32_t)(m3 * (ax.i1 - xlo));
+    uint32_t c0, c1;
+    if constexpr (FMT == B2_SRC_NV12) {
+      c0 = (uint32_t)((ax.i0 & ~1) - cxlo);
+      c1 = (uint32_t)((ax.i1 & ~1) - cxlo);
+    } else if constexpr (FMT == B2_SRC_I420) {
+      c0 = (uint32_t)((ax.i0 >> 1) - cxlo);
+      c1 = (uint32_t)((ax.i1 >> 1) - cxlo);
+    } else {
+      c0 = x0;
+      c1 = x1;
+    }
+    // stored so that the four-pixel groups of neighbouring threads read neighbouring entries
+    xtab[(ox & 3) * tab_groups + (ox >> 2)] =
+        make_uint4(x0 | (x1 << 16), c0 | (c1 << 16), __float_as_uint(ax.w1), 0u);
+  }
+  __syncthreads();  // s_off and xtab are visible
   {
     // Wait for the copies, with a limit: a wait that runs out abandons the tile.
     uint32_t done = 0;
@@ -191,45 +217,55 @@ __global__ void __launch_bounds__(kResizeThreads) resize_kernel(const ResizePara
     const Axis ay = axis_of(d.scale_y, (float)(d.crop_y + oy), d.src_h);
     const float wy1 = ay.w1, wy0 = __fsub_rn(1.0f, wy1);
     const int* so = s_off + r * kPlanes;
-    const unsigned char* y0p = smem + so[0] - blo;
-    const unsigned char* y1p = smem + so[1] - blo;
-    const unsigned char* u0p = kPlanes > 2 ? smem + so[2] - cxlo : nullptr;
-    const unsigned char* u1p = kPlanes > 2 ? smem + so[3] - cxlo : nullptr;
-    const unsigned char* v0p = kPlanes > 4 ? smem + so[4] - cxlo : nullptr;
-    const unsigned char* v1p = kPlanes > 4 ? smem + so[5] - cxlo : nullptr;
+    const unsigned char* y0p = smem + so[0];
+    const unsigned char* y1p = smem + so[1];
+    const unsigned char* u0p = kPlanes > 2 ? smem + so[2] : nullptr;
+    const unsigned char* u1p = kPlanes > 2 ? smem + so[3] : nullptr;
+    const unsigned char* v0p = kPlanes > 4 ? smem + so[4] : nullptr;
+    const unsigned char* v1p = kPlanes > 4 ? smem + so[5] : nullptr;
+    // interleaved chroma pairs can be fetched with one 16-bit load when the staged rows kept an
+    // even address (they do whenever the source plane and pitch are even)
+    const bool uv16 = FMT == B2_SRC_NV12 && ((so[2] | so[3]) & 1) == 0;
     float val[4][3];  // [pixel][output slot]
-    const float gx0 = (float)(d.crop_x + ox0);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       // pixels past the row end repeat the last column; they are never stored
-      const Axis ax = axis_of(d.scale_x, fminf(__fadd_rn(gx0, (float)k),
-                                               (float)(d.crop_x + p.out_w - 1)), d.src_w);
-      const float2 wx1 = dup2(ax.w1), wx0 = dup2(__fsub_rn(1.0f, ax.w1));
+      const int oxk = min(ox0 + k, p.out_w - 1);
+      const uint4 e = xtab[(oxk & 3) * tab_groups + (oxk >> 2)];
+      const float w1 = __uint_as_float(e.z);
+      const float2 wx1 = dup2(w1), wx0 = dup2(__fsub_rn(1.0f, w1));
       float2 t[2][3];  // [column x0/x1][channel], lanes = {row y0, row y1}, clamped 0..255
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        const int sx = c ? ax.i1 : ax.i0;
+        const int sx = c ? (int)(e.x >> 16) : (int)(e.x & 0xFFFFu);
+        const int ci = c ? (int)(e.y >> 16) : (int)(e.y & 0xFFFFu);
         if constexpr (!kYuv) {
           // already RGB: the taps are the bytes themselves
           const float2 off = dup2(-kTwo23);
           if constexpr (FMT == B2_SRC_RGB_PLANAR) {
             t[c][0] = x2_add(make_float2(biased(y0p[sx]), biased(y1p[sx])), off);
-            t[c][1] = x2_add(make_float2(biased(u0p[sx]), biased(u1p[sx])), off);
-            t[c][2] = x2_add(make_float2(biased(v0p[sx]), biased(v1p[sx])), off);
+            t[c][1] = x2_add(make_float2(biased(u0p[ci]), biased(u1p[ci])), off);
+            t[c][2] = x2_add(make_float2(biased(v0p[ci]), biased(v1p[ci])), off);
           } else {
 #pragma unroll
-            for (int e = 0; e < 3; ++e)
-              t[c][e] = x2_add(make_float2(biased(y0p[3 * sx + e]), biased(y1p[3 * sx + e])), off);
+            for (int ch = 0; ch < 3; ++ch)
+              t[c][ch] = x2_add(make_float2(biased(y0p[sx + ch]), biased(y1p[sx + ch])), off);
           }
           continue;
         }
         float2 bu, bv;
         if constexpr (FMT == B2_SRC_NV12) {
-          const int ci = sx & ~1;
-          bu = make_float2(biased(u0p[ci]), biased(u1p[ci]));
-          bv = make_float2(biased(u0p[ci + 1]), biased(u1p[ci + 1]));
+          uint32_t p0, p1;  // {U, V} of row 0 / row 1
+          if (uv16) {
+            p0 = *reinterpret_cast<const uint16_t*>(u0p + ci);
+            p1 = *reinterpret_cast<const uint16_t*>(u1p + ci);
+          } else {
+            p0 = u0p[ci] | ((uint32_t)u0p[ci + 1] << 8);
+            p1 = u1p[ci] | ((uint32_t)u1p[ci + 1] << 8);
+          }
+          bu = make_float2(biased_byte(p0, 0), biased_byte(p1, 0));
+          bv = make_float2(biased_byte(p0, 1), biased_byte(p1, 1));
         } else {
-          const int ci = sx >> 1;
           bu = make_float2(biased(u0p[ci]), biased(u1p[ci]));
           bv = make_float2(biased(v0p[ci]), biased(v1p[ci]));
         }
@@ -389,8 +425,8 @@ int launch_resize(const b2_resize_args& a, cudaStream_t stream) {
   const int row_bytes = a.src_format == B2_SRC_RGB_INTERLEAVED ? 3 * a.max_src_w : a.max_src_w;
   p.span_cap = ((row_bytes + 2 + 15 + 15) / 16) * 16;
   const int planes = a.src_format == B2_SRC_NV12 ? 4 : (a.src_format == B2_SRC_RGB_INTERLEAVED ? 2 : 6);
-  const size_t smem = (size_t)kRows * planes * p.span_cap;
-  if (smem > 200 * 1024)
+  const size_t smem = (size_t)kRows * planes * p.span_cap + (size_t)((a.out_w + 3) / 4) * 64;
+  if (p.span_cap >= 65536 || smem > 200 * 1024)
     return fail(B2_ERR_LIMIT, "max_src_w %d needs %zu bytes of staging; the limit is %d bytes",
                 a.max_src_w, smem, 200 * 1024);
   switch (a.src_format) {
