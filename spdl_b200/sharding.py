@@ -80,12 +80,20 @@ class ShardWorker:
         return shard_indices(total, self.info.rank, self.info.world_size, mode)
 
 
-def gather_stats(stats: Sequence[float], device: Any = None) -> list[list[float]]:
+def gather_stats(stats: Sequence[float], device: Any = None,
+                 on_failure: str = "raise") -> list[list[float]]:
     """All ranks' statistics vectors, in rank order.  Uses the initialised ``torch.distributed``
-    group (NCCL on GPUs, gloo on CPU); without one it returns ``[stats]``."""
+    group (NCCL on GPUs, gloo on CPU); without one it returns ``[stats]``.
+
+    The gather is bookkeeping, not part of the data path: with ``on_failure="local"`` a rank
+    whose peers have gone away (the collective raises or runs into the group's timeout) keeps
+    its own numbers and returns ``[stats]`` instead of failing the run.
+    """
     import torch
     import torch.distributed as dist
 
+    if on_failure not in ("raise", "local"):
+        raise RuntimeError(f"Unknown on_failure mode: {on_failure}")
     vec = [float(x) for x in stats]
     if not (dist.is_available() and dist.is_initialized()):
         return [vec]
@@ -94,5 +102,11 @@ def gather_stats(stats: Sequence[float], device: Any = None) -> list[list[float]
                                               if on_gpu else torch.device("cpu"))
     mine = torch.tensor(vec, dtype=torch.float64, device=dev)
     out = [torch.zeros_like(mine) for _ in range(dist.get_world_size())]
-    dist.all_gather(out, mine)
-    return [t.cpu().tolist() for t in out]
+    try:
+        dist.all_gather(out, mine)
+        result = [t.cpu().tolist() for t in out]
+    except Exception:
+        if on_failure == "raise":
+            raise
+        return [vec]
+    return result

@@ -92,3 +92,56 @@ def test_two_rank_gloo_gather():
     # whole-job throughput = all items / slowest rank
     total = sum(r[0] for r in want)
     assert total / max(r[2] for r in want) == 2048 / 1.5
+
+
+def _rank_that_may_leave(rank: int, world: int, port: int, q) -> None:
+    """Rank 1 leaves between steps without joining the gather; rank 0 must learn of it through
+    the collective's error (or the group's short timeout) and keep its own statistics."""
+    import datetime
+
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world),
+                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch.distributed as dist
+
+    from spdl_b200.sharding import gather_stats
+
+    dist.init_process_group("gloo", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=10))
+    dist.barrier()  # both ranks are up; the data path itself needs no communication
+    if rank == 1:
+        q.put((rank, "left"))
+        q.close()
+        q.join_thread()  # the message is on the pipe before the process goes away
+        os._exit(0)
+    import time
+
+    time.sleep(1.0)
+    try:
+        gather_stats([1.0], on_failure="raise")
+        strict = "no error"
+    except Exception as e:
+        strict = type(e).__name__
+    q.put((rank, strict, gather_stats([7.0, 8.0], on_failure="local")))
+    q.close()
+    q.join_thread()
+    os._exit(0)
+
+
+def test_gather_survives_a_rank_that_left():
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_that_may_leave, args=(r, 2, port, q)) for r in range(2)]
+    [p.start() for p in procs]
+    got = {}
+    for _ in range(2):
+        item = q.get(timeout=120)
+        got[item[0]] = item[1:]
+    [p.join(timeout=60) for p in procs]
+    assert got[1] == ("left",)
+    strict, local = got[0]
+    assert strict != "no error"        # the strict mode surfaces the failure
+    assert local == [[7.0, 8.0]]       # the tolerant mode keeps this rank's own numbers
