@@ -26,6 +26,7 @@ import numpy as np
 from .. import _lib
 from .._lib import BF16, BGR, F32, I420, NCHW, NHWC, NV12, RGB, U8
 from ._types import CPUBuffer, CUDABuffer, CUDAConfig, cuda_buffer
+from .utils import _tracing
 
 __all__ = [
     "nv12_to_rgb", "nv12_to_bgr", "convert_nv12", "convert_resize", "make_image_descs",
@@ -130,7 +131,9 @@ def _nv12_planar(buffers: Any, device_config: CUDAConfig, coeff: int, sync: bool
     args.layout, args.dtype, args.order = NCHW, U8, BGR if bgr else RGB
     args.scale = (ctypes.c_float * 3)(1, 1, 1)
     args.bias = (ctypes.c_float * 3)(0, 0, 0)
-    _lib.check(L.b2_convert_dense(ctypes.byref(args), device_config.stream))
+    with _tracing.trace_event("b2::nv12_to_planar"):
+        _lib.check(L.b2_convert_dense(ctypes.byref(args), device_config.stream))
+    _tracing.record("nv12_to_planar", n, n * h2 * w, out.nbytes)
     out._owner = buffers  # keep the source alive until the consumer lets go of the result
     if sync:
         synchronize_stream(device_config)
@@ -211,7 +214,9 @@ def convert_nv12(buffers: Any, *, device_config: CUDAConfig, coeff: int = 1,
     a.layout, a.dtype, a.order = lay, dt, od
     a.scale = (ctypes.c_float * 3)(*scale.tolist())
     a.bias = (ctypes.c_float * 3)(*bias.tolist())
-    _lib.check(_lib.lib().b2_convert_dense(ctypes.byref(a), device_config.stream))
+    with _tracing.trace_event("b2::convert_dense"):
+        _lib.check(_lib.lib().b2_convert_dense(ctypes.byref(a), device_config.stream))
+    _tracing.record("convert_nv12", n, n * h2 * w, out.nbytes)
     out._owner = buffers
     if sync:
         synchronize_stream(device_config)
@@ -335,7 +340,9 @@ def convert_resize(base: Any, descs: Any, *, out_size: tuple[int, int], max_src_
     a.dst, a.dst_image_stride = out.data_ptr, 0
     a.scale = (ctypes.c_float * 3)(*scale.tolist())
     a.bias = (ctypes.c_float * 3)(*bias.tolist())
-    _lib.check(_lib.lib().b2_convert_resize(ctypes.byref(a), device_config.stream))
+    with _tracing.trace_event("b2::convert_resize"):
+        _lib.check(_lib.lib().b2_convert_resize(ctypes.byref(a), device_config.stream))
+    _tracing.record("convert_resize", n, 0, out.nbytes)
     out._owner = (base, descs)
     if sync:
         synchronize_stream(device_config)
@@ -374,8 +381,10 @@ def transfer_buffer(buffer: Any, *, device_config: CUDAConfig) -> CUDABuffer:
         ptr, shape = arr.ctypes.data, arr.shape
         ec, depth = _NP_CLASS[arr.dtype.kind], arr.dtype.itemsize
     out = cuda_buffer(shape, device_config, ec, depth)
-    _lib.check(_lib.lib().b2_transfer_h2d(out.data_ptr, ptr, out.nbytes, int(pinned),
-                                          device_config.device_index, device_config.stream))
+    with _tracing.trace_event("b2::transfer_h2d"):
+        _lib.check(_lib.lib().b2_transfer_h2d(out.data_ptr, ptr, out.nbytes, int(pinned),
+                                              device_config.device_index, device_config.stream))
+    _tracing.record("transfer_buffer", 1, out.nbytes, out.nbytes)
     del keep
     return out
 

@@ -1,8 +1,10 @@
 """Build-feature probes, as ``spdl.io.utils`` (``src/spdl/io/utils/_build.py``)."""
 
 from ... import _lib
+from ._tracing import call_stats, reset_call_stats, trace_event, tracing
 
-__all__ = ["built_with_cuda", "built_with_nvcodec", "built_with_nvjpeg"]
+__all__ = ["built_with_cuda", "built_with_nvcodec", "built_with_nvjpeg", "call_stats",
+           "reset_call_stats", "trace_event", "tracing"]
 
 
 def built_with_cuda() -> bool:

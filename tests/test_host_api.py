@@ -257,3 +257,26 @@ def test_transfer_tensor_rejects_bad_local_rank(monkeypatch):
     with mock.patch.object(torch.cuda, "device_count", return_value=1):
         with pytest.raises(RuntimeError):
             _transfer.transfer_tensor(torch.zeros(1))
+
+
+def test_call_counters_and_tracing_switch():
+    from spdl_b200.io import utils
+    from spdl_b200.io.utils import _tracing
+
+    utils.reset_call_stats()
+    _tracing.record("convert_nv12", 4, 100, 200)
+    _tracing.record("convert_nv12", 2, 50, 100)
+    assert utils.call_stats() == {"convert_nv12": {"calls": 2, "units": 6, "bytes_in": 150,
+                                                   "bytes_out": 300}}
+    utils.reset_call_stats()
+    assert utils.call_stats() == {}
+    with utils.tracing(False):
+        with utils.trace_event("off"):  # no NVTX (and no torch.cuda) involved when off
+            pass
+    pushed = []
+    fake = mock.MagicMock()
+    fake.range_push.side_effect = pushed.append
+    with mock.patch.object(_tracing, "_nvtx", return_value=fake), utils.tracing(True):
+        with utils.trace_event("b2::convert_dense"):
+            pass
+    assert pushed == ["b2::convert_dense"] and fake.range_pop.call_count == 1
