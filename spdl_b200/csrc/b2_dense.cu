@@ -167,10 +167,13 @@ __global__ void __launch_bounds__(kDenseThreads, kDenseMinBlocks) dense_vec_kern
 #pragma unroll
           for (int s = 0; s < 3; ++s) {
             const uint32_t q01 = clamp2_bits(ch[s][0], ch[s][1]), q23 = clamp2_bits(ch[s][2], ch[s][3]);
-            f[s][0] = __fmaf_rn(lane_f32(q01, 0), p.sb.s[s], p.sb.b[s]);
-            f[s][1] = __fmaf_rn(lane_f32(q01, 1), p.sb.s[s], p.sb.b[s]);
-            f[s][2] = __fmaf_rn(lane_f32(q23, 0), p.sb.s[s], p.sb.b[s]);
-            f[s][3] = __fmaf_rn(lane_f32(q23, 1), p.sb.s[s], p.sb.b[s]);
+            // exact 0..255 floats of two pixels, then value * scale + bias, two lanes at a time
+            const float2 sc = dup2(p.sb.s[s]), bi = dup2(p.sb.b[s]), off = dup2(-kTwo23);
+            const float2 a = x2_fma(x2_add(make_float2(biased_byte(q01, 0), biased_byte(q01, 2)), off),
+                                    sc, bi);
+            const float2 b = x2_fma(x2_add(make_float2(biased_byte(q23, 0), biased_byte(q23, 2)), off),
+                                    sc, bi);
+            f[s][0] = a.x; f[s][1] = a.y; f[s][2] = b.x; f[s][3] = b.y;
           }
           if constexpr (DTYPE == B2_F32) {  // NW == 1
 #pragma unroll
