@@ -174,11 +174,6 @@ __device__ __forceinline__ uint32_t quant2(float a, float b) {
 __device__ __forceinline__ uint32_t bytes4(uint32_t p, uint32_t q) {
   return __byte_perm(p, q, 0x6420u);
 }
-// The float value (0..255, exact) of 16-bit lane k of a quant2 result.
-__device__ __forceinline__ float lane_f32(uint32_t p, int k) {
-  return __fsub_rn(__uint_as_float(__byte_perm(p, 0x4B000000u, 0x7540u + 2 * k)), kTwo23);
-}
-
 // One pixel straight to three integers (scalar path of the generic kernels).
 __device__ __forceinline__ void pixel_u8(const ColorMat& m, int y, int u, int v, int& r, int& g,
                                          int& b) {

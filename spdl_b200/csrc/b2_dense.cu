@@ -33,17 +33,6 @@ struct DenseParams {
   ScaleBias sb;
 };
 
-template <int NB>
-struct Vec;
-template <>
-struct Vec<16> { using type = uint4; };
-template <>
-struct Vec<8> { using type = uint2; };
-template <>
-struct Vec<4> { using type = uint32_t; };
-template <>
-struct Vec<2> { using type = uint16_t; };
-
 // Load NB bytes into ceil(NB/4) words.  Streaming (read-once) cache hint.
 template <int NB>
 __device__ __forceinline__ void load_bytes(const uint8_t* p, uint32_t* w) {
