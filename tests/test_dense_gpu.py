@@ -372,3 +372,28 @@ def test_full_size_batch_properties(cuda_cfg):
     # a checksum of checksums pins the whole batch in one number per layout
     assert int(sums.sum()) == int(io.frame_checksum(
         t_nchw.permute(0, 2, 3, 1).contiguous(), device_config=cuda_cfg).sum())
+
+
+@pytest.mark.parametrize("w", [16, 2])
+def test_more_frames_than_one_grid_dimension(cuda_cfg, w):
+    """70,000 tiny frames: more than the 65,535 a grid's z dimension holds, so the launcher has to
+    split the batch (vector path for w=16, any-shape path for w=2)."""
+    import spdl_b200.io as io
+
+    n, h = 70000, 2
+    nv = synth.nv12_batch(n, w, h, config=9, index=99, full_range=True)
+    got = _fetch(io.convert_nv12(_to_dev(nv), device_config=cuda_cfg, layout="NHWC", sync=True),
+                 "uint8")
+    want = _oracle_dense(nv, "nv12", "NHWC", "uint8", "rgb")
+    assert (got == want).all()
+
+
+def test_zero_sized_calls_are_no_ops(cuda_cfg):
+    """The C ABI accepts empty batches (nothing to do, status 0) without touching memory."""
+    from spdl_b200 import _lib
+
+    L = _lib.lib()
+    assert L.b2_nv12_to_planar_rgb(cuda_cfg.stream, None, 0, None, 0, 0, 0, 0, 1) == 0
+    assert L.b2_gather_surfaces(None, None, 0, 16, 8, None, 0, cuda_cfg.stream) == 0
+    assert L.b2_frame_checksum(None, 0, 0, None, 0, cuda_cfg.stream) == 0
+    assert L.b2_transfer_h2d(None, None, 0, 1, 0, cuda_cfg.stream) == 0
