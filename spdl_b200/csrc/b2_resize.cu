@@ -18,6 +18,8 @@
 //            a tap column ride in the two lanes of the packed fp32 instructions, so one
 //            instruction stream converts both rows of a column and the horizontal blend of both
 //            rows; 16-byte (fp32), 8-byte (bf16) or 4-byte (u8) stores per channel.
+#include <cuda_fp16.h>
+
 #include "b2_common.cuh"
 
 namespace b2 {
@@ -69,12 +71,17 @@ __device__ __forceinline__ Axis axis_of(float scale, float g, int n_in) {
 
 __device__ __forceinline__ float biased(uint32_t b) { return __uint_as_float(0x4B000000u | b); }
 
-// {row0, row1} channel values after the truncating clamp, as exact floats 0..255.
+// Two clamped 8-bit values in 16-bit lanes -> two floats, scaled by 2^-24: a halfword n (0..255)
+// read as an fp16 bit pattern is the subnormal n * 2^-24, and fp16 -> fp32 conversion is exact.
+// The blend below is linear, so it runs on the scaled values (scaling by a power of two commutes
+// with every rounding) and the factor 2^24 is folded into the final multiply.
+constexpr float kTapScale = 16777216.0f;  // 2^24
+__device__ __forceinline__ float2 halves_to_float2(uint32_t lanes) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&lanes));
+}
+// {row0, row1} channel values after the truncating clamp (see quant2), scaled by 2^-24.
 __device__ __forceinline__ float2 clamp_to_float2(float2 bits) {
-  const uint32_t c = clamp2_bits(bits.x, bits.y);
-  return x2_add(make_float2(__uint_as_float(__byte_perm(c, 0x4B000000u, 0x7540u)),
-                            __uint_as_float(__byte_perm(c, 0x4B000000u, 0x7542u))),
-                dup2(-kTwo23));
+  return halves_to_float2(clamp2_bits(bits.x, bits.y));
 }
 __device__ __forceinline__ float2 x2_mul(float2 a, float2 b) {
   unsigned long long d;
@@ -240,16 +247,15 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
         const int sx = c ? (int)(e.x >> 16) : (int)(e.x & 0xFFFFu);
         const int ci = c ? (int)(e.y >> 16) : (int)(e.y & 0xFFFFu);
         if constexpr (!kYuv) {
-          // already RGB: the taps are the bytes themselves
-          const float2 off = dup2(-kTwo23);
+          // already RGB: the taps are the bytes themselves (two rows into 16-bit lanes)
           if constexpr (FMT == B2_SRC_RGB_PLANAR) {
-            t[c][0] = x2_add(make_float2(biased(y0p[sx]), biased(y1p[sx])), off);
-            t[c][1] = x2_add(make_float2(biased(u0p[ci]), biased(u1p[ci])), off);
-            t[c][2] = x2_add(make_float2(biased(v0p[ci]), biased(v1p[ci])), off);
+            t[c][0] = halves_to_float2(__byte_perm(y0p[sx], y1p[sx], 0x5410u));
+            t[c][1] = halves_to_float2(__byte_perm(u0p[ci], u1p[ci], 0x5410u));
+            t[c][2] = halves_to_float2(__byte_perm(v0p[ci], v1p[ci], 0x5410u));
           } else {
 #pragma unroll
             for (int ch = 0; ch < 3; ++ch)
-              t[c][ch] = x2_add(make_float2(biased(y0p[sx + ch]), biased(y1p[sx + ch])), off);
+              t[c][ch] = halves_to_float2(__byte_perm(y0p[sx + ch], y1p[sx + ch], 0x5410u));
           }
           continue;
         }
@@ -292,7 +298,8 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
 #pragma unroll
       for (int k = 0; k < 4; ++k)
 #pragma unroll
-        for (int s = 0; s < 3; ++s) q[k][s] = __fadd_rz(__fadd_rn(val[k][s], 0.5f), kQuantMagic);
+        for (int s = 0; s < 3; ++s)
+          q[k][s] = __fadd_rz(__fmaf_rn(val[k][s], kTapScale, 0.5f), kQuantMagic);
       if (full4) {
         if constexpr (LAYOUT == B2_NCHW) {
 #pragma unroll
@@ -414,7 +421,7 @@ int launch_resize(const b2_resize_args& a, cudaStream_t stream) {
   p.dst = a.dst;
   p.dst_image_stride = a.dst_image_stride ? a.dst_image_stride : 3LL * a.out_w * a.out_h;
   for (int i = 0; i < 3; ++i) {
-    p.sb.s[i] = a.scale[i];
+    p.sb.s[i] = a.scale[i] * 16777216.0f;  // the kernel blends taps scaled by 2^-24 (exact)
     p.sb.b[i] = a.bias[i];
   }
   const int esz = a.dtype == B2_U8 ? 1 : (a.dtype == B2_F32 ? 4 : 2);
