@@ -352,6 +352,19 @@ def convert_resize(base: Any, descs: Any, *, out_size: tuple[int, int], max_src_
 # ---- transfer ----------------------------------------------------------------------------------
 
 _NP_CLASS = {"u": "u", "i": "i", "f": "f", "b": "u"}
+_warned_legacy_stream = False
+
+
+def _warn_legacy_stream_once() -> None:
+    global _warned_legacy_stream
+    if not _warned_legacy_stream:
+        _warned_legacy_stream = True
+        import warnings
+
+        warnings.warn(
+            "The CPU buffer is page-locked (pinned), but the legacy default CUDA stream (0) is "
+            "used. This is likely not what you intend. Please use a non-default CUDA stream to "
+            "overlap the data transfer with kernel execution.", RuntimeWarning, stacklevel=3)
 
 
 def transfer_buffer(buffer: Any, *, device_config: CUDAConfig) -> CUDABuffer:
@@ -380,6 +393,9 @@ def transfer_buffer(buffer: Any, *, device_config: CUDAConfig) -> CUDABuffer:
         keep = arr
         ptr, shape = arr.ctypes.data, arr.shape
         ec, depth = _NP_CLASS[arr.dtype.kind], arr.dtype.itemsize
+    if pinned and device_config.stream == 0:
+        # as the reference does once per process (src/libspdl/cuda/transfer.cpp:28-35,48-52)
+        _warn_legacy_stream_once()
     out = cuda_buffer(shape, device_config, ec, depth)
     with _tracing.trace_event("b2::transfer_h2d"):
         _lib.check(_lib.lib().b2_transfer_h2d(out.data_ptr, ptr, out.nbytes, int(pinned),
