@@ -208,10 +208,17 @@ def run_ours(args) -> None:
 
     info = rank_info()
     multi = info.world_size > 1
+    # stdout carries exactly one JSON line.  Libraries print there too (NCCL its version banner),
+    # so file descriptor 1 is pointed at stderr for the run and the line goes to the saved one.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(obj) -> None:
+        os.write(json_fd, (json.dumps(obj) + "\n").encode())
+
     if multi:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout
         dist.init_process_group("nccl", device_id=torch.device("cuda", info.local_rank))
     worker = ShardWorker(info)
     dev, stream, cfg = worker.device, worker.stream, worker.config
@@ -268,9 +275,8 @@ def run_ours(args) -> None:
 
     # -- end to end through the public API: pinned host NV12 -> H2D -> convert -> checksum -> D2H -
     if args.kernel_only:
-        print(json.dumps({"kernel_only": True, "ms_per_launch": ms_total / K,
-                          "gb_per_s": N_FRAMES * ALGO_BYTES_PER_FRAME / (ms_total / K * 1e-3) / 1e9}),
-              flush=True)
+        emit({"kernel_only": True, "ms_per_launch": ms_total / K,
+              "gb_per_s": N_FRAMES * ALGO_BYTES_PER_FRAME / (ms_total / K * 1e-3) / 1e9})
         return
     host = [io.CPUBuffer((N_FRAMES, H * 3 // 2, W), "u", 1,
                          io.cpu_storage(N_FRAMES * FRAME_IN, pin_memory=True)) for _ in range(2)]
@@ -341,7 +347,7 @@ def run_ours(args) -> None:
             ref = reference_kernel_fps(torch, inputs[0], cfg)
             if ref is not None:
                 line["reference_gpu_kernel"] = ref
-        print(json.dumps(line), flush=True)
+        emit(line)
     if multi:
         dist.barrier()
         dist.destroy_process_group()
