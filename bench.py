@@ -40,7 +40,7 @@ WORKLOAD = "64 x 1920x1080 NV12 -> interleaved RGB u8 (NHWC), BT.709 limited ran
 ROTATE = 4  # distinct input batches cycled through, so no step finds its input in L2
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dense kernel on this workload,
-# from the ncu capture summarised in profiles/dense_nhwc_u8_1080p_x64.md
+# from an ncu capture of this very workload (summary kept under profiles/)
 # (199,083,264 read + 362,917,632 written; part of the 398 MB output is still in L2 at kernel end).
 NCU_TRAFFIC_BYTES_PER_LAUNCH: int | None = 562_000_896
 

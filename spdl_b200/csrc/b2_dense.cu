@@ -25,11 +25,13 @@ struct DenseParams {
   const void* const* y_table;
   const void* const* u_table;
   const void* const* v_table;
-  long long y_pitch, uv_pitch, y_frame_stride, uv_frame_stride;
-  int width, height;  // height here is the even part of the frame height
+  long long y_frame_stride, uv_frame_stride;
+  int y_pitch, uv_pitch;  // bytes between rows (the launcher rejects pitches beyond 2^31)
+  int width, height;      // height here is the even part of the frame height
   ColorMat mat;
   void* dst;
-  long long dst_row_pitch, dst_plane_stride, dst_frame_stride;  // elements
+  long long dst_plane_stride, dst_frame_stride;  // elements
+  int dst_row_pitch;                              // elements
   ScaleBias sb;
 };
 
@@ -65,7 +67,8 @@ __device__ __forceinline__ uint32_t smem_addr(const void* p) {
 }
 
 constexpr int kDenseThreads = 128;
-// 12 resident CTAs (48 warps) per SM: measured best; caps the kernel at 40 registers per thread.
+// 12 resident CTAs (48 warps) per SM: measured best (CTAs of 64 threads are no faster, of 32
+// or 256 slower); caps the kernel at 40 registers per thread.
 constexpr int kDenseMinBlocks = 12;
 
 template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE>
@@ -84,6 +87,19 @@ __global__ void __launch_bounds__(kDenseThreads, kDenseMinBlocks) dense_vec_kern
 
   uint32_t out[2][12];  // 48 bytes per row, already in destination order
 
+  // Interleaved output is staged in shared memory per warp (2 rows x 32 lanes x 48 bytes).
+  extern __shared__ __align__(128) unsigned char stage_raw[];
+  const int lane = threadIdx.x & 31;
+  unsigned char* ws =
+      stage_raw + ((threadIdx.y * blockDim.x + threadIdx.x) >> 5) * (2 * 32 * 48) + lane * 48;
+  // The 16-byte pieces of a row are stored as soon as they are complete, which keeps fewer
+  // finished words alive in registers.
+  constexpr bool kEarlyStage = LAYOUT == B2_NHWC;
+  auto stage_piece = [&](int r, int i) {
+    *reinterpret_cast<uint4*>(ws + r * 1536 + i * 16) =
+        make_uint4(out[r][4 * i], out[r][4 * i + 1], out[r][4 * i + 2], out[r][4 * i + 3]);
+  };
+
   if (active) {
     const uint8_t *yb, *ub, *vb = nullptr;
     bool aligned = true;
@@ -98,20 +114,20 @@ __global__ void __launch_bounds__(kDenseThreads, kDenseMinBlocks) dense_vec_kern
       if constexpr (FMT == B2_SRC_I420) vb = p.v + (long long)n * p.uv_frame_stride;
     }
     uint32_t yw[2][NW], uw[UVW], vw[UVW];
-    const uint8_t* y0p = yb + (long long)(2 * rp) * p.y_pitch + x0;
-    const uint8_t* up = ub + (long long)rp * p.uv_pitch + (FMT == B2_SRC_NV12 ? x0 : x0 / 2);
+    const uint8_t* y0p = yb + (size_t)(2 * rp) * (unsigned)p.y_pitch + x0;
+    const uint8_t* up = ub + (size_t)rp * (unsigned)p.uv_pitch + (FMT == B2_SRC_NV12 ? x0 : x0 / 2);
     if constexpr (TABLE) {
       load_bytes_any<PX>(y0p, yw[0], aligned);
       load_bytes_any<PX>(y0p + p.y_pitch, yw[1], aligned);
       load_bytes_any<UVB>(up, uw, aligned);
       if constexpr (FMT == B2_SRC_I420)
-        load_bytes_any<UVB>(vb + (long long)rp * p.uv_pitch + x0 / 2, vw, aligned);
+        load_bytes_any<UVB>(vb + (size_t)rp * (unsigned)p.uv_pitch + x0 / 2, vw, aligned);
     } else {
       load_bytes<PX>(y0p, yw[0]);
       load_bytes<PX>(y0p + p.y_pitch, yw[1]);
       load_bytes<UVB>(up, uw);
       if constexpr (FMT == B2_SRC_I420)
-        load_bytes<UVB>(vb + (long long)rp * p.uv_pitch + x0 / 2, vw);
+        load_bytes<UVB>(vb + (size_t)rp * (unsigned)p.uv_pitch + x0 / 2, vw);
     }
     (void)vw;
 
@@ -150,6 +166,7 @@ __global__ void __launch_bounds__(kDenseThreads, kDenseMinBlocks) dense_vec_kern
             out[r][3 * j + 0] = bytes4(clamp2_bits(ch[0][0], ch[1][0]), clamp2_bits(ch[2][0], ch[0][1]));
             out[r][3 * j + 1] = bytes4(clamp2_bits(ch[1][1], ch[2][1]), clamp2_bits(ch[0][2], ch[1][2]));
             out[r][3 * j + 2] = bytes4(clamp2_bits(ch[2][2], ch[0][3]), clamp2_bits(ch[1][3], ch[2][3]));
+            if (j >= 1) stage_piece(r, j - 1);  // piece i needs the luma words up to i + 1
           }
         } else {
           float f[3][4];
@@ -170,6 +187,10 @@ __global__ void __launch_bounds__(kDenseThreads, kDenseMinBlocks) dense_vec_kern
 #pragma unroll
               for (int k = 0; k < 4; ++k)
                 out[r][LAYOUT == B2_NCHW ? 4 * s + k : 3 * k + s] = __float_as_uint(f[s][k]);
+            if constexpr (kEarlyStage) {
+#pragma unroll
+              for (int i = 0; i < 3; ++i) stage_piece(r, i);
+            }
           } else {  // bf16, NW == 2: 8 pixels, two per word
             if constexpr (LAYOUT == B2_NCHW) {
 #pragma unroll
@@ -186,6 +207,12 @@ __global__ void __launch_bounds__(kDenseThreads, kDenseMinBlocks) dense_vec_kern
                 const int e0 = 2 * w, e1 = 2 * w + 1;
                 __nv_bfloat162 t = __floats2bfloat162_rn(f[e0 % 3][e0 / 3], f[e1 % 3][e1 / 3]);
                 out[r][6 * j + w] = *reinterpret_cast<uint32_t*>(&t);
+              }
+              if (j == 0) {
+                stage_piece(r, 0);
+              } else {
+                stage_piece(r, 1);
+                stage_piece(r, 2);
               }
             }
           }
@@ -209,18 +236,6 @@ __global__ void __launch_bounds__(kDenseThreads, kDenseMinBlocks) dense_vec_kern
   } else {
     // Interleaved: the warp's 32 x 48 bytes per row are contiguous in the destination.  Stage
     // them in shared memory and hand each row segment to the bulk-copy engine.
-    extern __shared__ __align__(128) unsigned char stage_raw[];
-    const int lane = threadIdx.x & 31;
-    const int warp = (threadIdx.y * blockDim.x + threadIdx.x) >> 5;
-    unsigned char* ws = stage_raw + warp * (2 * 32 * 48);
-    if (active) {
-#pragma unroll
-      for (int r = 0; r < 2; ++r)
-#pragma unroll
-        for (int i = 0; i < 3; ++i)
-          *reinterpret_cast<uint4*>(ws + r * 1536 + lane * 48 + i * 16) =
-              make_uint4(out[r][4 * i], out[r][4 * i + 1], out[r][4 * i + 2], out[r][4 * i + 3]);
-    }
     // make the generic-proxy writes visible to the async proxy, then let lane 0 issue the copies
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncwarp();
@@ -234,7 +249,7 @@ __global__ void __launch_bounds__(kDenseThreads, kDenseMinBlocks) dense_vec_kern
         for (int r = 0; r < 2; ++r) {
           T* q = dst + (long long)(2 * rp + r) * p.dst_row_pitch + (long long)wx0 * 3;
           asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(q),
-                       "r"(smem_addr(ws + r * 1536)), "r"(bytes)
+                       "r"(smem_addr(ws + r * 1536)), "r"(bytes)  // lane 0: ws is the segment start
                        : "memory");
         }
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
@@ -354,12 +369,14 @@ int launch_dense(const DenseLaunch& L, cudaStream_t stream) {
   DenseParams p{};
   p.y = L.y; p.u = L.u; p.v = L.v;
   p.y_table = L.y_table; p.u_table = L.u_table; p.v_table = L.v_table;
-  p.y_pitch = L.y_pitch; p.uv_pitch = L.uv_pitch;
+  if (L.y_pitch > 0x7fffffffLL || L.uv_pitch > 0x7fffffffLL || L.dst_row_pitch > 0x7fffffffLL)
+    return fail(B2_ERR_LIMIT, "row pitch beyond 2^31-1 bytes");
+  p.y_pitch = (int)L.y_pitch; p.uv_pitch = (int)L.uv_pitch;
   p.y_frame_stride = L.y_frame_stride; p.uv_frame_stride = L.uv_frame_stride;
   p.width = L.width; p.height = L.height & ~1;
   p.mat = L.mat;
   p.dst = L.dst;
-  p.dst_row_pitch = L.dst_row_pitch;
+  p.dst_row_pitch = (int)L.dst_row_pitch;
   p.dst_plane_stride = L.dst_plane_stride;
   p.dst_frame_stride = L.dst_frame_stride;
   p.sb = L.sb;
