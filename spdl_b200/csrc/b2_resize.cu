@@ -38,9 +38,10 @@ struct ResizeParams {
 };
 
 constexpr int kRows = 4;  // output rows per CTA
-constexpr int kResizeThreads = 256;
-// 6 resident CTAs (48 warps) per SM measured best; caps the kernel at 40 registers per thread.
-constexpr int kResizeMinBlocks = 6;
+constexpr int kResizeThreads = 128;
+// 128-thread CTAs, 8 resident per SM (32 warps, 63 registers, no spills): measured best; larger
+// CTAs or tighter register caps (more warps, spills) were slower.
+constexpr int kResizeMinBlocks = 8;
 constexpr int kMaxSpans = kRows * 6;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
