@@ -14,6 +14,8 @@
 //            bulk-copy engine (cp.async.bulk global -> shared, completion on one mbarrier).  The
 //            spans are widened to 16-byte boundaries; global traffic is whole 16-byte segments
 //            of touched rows and nothing else.
+//   Table:   while the copies are in flight the CTA builds one entry per output column (tap
+//            offsets and weight): the horizontal taps are the same for every row of the image.
 //   Compute: each thread owns four consecutive output pixels of one row.  The two source rows of
 //            a tap column ride in the two lanes of the packed fp32 instructions, so one
 //            instruction stream converts both rows of a column and the horizontal blend of both
