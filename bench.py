@@ -480,6 +480,106 @@ def run_resize_workload(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_aux_workload(args) -> None:
+    """``--workload aux``: the small kernels around the two main ones, one GPU, CUDA events:
+    surface gather (frame batching), per-frame checksum, and the any-shape dense path."""
+    import torch
+
+    from spdl_b200 import _lib
+
+    torch.cuda.init()
+    dev = torch.device("cuda", 0)
+    stream = torch.cuda.Stream(dev)
+    L = _lib.lib()
+    K, Wm = args.steps, max(args.warmup, 3)
+    peak, _ = measured_peak()
+    n, w, h, pitch = N_FRAMES, W, H, 2048
+    h2 = h * 3 // 2
+    results = {}
+
+    def timed(fn):
+        for _ in range(Wm):
+            fn()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(K):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / K
+
+    with torch.cuda.stream(stream):
+        # 1. gather: 64 pitched 1080p NV12 surfaces (pitch 2048) -> packed batch
+        surf = [torch.randint(0, 256, (2, n, h2, pitch), dtype=torch.uint8, device=dev)]
+        packed = torch.empty((n, h2, w), dtype=torch.uint8, device=dev)
+        tabs = []
+        for c in range(2):
+            ptrs = torch.tensor([surf[0][c, i].data_ptr() for i in range(n)], dtype=torch.int64,
+                                device=dev)
+            tabs.append((ptrs, torch.full((n,), pitch, dtype=torch.int64, device=dev)))
+        stream.synchronize()
+        i = [0]
+
+        def gather():
+            i[0] += 1
+            p, q = tabs[i[0] % 2]
+            _lib.check(L.b2_gather_surfaces(p.data_ptr(), q.data_ptr(), n, w, h, packed.data_ptr(),
+                                            0, stream.cuda_stream))
+
+        ms = timed(gather)
+        b = 2 * n * h2 * w
+        results["gather_kernel"] = {"ms": ms, "bytes": b, "gb_per_s": b / ms / 1e6,
+                                    "frac": b / ms / 1e6 / peak,
+                                    "what": "64 x 1080p NV12 surfaces, pitch 2048 -> packed"}
+        # 2. checksum of a 64 x 1080p RGB batch
+        rgb = [torch.randint(0, 256, (n, h, w, 3), dtype=torch.uint8, device=dev)
+               for _ in range(2)]
+        sums = torch.empty(n, dtype=torch.int64, device=dev)
+        stream.synchronize()
+
+        def checksum():
+            i[0] += 1
+            _lib.check(L.b2_frame_checksum(rgb[i[0] % 2].data_ptr(), h * w * 3, n, sums.data_ptr(),
+                                           0, stream.cuda_stream))
+
+        ms = timed(checksum)
+        b = n * h * w * 3
+        results["checksum_kernel"] = {"ms": ms, "bytes": b, "gb_per_s": b / ms / 1e6,
+                                      "frac": b / ms / 1e6 / peak,
+                                      "what": "64 x 1080p RGB frames (read only)"}
+        # 3. any-shape dense path: width 1918 (not a multiple of 16) forces byte accesses
+        wq = 1918
+        srcq = [torch.randint(16, 236, (n, h2, wq), dtype=torch.uint8, device=dev)
+                for _ in range(2)]
+        dstq = torch.empty((n, h, wq, 3), dtype=torch.uint8, device=dev)
+        calls = []
+        for s in srcq:
+            a = _lib.DenseArgs()
+            a.struct_size = ctypes.sizeof(_lib.DenseArgs)
+            a.device, a.y, a.u = 0, s.data_ptr(), s.data_ptr() + h * wq
+            a.y_pitch = a.uv_pitch = wq
+            a.y_frame_stride = a.uv_frame_stride = h2 * wq
+            a.src_format, a.width, a.height, a.num_frames = _lib.NV12, wq, h, n
+            a.matrix_coeff, a.dst = 1, dstq.data_ptr()
+            a.layout, a.dtype, a.order = _lib.NHWC, _lib.U8, _lib.RGB
+            a.scale = (ctypes.c_float * 3)(1, 1, 1)
+            calls.append(a)
+        stream.synchronize()
+
+        def quad():
+            i[0] += 1
+            _lib.check(L.b2_convert_dense(ctypes.byref(calls[i[0] % 2]), stream.cuda_stream))
+
+        ms = timed(quad)
+        b = n * h * wq * 9 // 2
+        results["dense_quad_kernel"] = {"ms": ms, "bytes": b, "gb_per_s": b / ms / 1e6,
+                                        "frac": b / ms / 1e6 / peak,
+                                        "what": "64 x 1918x1080 NV12 -> NHWC u8 (unaligned width)"}
+    print(json.dumps({"workload": "aux", "steps": K, "warmup": Wm, "peak_gb_per_s": peak,
+                      "kernels": results}), flush=True)
+
+
 def reference_kernel_fps(torch, src, cfg) -> dict | None:
     """The reference's own kernel (planar RGB, compiled unmodified for sm_100a) on the same input,
     as the GPU-side kernel to beat.  Informational; absent when oracle/_ref was not built."""
@@ -517,14 +617,16 @@ def main() -> None:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU legs (for profiler captures)")
-    ap.add_argument("--workload", choices=["c2", "c3", "c4", "c5"], default="c2",
-                    help="c2 = the headline dense workload; c3/c4/c5 = fused resize workloads "
-                         "(one GPU, informational)")
+    ap.add_argument("--workload", choices=["c2", "c3", "c4", "c5", "aux"], default="c2",
+                    help="c2 = the headline dense workload; c3/c4/c5 = fused resize workloads; "
+                         "aux = gather, checksum and any-shape kernels (one GPU, informational)")
     ap.add_argument("--scale", default="1.0",
                     help="fraction of a resize workload's batch (for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "aux":
+        run_aux_workload(args)
     elif args.workload != "c2":
         run_resize_workload(args)
     else:

@@ -5,7 +5,7 @@ namespace b2 {
 namespace {
 
 // One CTA row copies one row of one surface.  16-byte vectors when both ends allow it.
-__global__ void __launch_bounds__(256) gather_kernel(const void* const* surfaces,
+__global__ void __launch_bounds__(128) gather_kernel(const void* const* surfaces,
                                                      const long long* pitches, int width, int h2,
                                                      uint8_t* dst) {
   const int n = blockIdx.z;
@@ -34,13 +34,29 @@ __global__ void __launch_bounds__(256) checksum_kernel(const uint8_t* src, long 
   const bool vec = (((uintptr_t)f) & 15) == 0;
   const long long nvec = vec ? frame_bytes >> 4 : 0;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
-    const uint4 q = __ldg(reinterpret_cast<const uint4*>(f) + i);
+    const uint4 q = __ldcs(reinterpret_cast<const uint4*>(f) + i);
     const uint32_t w[4] = {q.x, q.y, q.z, q.w};
     uint32_t k = (uint32_t)((i << 4) % 65521);
+    if (k + 15u < 65521u) {
+      // no wrap of the weight inside these 16 bytes:
+      //   sum (b_i + 1)(1 + k + i) = (1 + k)(sum b_i + 16) + (sum i*b_i + 120)
+      // with both byte sums from four-way dot products
+      uint32_t s1 = 16u, s2 = 120u;
+      s1 = __dp4a(w[0], 0x01010101u, s1);
+      s1 = __dp4a(w[1], 0x01010101u, s1);
+      s1 = __dp4a(w[2], 0x01010101u, s1);
+      s1 = __dp4a(w[3], 0x01010101u, s1);
+      s2 = __dp4a(w[0], 0x03020100u, s2);
+      s2 = __dp4a(w[1], 0x07060504u, s2);
+      s2 = __dp4a(w[2], 0x0B0A0908u, s2);
+      s2 = __dp4a(w[3], 0x0F0E0D0Cu, s2);
+      acc += (unsigned long long)(1u + k) * s1 + s2;
+    } else {
 #pragma unroll
-    for (int b = 0; b < 16; ++b) {
-      acc += (unsigned long long)(((w[b >> 2] >> (8 * (b & 3))) & 255u) + 1u) * (1u + k);
-      k = k + 1 == 65521u ? 0u : k + 1;
+      for (int b = 0; b < 16; ++b) {
+        acc += (unsigned long long)(((w[b >> 2] >> (8 * (b & 3))) & 255u) + 1u) * (1u + k);
+        k = k + 1 == 65521u ? 0u : k + 1;
+      }
     }
   }
   for (long long j = (nvec << 4) + (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -67,8 +83,8 @@ int launch_gather(const void* const* surfaces, const int64_t* pitches, int num_f
   const int per_row = (width + 15) / 16;
   for (int n0 = 0; n0 < num_frames; n0 += 65535) {
     const int nn = num_frames - n0 < 65535 ? num_frames - n0 : 65535;
-    dim3 grid((per_row + 255) / 256, h2, nn);
-    gather_kernel<<<grid, 256, 0, stream>>>(surfaces + n0,
+    dim3 grid((per_row + 127) / 128, h2, nn);
+    gather_kernel<<<grid, 128, 0, stream>>>(surfaces + n0,
                                             reinterpret_cast<const long long*>(pitches) + n0, width,
                                             h2, dst + (long long)n0 * h2 * width);
     B2_CUDA(cudaPeekAtLastError(), "launch of the surface gather kernel failed");
@@ -82,8 +98,9 @@ int launch_checksum(const uint8_t* src, int64_t frame_bytes, int num_frames, uin
   B2_CUDA(cudaMemsetAsync(out, 0, sizeof(uint64_t) * (size_t)num_frames, stream),
           "clearing the checksum output failed");
   if (frame_bytes == 0) return B2_OK;
-  long long blocks = (frame_bytes / 16 + 255) / 256;
-  if (blocks > 64) blocks = 64;
+  // about four 16-byte vectors per thread, at most 1024 CTAs per frame
+  long long blocks = (frame_bytes / 16 + 1023) / 1024;
+  if (blocks > 1024) blocks = 1024;
   if (blocks < 1) blocks = 1;
   for (int n0 = 0; n0 < num_frames; n0 += 65535) {
     const int nn = num_frames - n0 < 65535 ? num_frames - n0 : 65535;
