@@ -548,7 +548,7 @@ def run_aux_workload(args) -> None:
         results["checksum_kernel"] = {"ms": ms, "bytes": b, "gb_per_s": b / ms / 1e6,
                                       "frac": b / ms / 1e6 / peak,
                                       "what": "64 x 1080p RGB frames (read only)"}
-        # 3. any-shape dense path: width 1918 (not a multiple of 16) forces byte accesses
+        # 3. unaligned rows: width 1918 (not a multiple of 16) takes the realigning rows kernel
         wq = 1918
         srcq = [torch.randint(16, 236, (n, h2, wq), dtype=torch.uint8, device=dev)
                 for _ in range(2)]
@@ -573,7 +573,7 @@ def run_aux_workload(args) -> None:
 
         ms = timed(quad)
         b = n * h * wq * 9 // 2
-        results["dense_quad_kernel"] = {"ms": ms, "bytes": b, "gb_per_s": b / ms / 1e6,
+        results["dense_rows_kernel"] = {"ms": ms, "bytes": b, "gb_per_s": b / ms / 1e6,
                                         "frac": b / ms / 1e6 / peak,
                                         "what": "64 x 1918x1080 NV12 -> NHWC u8 (unaligned width)"}
     print(json.dumps({"workload": "aux", "steps": K, "warmup": Wm, "peak_gb_per_s": peak,

@@ -260,6 +260,246 @@ __global__ void __launch_bounds__(kDenseThreads, kDenseMinBlocks) dense_vec_kern
   }
 }
 
+// One thread's block of 2 rows x PX pixels: luma words yw, chroma words uw (and vw for I420) in,
+// 48 bytes per row out, already in destination order (interleaved: linear; planar: 16 bytes per
+// output slot).  The same arithmetic as the vector kernel's inner loop.
+template <int FMT, int LAYOUT, int DTYPE, bool BGR, int NW, int UVW>
+__device__ __forceinline__ void convert_chunk(const ColorMat& m, const ScaleBias& sb,
+                                              const uint32_t (&yw)[2][NW],
+                                              const uint32_t (&uw)[UVW],
+                                              const uint32_t (&vw)[UVW], uint32_t (&out)[2][12]) {
+#pragma unroll
+  for (int j = 0; j < NW; ++j) {
+    Chroma2 c;
+    if constexpr (FMT == B2_SRC_NV12) {
+      c = chroma2_of(m, make_float2(biased_byte(uw[j], 0), biased_byte(uw[j], 2)),
+                     make_float2(biased_byte(uw[j], 1), biased_byte(uw[j], 3)));
+    } else {
+      const int w = j >> 1, b = (j & 1) * 2;
+      c = chroma2_of(m, make_float2(biased_byte(uw[w], b), biased_byte(uw[w], b + 1)),
+                     make_float2(biased_byte(vw[w], b), biased_byte(vw[w], b + 1)));
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      float ch[3][4];
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        float2 cr, cg, cb;
+        pixel2_bits(m, make_float2(biased_byte(yw[r][j], k), biased_byte(yw[r][j], k + 2)), c, cr,
+                    cg, cb);
+        ch[BGR ? 2 : 0][k] = cr.x; ch[BGR ? 2 : 0][k + 2] = cr.y;
+        ch[1][k] = cg.x;           ch[1][k + 2] = cg.y;
+        ch[BGR ? 0 : 2][k] = cb.x; ch[BGR ? 0 : 2][k + 2] = cb.y;
+      }
+      if constexpr (DTYPE == B2_U8) {
+        if constexpr (LAYOUT == B2_NCHW) {
+#pragma unroll
+          for (int s = 0; s < 3; ++s)
+            out[r][4 * s + j] =
+                bytes4(clamp2_bits(ch[s][0], ch[s][1]), clamp2_bits(ch[s][2], ch[s][3]));
+        } else {
+          out[r][3 * j + 0] = bytes4(clamp2_bits(ch[0][0], ch[1][0]), clamp2_bits(ch[2][0], ch[0][1]));
+          out[r][3 * j + 1] = bytes4(clamp2_bits(ch[1][1], ch[2][1]), clamp2_bits(ch[0][2], ch[1][2]));
+          out[r][3 * j + 2] = bytes4(clamp2_bits(ch[2][2], ch[0][3]), clamp2_bits(ch[1][3], ch[2][3]));
+        }
+      } else {
+        float f[3][4];
+#pragma unroll
+        for (int s = 0; s < 3; ++s) {
+          const uint32_t q01 = clamp2_bits(ch[s][0], ch[s][1]), q23 = clamp2_bits(ch[s][2], ch[s][3]);
+          const float2 sc = dup2(sb.s[s]), bi = dup2(sb.b[s]), off = dup2(-kTwo23);
+          const float2 a = x2_fma(
+              x2_add(make_float2(biased_byte(q01, 0), biased_byte(q01, 2)), off), sc, bi);
+          const float2 b = x2_fma(
+              x2_add(make_float2(biased_byte(q23, 0), biased_byte(q23, 2)), off), sc, bi);
+          f[s][0] = a.x; f[s][1] = a.y; f[s][2] = b.x; f[s][3] = b.y;
+        }
+        if constexpr (DTYPE == B2_F32) {
+#pragma unroll
+          for (int s = 0; s < 3; ++s)
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              out[r][LAYOUT == B2_NCHW ? 4 * s + k : 3 * k + s] = __float_as_uint(f[s][k]);
+        } else if constexpr (LAYOUT == B2_NCHW) {
+#pragma unroll
+          for (int s = 0; s < 3; ++s)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              __nv_bfloat162 t = __floats2bfloat162_rn(f[s][2 * h], f[s][2 * h + 1]);
+              out[r][4 * s + 2 * j + h] = *reinterpret_cast<uint32_t*>(&t);
+            }
+        } else {
+#pragma unroll
+          for (int w = 0; w < 6; ++w) {
+            const int e0 = 2 * w, e1 = 2 * w + 1;
+            __nv_bfloat162 t = __floats2bfloat162_rn(f[e0 % 3][e0 / 3], f[e1 % 3][e1 / 3]);
+            out[r][6 * j + w] = *reinterpret_cast<uint32_t*>(&t);
+          }
+        }
+      }
+    }
+  }
+}
+
+// ---- rows path: any alignment, vector arithmetic ------------------------------------------------
+// Packed batches whose width is not a multiple of 16 (854x480 video, odd crops) have rows that
+// start on arbitrary byte boundaries, which rules out the vector kernel's direct 16-byte
+// accesses.  Here one CTA owns a row pair of one frame: it copies the source rows into shared
+// memory with aligned 16-byte global loads, shifting bytes into place with funnel shifts, runs
+// the same packed arithmetic out of shared memory, assembles the output rows in shared memory
+// and writes them with aligned 16-byte global stores (plus a few byte stores at the ragged ends).
+
+// smem[0..n) = g[0..n) for any alignment of g.  Reads whole aligned 16-byte segments (each holds
+// at least one valid byte, so it lies inside the allocation); writes whole 16-byte vectors, i.e.
+// up to 15 bytes of padding past n.
+__device__ __forceinline__ void rows_load(unsigned char* s, const uint8_t* g, int n, int tid,
+                                          int nthreads) {
+  const int a = (int)((uintptr_t)g & 15);
+  const uint4* gv = reinterpret_cast<const uint4*>(g - a);
+  const int nsrc = (a + n + 15) >> 4, ndst = (n + 15) >> 4;
+  const int ws = a >> 2, bs = (a & 3) * 8;
+  for (int k = tid; k < ndst; k += nthreads) {
+    const uint4 lo = __ldg(gv + k);
+    const uint4 hi = k + 1 < nsrc ? __ldg(gv + k + 1) : make_uint4(0u, 0u, 0u, 0u);
+    uint32_t w0, w1, w2, w3, w4;  // five consecutive source words starting at word `ws`
+    switch (ws) {
+      case 0: w0 = lo.x; w1 = lo.y; w2 = lo.z; w3 = lo.w; w4 = hi.x; break;
+      case 1: w0 = lo.y; w1 = lo.z; w2 = lo.w; w3 = hi.x; w4 = hi.y; break;
+      case 2: w0 = lo.z; w1 = lo.w; w2 = hi.x; w3 = hi.y; w4 = hi.z; break;
+      default: w0 = lo.w; w1 = hi.x; w2 = hi.y; w3 = hi.z; w4 = hi.w; break;
+    }
+    reinterpret_cast<uint4*>(s)[k] =
+        make_uint4(__funnelshift_r(w0, w1, bs), __funnelshift_r(w1, w2, bs),
+                   __funnelshift_r(w2, w3, bs), __funnelshift_r(w3, w4, bs));
+  }
+}
+
+// g[0..n) = smem[0..n) for any alignment of g; `s` is 16-byte aligned and readable up to
+// n + 19 bytes.  Aligned 16-byte stores for the body, byte stores for the ragged head and tail.
+__device__ __forceinline__ void rows_store(uint8_t* g, const unsigned char* s, int n, int tid,
+                                           int nthreads) {
+  int head = (int)((16 - ((uintptr_t)g & 15)) & 15);
+  if (head > n) head = n;
+  const int nvec = (n - head) >> 4;
+  const int tail0 = head + (nvec << 4);
+  for (int i = tid; i < head; i += nthreads) g[i] = s[i];
+  for (int i = tail0 + tid; i < n; i += nthreads) g[i] = s[i];
+  const uint32_t* sw = reinterpret_cast<const uint32_t*>(s + (head & ~3));
+  const int bs = (head & 3) * 8;
+  uint4* gv = reinterpret_cast<uint4*>(g + head);
+  for (int k = tid; k < nvec; k += nthreads) {
+    const uint32_t* q = sw + 4 * k;
+    const uint32_t w0 = q[0], w1 = q[1], w2 = q[2], w3 = q[3], w4 = q[4];
+    __stcs(gv + k, make_uint4(__funnelshift_r(w0, w1, bs), __funnelshift_r(w1, w2, bs),
+                              __funnelshift_r(w2, w3, bs), __funnelshift_r(w3, w4, bs)));
+  }
+}
+
+constexpr int kRowsThreads = 128;
+
+// Shared-memory plan of the rows kernel for a frame width, per row pair.
+struct RowsPlan {
+  int in_row;    // bytes reserved per staged source row
+  int out_row;   // bytes reserved per assembled output row (NHWC) or plane row (NCHW)
+  int total;
+};
+template <int LAYOUT, int DTYPE>
+__host__ __device__ inline RowsPlan rows_plan(int width) {
+  constexpr int esz = DTYPE == B2_U8 ? 1 : (DTYPE == B2_F32 ? 4 : 2);
+  constexpr int px = 16 / esz;
+  const int chunks = (width + px - 1) / px;
+  RowsPlan r;
+  r.in_row = ((width + 15) & ~15) + 32;
+  r.out_row = LAYOUT == B2_NHWC ? chunks * 48 + 32 : chunks * 16 + 32;
+  r.total = 4 * r.in_row + 2 * (LAYOUT == B2_NHWC ? 1 : 3) * r.out_row;
+  return r;
+}
+
+template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE>
+__global__ void __launch_bounds__(kRowsThreads) dense_rows_kernel(const DenseParams p) {
+  using T = typename OutT<DTYPE>::type;
+  constexpr int PX = 16 / (int)sizeof(T);
+  constexpr int NW = PX / 4;
+  constexpr int UVB = FMT == B2_SRC_NV12 ? PX : PX / 2;
+  constexpr int UVW = (UVB + 3) / 4;
+  extern __shared__ __align__(128) unsigned char rows_smem[];
+  const RowsPlan plan = rows_plan<LAYOUT, DTYPE>(p.width);
+  unsigned char* sy0 = rows_smem;
+  unsigned char* sy1 = sy0 + plan.in_row;
+  unsigned char* su = sy1 + plan.in_row;
+  unsigned char* sv = su + plan.in_row;
+  unsigned char* so = sv + plan.in_row;  // [2][kOutRows][out_row]
+
+  const int rp = blockIdx.x, n = blockIdx.y, tid = threadIdx.x;
+  const int we = p.width & ~1;  // a trailing odd column is left untouched
+  const uint8_t *yb, *ub, *vb = nullptr;
+  if constexpr (TABLE) {
+    yb = static_cast<const uint8_t*>(p.y_table[n]);
+    ub = static_cast<const uint8_t*>(p.u_table[n]);
+    if constexpr (FMT == B2_SRC_I420) vb = static_cast<const uint8_t*>(p.v_table[n]);
+  } else {
+    yb = p.y + (long long)n * p.y_frame_stride;
+    ub = p.u + (long long)n * p.uv_frame_stride;
+    if constexpr (FMT == B2_SRC_I420) vb = p.v + (long long)n * p.uv_frame_stride;
+  }
+  rows_load(sy0, yb + (size_t)(2 * rp) * (unsigned)p.y_pitch, we, tid, kRowsThreads);
+  rows_load(sy1, yb + (size_t)(2 * rp + 1) * (unsigned)p.y_pitch, we, tid, kRowsThreads);
+  rows_load(su, ub + (size_t)rp * (unsigned)p.uv_pitch, FMT == B2_SRC_NV12 ? we : we / 2, tid,
+            kRowsThreads);
+  if constexpr (FMT == B2_SRC_I420)
+    rows_load(sv, vb + (size_t)rp * (unsigned)p.uv_pitch, we / 2, tid, kRowsThreads);
+  __syncthreads();
+
+  const ColorMat& m = p.mat;
+  const int chunks = (we + PX - 1) / PX;
+  for (int c = tid; c < chunks; c += kRowsThreads) {
+    uint32_t yw[2][NW], uw[UVW], vw[UVW];
+#pragma unroll
+    for (int i = 0; i < NW; ++i) {
+      yw[0][i] = reinterpret_cast<const uint32_t*>(sy0)[c * NW + i];
+      yw[1][i] = reinterpret_cast<const uint32_t*>(sy1)[c * NW + i];
+    }
+    if constexpr (UVB >= 4) {
+#pragma unroll
+      for (int i = 0; i < UVW; ++i) {
+        uw[i] = reinterpret_cast<const uint32_t*>(su)[c * UVW + i];
+        if constexpr (FMT == B2_SRC_I420) vw[i] = reinterpret_cast<const uint32_t*>(sv)[c * UVW + i];
+      }
+    } else {  // fp32 output from I420: two chroma bytes per plane and chunk
+      uw[0] = reinterpret_cast<const uint16_t*>(su)[c];
+      vw[0] = reinterpret_cast<const uint16_t*>(sv)[c];
+    }
+    (void)vw;
+    uint32_t out[2][12];
+    convert_chunk<FMT, LAYOUT, DTYPE, BGR>(m, p.sb, yw, uw, vw, out);
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+      for (int i = 0; i < 3; ++i) {
+        unsigned char* q = LAYOUT == B2_NHWC ? so + (size_t)r * plan.out_row + c * 48 + i * 16
+                                             : so + (size_t)(r * 3 + i) * plan.out_row + c * 16;
+        *reinterpret_cast<uint4*>(q) =
+            make_uint4(out[r][4 * i], out[r][4 * i + 1], out[r][4 * i + 2], out[r][4 * i + 3]);
+      }
+  }
+  __syncthreads();
+
+  uint8_t* dst = reinterpret_cast<uint8_t*>(static_cast<T*>(p.dst) + (long long)n * p.dst_frame_stride);
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const long long row = 2 * rp + r;
+    if constexpr (LAYOUT == B2_NHWC) {
+      rows_store(dst + row * p.dst_row_pitch * (long long)sizeof(T), so + (size_t)r * plan.out_row,
+                 we * 3 * (int)sizeof(T), tid, kRowsThreads);
+    } else {
+#pragma unroll
+      for (int s = 0; s < 3; ++s)
+        rows_store(dst + (s * p.dst_plane_stride + row * p.dst_row_pitch) * (long long)sizeof(T),
+                   so + (size_t)(r * 3 + s) * plan.out_row, we * (int)sizeof(T), tid, kRowsThreads);
+    }
+  }
+}
+
 // Any-shape path: one thread per 2x2 quad (color_conversion.cu:98-137 has the same ownership).
 template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE>
 __global__ void __launch_bounds__(256) dense_quad_kernel(const DenseParams p) {
@@ -333,6 +573,15 @@ int launch_t(const DenseLaunch& L, const DenseParams& p, bool vec, cudaStream_t 
       dim3 block(bx, by), grid((chunks + bx - 1) / bx, (He / 2 + by - 1) / by, nn);
       const size_t smem = LAYOUT == B2_NHWC ? (size_t)(kDenseThreads / 32) * 2 * 32 * 48 : 0;
       dense_vec_kernel<FMT, LAYOUT, DTYPE, BGR, TABLE><<<grid, block, smem, stream>>>(q);
+    } else if (rows_plan<LAYOUT, DTYPE>(L.width).total <= 200 * 1024 && L.width >= 16) {
+      // unaligned rows: realign through shared memory, one CTA per row pair
+      if (He < 2) continue;
+      auto kern = dense_rows_kernel<FMT, LAYOUT, DTYPE, BGR, TABLE>;
+      const int smem = rows_plan<LAYOUT, DTYPE>(L.width).total;
+      if (smem > 48 * 1024)
+        B2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+                "raising the shared-memory limit of the rows kernel failed");
+      kern<<<dim3(He / 2, nn), kRowsThreads, smem, stream>>>(q);
     } else {
       dim3 block(32, 8), grid((L.width / 2 + 31) / 32, (He / 2 + 7) / 8, nn);
       if (grid.x == 0 || grid.y == 0) continue;
