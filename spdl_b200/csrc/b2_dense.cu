@@ -1,6 +1,6 @@
 // Dense colour conversion: every pixel of every frame, no resampling.
 //
-// Two kernel families.
+// Three kernel families.
 //   dense_vec_kernel   the fast path.  One thread owns a 2-row x PX-pixel block (PX = 16 bytes
 //                      of output per channel: 16 px for u8, 8 for bf16, 4 for fp32), so the two
 //                      rows share one chroma load, every global load is one 4/8/16-byte vector
@@ -9,8 +9,11 @@
 //                      instruction).  Interleaved output (48 bytes per thread per row) is staged
 //                      in shared memory by the warp and leaves as one bulk asynchronous copy
 //                      (cp.async.bulk shared->global) per row segment.
-//   dense_quad_kernel  the any-shape path: one thread per 2x2 quad with byte accesses.  Taken
-//                      when a pointer, pitch or the width breaks the vector path's alignment.
+//   dense_rows_kernel  rows on arbitrary byte boundaries (a pointer, pitch or width that breaks
+//                      the vector path's alignment): one CTA per row pair realigns the rows
+//                      through shared memory and runs the same packed arithmetic from there.
+//   dense_quad_kernel  the last resort: one thread per 2x2 quad with byte accesses (widths under
+//                      16, rows too wide for shared memory).
 //
 // The kernels are HBM-bound: 1.5 bytes read and 3*sizeof(T) written per pixel.
 #include "b2_common.cuh"
