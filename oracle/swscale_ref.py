@@ -71,9 +71,11 @@ def load():
 
 
 class I420ToRGB:
-    """One converter (one ``SwsContext``): yuv420p ``w x h`` -> rgb24, limited -> full range."""
+    """One converter (one ``SwsContext``): yuv420p ``w x h`` -> rgb24, limited (or, with
+    ``full_range``, full) -> full range."""
 
-    def __init__(self, w: int, h: int, colorspace: int = SWS_CS_ITU709, dst_fmt: str = "rgb24"):
+    def __init__(self, w: int, h: int, colorspace: int = SWS_CS_ITU709, dst_fmt: str = "rgb24",
+                 full_range: bool = False):
         sws = load()
         if sws is None:
             raise RuntimeError("libswscale is not available on this machine")
@@ -84,7 +86,7 @@ class I420ToRGB:
         if not self.ctx:
             raise RuntimeError("sws_getContext failed")
         coefs = sws.sws_getCoefficients(colorspace)
-        sws.sws_setColorspaceDetails(self.ctx, coefs, 0, coefs, 1, 0, 1 << 16, 1 << 16)
+        sws.sws_setColorspaceDetails(self.ctx, coefs, int(full_range), coefs, 1, 0, 1 << 16, 1 << 16)
 
     def __call__(self, i420: np.ndarray, out: np.ndarray) -> None:
         """``i420``: ``[h*3/2, w]`` u8 (Y rows, U block, V block); ``out``: ``[h, w, 3]`` u8."""

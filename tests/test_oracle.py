@@ -200,3 +200,58 @@ def test_small_batches_match_reference_kernel():
         for coeff in (1, 6, 9):
             assert (oracle.nv12_to_planar(nv, coeff=coeff) == z[f"{name}_rgb_{coeff}"]).all()
         assert (oracle.nv12_to_planar(nv, coeff=1, order=oracle.BGR) == z[f"{name}_bgr_1"]).all()
+
+
+# ---- libswscale, the arithmetic of the reference's CPU route ------------------------------------
+
+
+@pytest.mark.parametrize("colorspace,coeff", [(1, 1), (5, 6)])
+@pytest.mark.parametrize("full", [False, True])
+def test_swscale_computes_the_same_transform(colorspace, coeff, full):
+    """The reference's CPU route (libswscale, fixed-point tables, nearest chroma) and its CUDA
+    kernel (fp32) are two implementations of one transform: on in-gamut input they agree to the
+    table precision of libswscale -- at most 1 apart for full-range sources, at most 4 apart and
+    99 % within 2 for limited-range ones.  This is what makes libswscale a fair CPU baseline."""
+    from oracle import swscale_ref
+
+    if not swscale_ref.available():
+        pytest.skip("no libswscale on this machine")
+    w, h = 256, 128
+    r = np.random.default_rng(11)
+    i420 = np.empty((1, h * 3 // 2, w), np.uint8)
+    i420[0, :h] = r.integers(16, 236, (h, w))
+    i420[0, h:] = r.integers(100, 156, (h // 2, w))
+    got = np.empty((h, w, 3), np.uint8)
+    swscale_ref.I420ToRGB(w, h, colorspace=colorspace, full_range=full)(i420[0], got)
+    flat = i420.reshape(-1)
+    want = oracle.convert_dense(
+        i420, flat[h * w:], flat[h * w + (h // 2) * (w // 2):], width=w, height=h, num_frames=1,
+        y_pitch=w, uv_pitch=w // 2, y_frame_stride=h * 3 // 2 * w, uv_frame_stride=h * 3 // 2 * w,
+        src_format=oracle.I420, layout=oracle.NHWC, coeff=coeff, full_range=full)[0]
+    d = np.abs(got.astype(np.int16) - want)
+    if full:
+        assert d.max() <= 1
+    else:
+        assert d.max() <= 4 and (d <= 2).mean() > 0.99
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_bilinear_matches_torch_random_geometry(seed):
+    """Random source and target sizes (up- and down-scaling, odd sizes), with and without a
+    crop: the resize restatement equals torch's bilinear on the converted RGB, the crop being a
+    slice of the uncropped result."""
+    import spdl_b200.io as io
+
+    r = np.random.default_rng(4000 + seed)
+    w, h = int(r.integers(4, 40)) * 2, int(r.integers(4, 40)) * 2
+    rw, rh = int(r.integers(2, 90)), int(r.integers(2, 90))
+    nv = synth.nv12_batch(1, w, h, config=9, index=seed)
+    rgb = oracle.nv12_to_planar(nv)
+    want = _torch_bilinear(rgb, (rh, rw))
+    geom = dict(resize=(rw, rh))
+    if seed % 2:
+        geom["crop"] = (int(r.integers(1, rw + 1)), int(r.integers(1, rh + 1)))
+    descs, (ow, oh) = io.make_image_descs([w], [h], **geom)
+    got = oracle.convert_resize(nv.reshape(-1), descs, out_w=ow, out_h=oh, dtype=oracle.F32)
+    cx, cy = int(descs["crop_x"][0]), int(descs["crop_y"][0])
+    np.testing.assert_allclose(got, want[:, :, cy:cy + oh, cx:cx + ow], rtol=0, atol=3e-4)
