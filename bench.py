@@ -32,6 +32,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 N_FRAMES, W, H = 64, 1920, 1080
+SCALING = "weak"
 FRAME_IN = W * H * 3 // 2
 FRAME_OUT = W * H * 3
 ALGO_BYTES_PER_FRAME = FRAME_IN + FRAME_OUT  # 9,331,200
@@ -161,8 +162,23 @@ def time_cpu(frames: int, steps: int, warmup: int, budget_s: float = 60.0) -> di
     for _ in range(steps):
         run()
     dt = time.perf_counter() - t0
-    return {"value": frames * steps / dt, "unit": "frames/s", "cores": cpu_cores(), "kind": kind,
-            "sample": desc, "ms_per_step": 1e3 * dt / steps, "frames_per_step": frames}
+    res = {"value": frames * steps / dt, "unit": "frames/s", "cores": cpu_cores(), "kind": kind,
+           "sample": desc, "ms_per_step": 1e3 * dt / steps, "frames_per_step": frames}
+    if kind == "reference":
+        # The reference's filter graph runs on one thread
+        # (src/libspdl/core/detail/ffmpeg/filter_graph.cpp:52); that figure, on 8 frames.
+        from oracle import swscale_ref
+        from tests import synth
+
+        one = swscale_ref.BatchConverter(W, H, 1)
+        b8 = synth.i420_batch_gradient(8, W, H, config=1)
+        o8 = np.empty((8, H, W, 3), np.uint8)
+        one(b8[:1], o8[:1])
+        t0 = time.perf_counter()
+        one(b8, o8)
+        res["single_thread_frames_per_s"] = 8 / (time.perf_counter() - t0)
+        one.close()
+    return res
 
 
 def run_reference_arm(args) -> None:
@@ -178,7 +194,8 @@ def run_reference_arm(args) -> None:
         "config": {"workload": WORKLOAD, "frames_per_step": r["frames_per_step"],
                    "note": "CPU path takes yuv420p (what FFmpeg decoders emit) instead of NV12; "
                            "a step is a bounded sample of the 64-frame batch"},
-        "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample",
+                                           "single_thread_frames_per_s") if k in r},
         "e2e": {"value": r["value"], "unit": "frames/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
     }
@@ -226,7 +243,8 @@ def run_ours(args) -> None:
     K, Wm = args.steps, max(args.warmup, 3)
 
     inputs = [synth_batch_on_device(torch, dev, 2000 + 17 * info.rank + i) for i in range(ROTATE)]
-    outputs = [torch.empty((N_FRAMES, H, W, 3), dtype=torch.uint8, device=dev) for _ in range(2)]
+    outputs = [torch.empty((N_FRAMES, H, W, 3), dtype=torch.uint8, device=dev)
+               for _ in range(ROTATE // 2)]
     torch.cuda.synchronize(dev)
 
     def dense_args(src, dst):
@@ -244,7 +262,7 @@ def run_ours(args) -> None:
         a.bias = (ctypes.c_float * 3)(0, 0, 0)
         return a
 
-    calls = [dense_args(inputs[i % ROTATE], outputs[i % 2]) for i in range(ROTATE * 2)]
+    calls = [dense_args(inputs[i % ROTATE], outputs[i % len(outputs)]) for i in range(ROTATE * 2)]
     launches = 0
 
     def step(i):
@@ -321,11 +339,12 @@ def run_ours(args) -> None:
         line = {
             "metric": METRIC, "value": total_frames / (ms_max * 1e-3), "unit": "frames/s",
             "n_gpus": info.world_size, "steps": K, "warmup": Wm, "ms_per_step": ms_max / K,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8",
+            "higher_is_better": True, "scaling": SCALING, "vs_baseline": None, "dtype": "u8",
             "data": "synthetic",
             "config": {"workload": WORKLOAD, "frames_per_step_per_gpu": N_FRAMES,
-                       "l2": f"inputs (199 MB per batch) exceed L2 and rotate over {ROTATE} "
-                             f"batches",
+                       "l2": f"inputs ({N_FRAMES * FRAME_IN / 1e6:.0f} MB per batch) rotate over "
+                             f"{ROTATE} batches, {ROTATE * N_FRAMES * FRAME_IN / 1e6:.0f} MB in "
+                             f"all, more than L2",
                        "sharding": "each rank converts its own frames; no data-path collective"},
             "e2e": {"value": N_FRAMES * info.world_size / e2e_max, "unit": "frames/s",
                     "steps": min(K, 50),
@@ -334,7 +353,8 @@ def run_ours(args) -> None:
                             "host, per step, two worker threads on private streams, host-timed"},
             "gpu_launches": timed_launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                         "frac": achieved / peak, "frac_of_nominal_8000": achieved / 8000.0,
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH * N_FRAMES // 64,
                          "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)"
                          if peak_kind == "measured" else "fallback 6650 GB/s",
                          "algorithmic_bytes_per_launch": N_FRAMES * ALGO_BYTES_PER_FRAME,
@@ -605,8 +625,25 @@ def reference_kernel_fps(torch, src, cfg) -> dict | None:
     e1.record(stream)
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / 20
+
+    # The reference's call around that kernel allocates the output with cudaMalloc every time
+    # (src/libspdl/cuda/storage.cpp:44-58) and frees it when the buffer dies: the same launches
+    # with that allocation pattern, host-timed.
+    from spdl_b200 import _lib
+
+    L, index = _lib.lib(), src.device.index or 0
+    t0 = time.perf_counter()
+    for _ in range(10):
+        p = ctypes.c_void_p()
+        _lib.check(L.b2_device_alloc(ctypes.byref(p), N_FRAMES * 3 * H * W, index))
+        ref.ref_nv12_to_planar_rgb(stream.cuda_stream, src.data_ptr(), W, p.value, W, W, H,
+                                   N_FRAMES, 1)
+        stream.synchronize()
+        _lib.check(L.b2_device_free(p, index))
+    alloc_s = (time.perf_counter() - t0) / 10
     return {"value": N_FRAMES / (ms * 1e-3), "unit": "frames/s", "layout": "planar RGB u8",
-            "gb_per_s": N_FRAMES * ALGO_BYTES_PER_FRAME / (ms * 1e-3) / 1e9}
+            "gb_per_s": N_FRAMES * ALGO_BYTES_PER_FRAME / (ms * 1e-3) / 1e9,
+            "with_per_call_cudaMalloc": N_FRAMES / alloc_s}
 
 
 def main() -> None:
@@ -622,7 +659,16 @@ def main() -> None:
                          "aux = gather, checksum and any-shape kernels (one GPU, informational)")
     ap.add_argument("--scale", default="1.0",
                     help="fraction of a resize workload's batch (for profiler captures)")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
+                    help="c2 only: weak = 64 frames per GPU (default); strong = 64 frames per step "
+                         "split over the GPUs")
     args = ap.parse_args()
+    if args.scaling == "strong" and args.workload == "c2" and args.impl == "ours":
+        global N_FRAMES, SCALING, ROTATE
+        if 64 % max(args.gpus, 1):
+            raise SystemExit("--scaling strong needs a GPU count that divides 64")
+        N_FRAMES, SCALING = 64 // max(args.gpus, 1), "strong"
+        ROTATE = 4 * 64 // N_FRAMES  # keep the rotated inputs at 796 MB per GPU, well above L2
     if args.impl == "reference":
         run_reference_arm(args)
     elif args.workload == "aux":

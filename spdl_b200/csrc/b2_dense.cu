@@ -378,7 +378,7 @@ __device__ __forceinline__ void rows_load(unsigned char* s, const uint8_t* g, in
 }
 
 // g[0..n) = smem[0..n) for any alignment of g; `s` is 16-byte aligned and readable up to
-// n + 19 bytes.  Aligned 16-byte stores for the body, byte stores for the ragged head and tail.
+// n + 16 bytes.  Aligned 16-byte stores for the body, byte stores for the ragged head and tail.
 __device__ __forceinline__ void rows_store(uint8_t* g, const unsigned char* s, int n, int tid,
                                            int nthreads) {
   int head = (int)((16 - ((uintptr_t)g & 15)) & 15);
@@ -387,14 +387,36 @@ __device__ __forceinline__ void rows_store(uint8_t* g, const unsigned char* s, i
   const int tail0 = head + (nvec << 4);
   for (int i = tid; i < head; i += nthreads) g[i] = s[i];
   for (int i = tail0 + tid; i < n; i += nthreads) g[i] = s[i];
-  const uint32_t* sw = reinterpret_cast<const uint32_t*>(s + (head & ~3));
-  const int bs = (head & 3) * 8;
+  // two aligned 16-byte shared loads per vector (conflict-free), then the same word select and
+  // byte shift as on the load side
+  const uint4* sv = reinterpret_cast<const uint4*>(s);
+  const int ws = head >> 2, bs = (head & 3) * 8;
   uint4* gv = reinterpret_cast<uint4*>(g + head);
   for (int k = tid; k < nvec; k += nthreads) {
-    const uint32_t* q = sw + 4 * k;
-    const uint32_t w0 = q[0], w1 = q[1], w2 = q[2], w3 = q[3], w4 = q[4];
+    const uint4 lo = sv[k], hi = sv[k + 1];
+    uint32_t w0, w1, w2, w3, w4;
+    switch (ws) {
+      case 0: w0 = lo.x; w1 = lo.y; w2 = lo.z; w3 = lo.w; w4 = hi.x; break;
+      case 1: w0 = lo.y; w1 = lo.z; w2 = lo.w; w3 = hi.x; w4 = hi.y; break;
+      case 2: w0 = lo.z; w1 = lo.w; w2 = hi.x; w3 = hi.y; w4 = hi.z; break;
+      default: w0 = lo.w; w1 = hi.x; w2 = hi.y; w3 = hi.z; w4 = hi.w; break;
+    }
     __stcs(gv + k, make_uint4(__funnelshift_r(w0, w1, bs), __funnelshift_r(w1, w2, bs),
                               __funnelshift_r(w2, w3, bs), __funnelshift_r(w3, w4, bs)));
+  }
+}
+
+// One aligned shared load of NW 32-bit words.
+template <int NW>
+__device__ __forceinline__ void lds_words(const unsigned char* s, int index, uint32_t (&w)[NW]) {
+  if constexpr (NW == 4) {
+    const uint4 q = reinterpret_cast<const uint4*>(s)[index];
+    w[0] = q.x; w[1] = q.y; w[2] = q.z; w[3] = q.w;
+  } else if constexpr (NW == 2) {
+    const uint2 q = reinterpret_cast<const uint2*>(s)[index];
+    w[0] = q.x; w[1] = q.y;
+  } else {
+    w[0] = reinterpret_cast<const uint32_t*>(s)[index];
   }
 }
 
@@ -457,17 +479,11 @@ __global__ void __launch_bounds__(kRowsThreads) dense_rows_kernel(const DensePar
   const int chunks = (we + PX - 1) / PX;
   for (int c = tid; c < chunks; c += kRowsThreads) {
     uint32_t yw[2][NW], uw[UVW], vw[UVW];
-#pragma unroll
-    for (int i = 0; i < NW; ++i) {
-      yw[0][i] = reinterpret_cast<const uint32_t*>(sy0)[c * NW + i];
-      yw[1][i] = reinterpret_cast<const uint32_t*>(sy1)[c * NW + i];
-    }
+    lds_words<NW>(sy0, c, yw[0]);
+    lds_words<NW>(sy1, c, yw[1]);
     if constexpr (UVB >= 4) {
-#pragma unroll
-      for (int i = 0; i < UVW; ++i) {
-        uw[i] = reinterpret_cast<const uint32_t*>(su)[c * UVW + i];
-        if constexpr (FMT == B2_SRC_I420) vw[i] = reinterpret_cast<const uint32_t*>(sv)[c * UVW + i];
-      }
+      lds_words<UVW>(su, c, uw);
+      if constexpr (FMT == B2_SRC_I420) lds_words<UVW>(sv, c, vw);
     } else {  // fp32 output from I420: two chroma bytes per plane and chunk
       uw[0] = reinterpret_cast<const uint16_t*>(su)[c];
       vw[0] = reinterpret_cast<const uint16_t*>(sv)[c];
