@@ -568,34 +568,37 @@ def run_aux_workload(args) -> None:
         results["checksum_kernel"] = {"ms": ms, "bytes": b, "gb_per_s": b / ms / 1e6,
                                       "frac": b / ms / 1e6 / peak,
                                       "what": "64 x 1080p RGB frames (read only)"}
-        # 3. unaligned rows: width 1918 (not a multiple of 16) takes the realigning rows kernel
+        # 3. unaligned rows: width 1918 (not a multiple of 16) takes the window kernel; the same
+        #    batch written to an odd address takes the general shift kernel
         wq = 1918
         srcq = [torch.randint(16, 236, (n, h2, wq), dtype=torch.uint8, device=dev)
                 for _ in range(2)]
-        dstq = torch.empty((n, h, wq, 3), dtype=torch.uint8, device=dev)
-        calls = []
-        for s in srcq:
-            a = _lib.DenseArgs()
-            a.struct_size = ctypes.sizeof(_lib.DenseArgs)
-            a.device, a.y, a.u = 0, s.data_ptr(), s.data_ptr() + h * wq
-            a.y_pitch = a.uv_pitch = wq
-            a.y_frame_stride = a.uv_frame_stride = h2 * wq
-            a.src_format, a.width, a.height, a.num_frames = _lib.NV12, wq, h, n
-            a.matrix_coeff, a.dst = 1, dstq.data_ptr()
-            a.layout, a.dtype, a.order = _lib.NHWC, _lib.U8, _lib.RGB
-            a.scale = (ctypes.c_float * 3)(1, 1, 1)
-            calls.append(a)
-        stream.synchronize()
-
-        def quad():
-            i[0] += 1
-            _lib.check(L.b2_convert_dense(ctypes.byref(calls[i[0] % 2]), stream.cuda_stream))
-
-        ms = timed(quad)
+        dstq = torch.empty((n * h * wq * 3 + 16,), dtype=torch.uint8, device=dev)
         b = n * h * wq * 9 // 2
-        results["dense_rows_kernel"] = {"ms": ms, "bytes": b, "gb_per_s": b / ms / 1e6,
-                                        "frac": b / ms / 1e6 / peak,
-                                        "what": "64 x 1918x1080 NV12 -> NHWC u8 (unaligned width)"}
+        for name, off, what in (
+                ("dense_window_kernel", 0, "64 x 1918x1080 NV12 -> NHWC u8 (unaligned width)"),
+                ("dense_shift_kernel", 1, "the same batch written to an odd address")):
+            calls = []
+            for s in srcq:
+                a = _lib.DenseArgs()
+                a.struct_size = ctypes.sizeof(_lib.DenseArgs)
+                a.device, a.y, a.u = 0, s.data_ptr(), s.data_ptr() + h * wq
+                a.y_pitch = a.uv_pitch = wq
+                a.y_frame_stride = a.uv_frame_stride = h2 * wq
+                a.src_format, a.width, a.height, a.num_frames = _lib.NV12, wq, h, n
+                a.matrix_coeff, a.dst = 1, dstq.data_ptr() + off
+                a.layout, a.dtype, a.order = _lib.NHWC, _lib.U8, _lib.RGB
+                a.scale = (ctypes.c_float * 3)(1, 1, 1)
+                calls.append(a)
+            stream.synchronize()
+
+            def unaligned(calls=calls):
+                i[0] += 1
+                _lib.check(L.b2_convert_dense(ctypes.byref(calls[i[0] % 2]), stream.cuda_stream))
+
+            ms = timed(unaligned)
+            results[name] = {"ms": ms, "bytes": b, "gb_per_s": b / ms / 1e6,
+                             "frac": b / ms / 1e6 / peak, "what": what}
     print(json.dumps({"workload": "aux", "steps": K, "warmup": Wm, "peak_gb_per_s": peak,
                       "kernels": results}), flush=True)
 

@@ -9,11 +9,12 @@
 //                      instruction).  Interleaved output (48 bytes per thread per row) is staged
 //                      in shared memory by the warp and leaves as one bulk asynchronous copy
 //                      (cp.async.bulk shared->global) per row segment.
-//   dense_rows_kernel  rows on arbitrary byte boundaries (a pointer, pitch or width that breaks
-//                      the vector path's alignment): one CTA per row pair realigns the rows
-//                      through shared memory and runs the same packed arithmetic from there.
-//   dense_quad_kernel  the last resort: one thread per 2x2 quad with byte accesses (widths under
-//                      16, rows too wide for shared memory).
+//   dense_window_kernel rows that start on arbitrary (even) byte boundaries, e.g. packed frames
+//                      whose width is not a multiple of 16: one row per thread, the chunk grid of
+//                      each row slid so that the OUTPUT accesses stay 16-byte aligned, the input
+//                      realigned with 4-byte loads and funnel shifts.
+//   dense_shift_kernel the general case (odd addresses and pitches, any width): 4-byte accesses
+//                      on both sides, output realigned through shared memory.
 //
 // The kernels are HBM-bound: 1.5 bytes read and 3*sizeof(T) written per pixel.
 #include "b2_common.cuh"
@@ -263,14 +264,15 @@ __global__ void __launch_bounds__(kDenseThreads, kDenseMinBlocks) dense_vec_kern
   }
 }
 
-// One thread's block of 2 rows x PX pixels: luma words yw, chroma words uw (and vw for I420) in,
-// 48 bytes per row out, already in destination order (interleaved: linear; planar: 16 bytes per
+// One thread's block of ROWS (1 or 2) rows x PX pixels under one chroma row: luma words yw,
+// chroma words uw (and vw for I420) in, 48 bytes per row out, already in destination order (interleaved: linear; planar: 16 bytes per
 // output slot).  The same arithmetic as the vector kernel's inner loop.
-template <int FMT, int LAYOUT, int DTYPE, bool BGR, int NW, int UVW>
+template <int FMT, int LAYOUT, int DTYPE, bool BGR, int NW, int UVW, int ROWS>
 __device__ __forceinline__ void convert_chunk(const ColorMat& m, const ScaleBias& sb,
-                                              const uint32_t (&yw)[2][NW],
+                                              const uint32_t (&yw)[ROWS][NW],
                                               const uint32_t (&uw)[UVW],
-                                              const uint32_t (&vw)[UVW], uint32_t (&out)[2][12]) {
+                                              const uint32_t (&vw)[UVW],
+                                              uint32_t (&out)[ROWS][12]) {
 #pragma unroll
   for (int j = 0; j < NW; ++j) {
     Chroma2 c;
@@ -283,7 +285,7 @@ __device__ __forceinline__ void convert_chunk(const ColorMat& m, const ScaleBias
                      make_float2(biased_byte(vw[w], b), biased_byte(vw[w], b + 1)));
     }
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
+    for (int r = 0; r < ROWS; ++r) {
       float ch[3][4];
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
@@ -344,119 +346,233 @@ __device__ __forceinline__ void convert_chunk(const ColorMat& m, const ScaleBias
   }
 }
 
-// ---- rows path: any alignment, vector arithmetic ------------------------------------------------
-// Packed batches whose width is not a multiple of 16 (854x480 video, odd crops) have rows that
-// start on arbitrary byte boundaries, which rules out the vector kernel's direct 16-byte
-// accesses.  Here one CTA owns a row pair of one frame: it copies the source rows into shared
-// memory with aligned 16-byte global loads, shifting bytes into place with funnel shifts, runs
-// the same packed arithmetic out of shared memory, assembles the output rows in shared memory
-// and writes them with aligned 16-byte global stores (plus a few byte stores at the ragged ends).
+// ---- window path: rows on even byte boundaries -----------------------------------------------------
+// Packed batches whose width is not a multiple of 16 (854x480 video, crops) have rows that start
+// anywhere, which rules out the vector kernel's direct 16-byte accesses.  Here a thread owns PX
+// pixels of ONE row, and the chunk grid of every row is slid left by d pixels, d chosen per row
+// so that chunk boundaries fall on 16-byte boundaries of the DESTINATION row.  The output side is
+// then that of the vector kernel (16-byte stores, bulk copies for interleaved output; only the
+// first and last chunk of a row are ragged), and the alignment work moves to the source side,
+// where it is cheap: the 4-byte words that cover the chunk, funnel-shifted.  d must be even so
+// that a chunk starts on a chroma pair, which holds when the destination rows start on even
+// element pairs; rows 2r and 2r+1 get different d, so each thread loads its own chroma.
 
-// smem[0..n) = g[0..n) for any alignment of g.  Reads whole aligned 16-byte segments (each holds
-// at least one valid byte, so it lies inside the allocation); writes whole 16-byte vectors, i.e.
-// up to 15 bytes of padding past n.
-__device__ __forceinline__ void rows_load(unsigned char* s, const uint8_t* g, int n, int tid,
-                                          int nthreads) {
-  const int a = (int)((uintptr_t)g & 15);
-  const uint4* gv = reinterpret_cast<const uint4*>(g - a);
-  const int nsrc = (a + n + 15) >> 4, ndst = (n + 15) >> 4;
-  const int ws = a >> 2, bs = (a & 3) * 8;
-  for (int k = tid; k < ndst; k += nthreads) {
-    const uint4 lo = __ldg(gv + k);
-    const uint4 hi = k + 1 < nsrc ? __ldg(gv + k + 1) : make_uint4(0u, 0u, 0u, 0u);
-    uint32_t w0, w1, w2, w3, w4;  // five consecutive source words starting at word `ws`
-    switch (ws) {
-      case 0: w0 = lo.x; w1 = lo.y; w2 = lo.z; w3 = lo.w; w4 = hi.x; break;
-      case 1: w0 = lo.y; w1 = lo.z; w2 = lo.w; w3 = hi.x; w4 = hi.y; break;
-      case 2: w0 = lo.z; w1 = lo.w; w2 = hi.x; w3 = hi.y; w4 = hi.z; break;
-      default: w0 = lo.w; w1 = hi.x; w2 = hi.y; w3 = hi.z; w4 = hi.w; break;
-    }
-    reinterpret_cast<uint4*>(s)[k] =
-        make_uint4(__funnelshift_r(w0, w1, bs), __funnelshift_r(w1, w2, bs),
-                   __funnelshift_r(w2, w3, bs), __funnelshift_r(w3, w4, bs));
-  }
-}
-
-// g[0..n) = smem[0..n) for any alignment of g; `s` is 16-byte aligned and readable up to
-// n + 16 bytes.  Aligned 16-byte stores for the body, byte stores for the ragged head and tail.
-__device__ __forceinline__ void rows_store(uint8_t* g, const unsigned char* s, int n, int tid,
-                                           int nthreads) {
-  int head = (int)((16 - ((uintptr_t)g & 15)) & 15);
-  if (head > n) head = n;
-  const int nvec = (n - head) >> 4;
-  const int tail0 = head + (nvec << 4);
-  for (int i = tid; i < head; i += nthreads) g[i] = s[i];
-  for (int i = tail0 + tid; i < n; i += nthreads) g[i] = s[i];
-  // two aligned 16-byte shared loads per vector (conflict-free), then the same word select and
-  // byte shift as on the load side
-  const uint4* sv = reinterpret_cast<const uint4*>(s);
-  const int ws = head >> 2, bs = (head & 3) * 8;
-  uint4* gv = reinterpret_cast<uint4*>(g + head);
-  for (int k = tid; k < nvec; k += nthreads) {
-    const uint4 lo = sv[k], hi = sv[k + 1];
-    uint32_t w0, w1, w2, w3, w4;
-    switch (ws) {
-      case 0: w0 = lo.x; w1 = lo.y; w2 = lo.z; w3 = lo.w; w4 = hi.x; break;
-      case 1: w0 = lo.y; w1 = lo.z; w2 = lo.w; w3 = hi.x; w4 = hi.y; break;
-      case 2: w0 = lo.z; w1 = lo.w; w2 = hi.x; w3 = hi.y; w4 = hi.z; break;
-      default: w0 = lo.w; w1 = hi.x; w2 = hi.y; w3 = hi.z; w4 = hi.w; break;
-    }
-    __stcs(gv + k, make_uint4(__funnelshift_r(w0, w1, bs), __funnelshift_r(w1, w2, bs),
-                              __funnelshift_r(w2, w3, bs), __funnelshift_r(w3, w4, bs)));
-  }
-}
-
-// One aligned shared load of NW 32-bit words.
-template <int NW>
-__device__ __forceinline__ void lds_words(const unsigned char* s, int index, uint32_t (&w)[NW]) {
-  if constexpr (NW == 4) {
-    const uint4 q = reinterpret_cast<const uint4*>(s)[index];
-    w[0] = q.x; w[1] = q.y; w[2] = q.z; w[3] = q.w;
-  } else if constexpr (NW == 2) {
-    const uint2 q = reinterpret_cast<const uint2*>(s)[index];
-    w[0] = q.x; w[1] = q.y;
+// w = row[x .. x+NB) for any alignment; bytes outside [0, limit) of the row are not needed and
+// only aligned words that hold at least one byte of the row are read.
+template <int NB>
+__device__ __forceinline__ void load_window(const uint8_t* row, int x, int limit, uint32_t* w) {
+  constexpr int NWD = (NB + 3) / 4;
+  const uint8_t* p = row + x;
+  const int a = (int)((uintptr_t)p & 3);
+  const uint32_t* q = reinterpret_cast<const uint32_t*>(p - a);
+  const int t = x - a;  // row index of the first byte of q[0]
+  uint32_t v[NWD + 1];
+  if (t >= 0 && t + 4 * (NWD + 1) <= limit) {
+#pragma unroll
+    for (int i = 0; i <= NWD; ++i) v[i] = __ldg(q + i);
   } else {
-    w[0] = reinterpret_cast<const uint32_t*>(s)[index];
+#pragma unroll
+    for (int i = 0; i <= NWD; ++i) {
+      const int b = t + 4 * i;
+      v[i] = (b + 3 >= 0 && b < limit) ? __ldg(q + i) : 0u;
+    }
   }
+#pragma unroll
+  for (int i = 0; i < NWD; ++i) w[i] = __funnelshift_r(v[i], v[i + 1], a * 8);
 }
 
-constexpr int kRowsThreads = 128;
-
-// Shared-memory plan of the rows kernel for a frame width, per row pair.
-struct RowsPlan {
-  int in_row;    // bytes reserved per staged source row
-  int out_row;   // bytes reserved per assembled output row (NHWC) or plane row (NCHW)
-  int total;
-};
-template <int LAYOUT, int DTYPE>
-__host__ __device__ inline RowsPlan rows_plan(int width) {
-  constexpr int esz = DTYPE == B2_U8 ? 1 : (DTYPE == B2_F32 ? 4 : 2);
-  constexpr int px = 16 / esz;
-  const int chunks = (width + px - 1) / px;
-  RowsPlan r;
-  r.in_row = ((width + 15) & ~15) + 32;
-  r.out_row = LAYOUT == B2_NHWC ? chunks * 48 + 32 : chunks * 16 + 32;
-  r.total = 4 * r.in_row + 2 * (LAYOUT == B2_NHWC ? 1 : 3) * r.out_row;
-  return r;
-}
+constexpr int kWindowThreads = 128;
 
 template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE>
-__global__ void __launch_bounds__(kRowsThreads) dense_rows_kernel(const DenseParams p) {
+__global__ void __launch_bounds__(kWindowThreads) dense_window_kernel(const DenseParams p) {
   using T = typename OutT<DTYPE>::type;
-  constexpr int PX = 16 / (int)sizeof(T);
+  constexpr int ESZ = (int)sizeof(T);
+  constexpr int PX = 16 / ESZ;
   constexpr int NW = PX / 4;
   constexpr int UVB = FMT == B2_SRC_NV12 ? PX : PX / 2;
   constexpr int UVW = (UVB + 3) / 4;
-  extern __shared__ __align__(128) unsigned char rows_smem[];
-  const RowsPlan plan = rows_plan<LAYOUT, DTYPE>(p.width);
-  unsigned char* sy0 = rows_smem;
-  unsigned char* sy1 = sy0 + plan.in_row;
-  unsigned char* su = sy1 + plan.in_row;
-  unsigned char* sv = su + plan.in_row;
-  unsigned char* so = sv + plan.in_row;  // [2][kOutRows][out_row]
+  extern __shared__ __align__(128) unsigned char window_smem[];  // interleaved: 1536 B per warp
+  const int lane = threadIdx.x & 31;
 
-  const int rp = blockIdx.x, n = blockIdx.y, tid = threadIdx.x;
+  const int row = blockIdx.y, n = blockIdx.z;
   const int we = p.width & ~1;  // a trailing odd column is left untouched
+  uint8_t* grow = reinterpret_cast<uint8_t*>(static_cast<T*>(p.dst) + (long long)n * p.dst_frame_stride +
+                                             (long long)row * p.dst_row_pitch);
+  // pixels to slide the chunk grid left so that chunks start on 16-byte boundaries of this row
+  const int a = (int)((uintptr_t)grow & 15);
+  int d;
+  if constexpr (LAYOUT == B2_NCHW) d = (a / ESZ) & (PX - 1);                // ESZ*d = a (mod 16)
+  else if constexpr (DTYPE == B2_U8) d = (11 * a) & 15;                      // 3d = a (mod 16)
+  else if constexpr (DTYPE == B2_BF16) d = (3 * (a >> 1)) & 7;               // 6d = a (mod 16)
+  else d = (3 * (a >> 2)) & 3;                                               // 12d = a (mod 16)
+  const int cx = blockIdx.x * blockDim.x + threadIdx.x;
+  const int x0 = cx * PX - d, wx0 = (cx - lane) * PX - d;
+  if (wx0 >= we) return;  // the whole warp lies past the row end
+
+  uint32_t out[1][12];
+  if (x0 < we) {
+    const uint8_t *yb, *ub, *vb = nullptr;
+    if constexpr (TABLE) {
+      yb = static_cast<const uint8_t*>(p.y_table[n]);
+      ub = static_cast<const uint8_t*>(p.u_table[n]);
+      if constexpr (FMT == B2_SRC_I420) vb = static_cast<const uint8_t*>(p.v_table[n]);
+    } else {
+      yb = p.y + (long long)n * p.y_frame_stride;
+      ub = p.u + (long long)n * p.uv_frame_stride;
+      if constexpr (FMT == B2_SRC_I420) vb = p.v + (long long)n * p.uv_frame_stride;
+    }
+    uint32_t yw[1][NW], uw[UVW], vw[UVW];
+    load_window<PX>(yb + (size_t)row * (unsigned)p.y_pitch, x0, we, yw[0]);
+    const size_t uv_off = (size_t)(row >> 1) * (unsigned)p.uv_pitch;
+    if constexpr (FMT == B2_SRC_NV12) {
+      load_window<UVB>(ub + uv_off, x0, we, uw);
+    } else {
+      load_window<UVB>(ub + uv_off, x0 / 2, we / 2, uw);
+      load_window<UVB>(vb + uv_off, x0 / 2, we / 2, vw);
+    }
+    (void)vw;
+    convert_chunk<FMT, LAYOUT, DTYPE, BGR>(p.mat, p.sb, yw, uw, vw, out);
+  }
+
+  if constexpr (LAYOUT == B2_NCHW) {
+    if (x0 >= we) return;
+    if (x0 >= 0 && x0 + PX <= we) {
+#pragma unroll
+      for (int s = 0; s < 3; ++s)
+        __stcs(reinterpret_cast<uint4*>(grow + (s * p.dst_plane_stride + x0) * (long long)ESZ),
+               make_uint4(out[0][4 * s], out[0][4 * s + 1], out[0][4 * s + 2], out[0][4 * s + 3]));
+    } else {  // first or last chunk of the row: element by element
+#pragma unroll
+      for (int s = 0; s < 3; ++s) {
+        T* q = reinterpret_cast<T*>(grow) + s * p.dst_plane_stride + x0;
+#pragma unroll
+        for (int k = 0; k < PX; ++k) {
+          if (x0 + k < 0 || x0 + k >= we) continue;
+          const uint32_t word = out[0][4 * s + k * ESZ / 4];
+          if constexpr (ESZ == 1) reinterpret_cast<uint8_t*>(q)[k] = (uint8_t)(word >> (8 * (k & 3)));
+          else if constexpr (ESZ == 2)
+            reinterpret_cast<uint16_t*>(q)[k] = (uint16_t)(word >> (16 * (k & 1)));
+          else reinterpret_cast<uint32_t*>(q)[k] = word;
+        }
+      }
+    }
+  } else {
+    unsigned char* seg = window_smem + (threadIdx.x >> 5) * 1536;
+    if (x0 < we) {
+#pragma unroll
+      for (int i = 0; i < 3; ++i)
+        *reinterpret_cast<uint4*>(seg + lane * 48 + i * 16) =
+            make_uint4(out[0][4 * i], out[0][4 * i + 1], out[0][4 * i + 2], out[0][4 * i + 3]);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    // The warp's 1536-byte segment starts 16-byte aligned at gseg; bytes [s0, s1) of it lie in
+    // the row.  Whole 16-byte pieces leave as one bulk copy, the ragged ends byte by byte.
+    const long long seg_off = (long long)wx0 * (3 * ESZ);
+    uint8_t* gseg = grow + seg_off;
+    const int s0 = seg_off < 0 ? (int)-seg_off : 0;
+    const long long left = (long long)we * (3 * ESZ) - seg_off;
+    const int s1 = left < 1536 ? (int)left : 1536;
+    const int b0 = (s0 + 15) & ~15, b1 = s1 & ~15;
+    const bool bulk = b1 > b0;
+    const int head_end = bulk ? b0 : s1;
+    if (s0 + lane < head_end) gseg[s0 + lane] = seg[s0 + lane];
+    if (bulk && b1 + lane < s1) gseg[b1 + lane] = seg[b1 + lane];
+    if (lane == 0 && bulk) {
+      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gseg + b0),
+                   "r"(smem_addr(seg + b0)), "r"((uint32_t)(b1 - b0))
+                   : "memory");
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      // the staging buffer must outlive the engine's reads of it
+      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    }
+  }
+}
+
+// ---- shift path: any alignment, no block-wide staging --------------------------------------------
+// For rows on arbitrary byte boundaries.  A warp owns the same 2-row x 32*PX-pixel block as in the
+// vector kernel, but its lanes take the luma words of a row in turn (lane l owns words l, l+32,
+// ...), so every access is a coalesced 4-byte access and a row that starts between two words
+// costs one funnel shift per word, with no dependence on where the row starts.  The output
+// segments of the warp are assembled in shared memory and leave as 4-byte stores shifted the
+// other way, with byte stores at the ragged ends.  Needs only __syncwarp.
+
+// The 32-bit word at any address p (its first byte is valid; bytes at or past `end` are not
+// needed).  Reads only aligned words that hold at least one valid byte.
+__device__ __forceinline__ uint32_t ldg_word_any(const uint8_t* p, const uint8_t* end) {
+  const int a = (int)((uintptr_t)p & 3);
+  const uint8_t* base = p - a;
+  const uint32_t lo = __ldg(reinterpret_cast<const uint32_t*>(base));
+  uint32_t hi = 0u;
+  if (a != 0 && base + 4 < end) hi = __ldg(reinterpret_cast<const uint32_t*>(base + 4));
+  return __funnelshift_r(lo, hi, a * 8);
+}
+
+template <int N>
+__device__ __forceinline__ void sts_words(unsigned char* q, const uint32_t* w) {
+  if constexpr (N % 4 == 0) {
+#pragma unroll
+    for (int i = 0; i < N; i += 4)
+      *reinterpret_cast<uint4*>(q + 4 * i) = make_uint4(w[i], w[i + 1], w[i + 2], w[i + 3]);
+  } else if constexpr (N % 2 == 0) {
+#pragma unroll
+    for (int i = 0; i < N; i += 2) *reinterpret_cast<uint2*>(q + 4 * i) = make_uint2(w[i], w[i + 1]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) *reinterpret_cast<uint32_t*>(q + 4 * i) = w[i];
+  }
+}
+
+// g[0..n) = s[0..n) by one warp for any alignment of g; s is 4-byte aligned shared memory,
+// readable up to n + 4 bytes; n <= MAXB.
+template <int MAXB>
+__device__ __forceinline__ void warp_store(uint8_t* g, const unsigned char* s, int n, int lane) {
+  int head = (int)((4 - ((uintptr_t)g & 3)) & 3);
+  if (head > n) head = n;
+  const int nw = (n - head) >> 2;
+  const int tail0 = head + (nw << 2);
+  if (lane < head) g[lane] = s[lane];
+  if (tail0 + lane < n) g[tail0 + lane] = s[tail0 + lane];
+  const uint32_t* sw = reinterpret_cast<const uint32_t*>(s);
+  uint32_t* gw = reinterpret_cast<uint32_t*>(g + head);
+  const int bs = head * 8;
+  if (bs == 0) {
+#pragma unroll
+    for (int i = 0; i < MAXB / 128; ++i) {
+      const int m = lane + 32 * i;
+      if (m < nw) __stcs(gw + m, sw[m]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < MAXB / 128; ++i) {
+      const int m = lane + 32 * i;
+      if (m < nw) __stcs(gw + m, __funnelshift_r(sw[m], sw[m + 1], bs));
+    }
+  }
+}
+
+constexpr int kShiftThreads = 128;
+constexpr int kShiftWarpSmem = 2 * 1536 + 16;  // two interleaved or six planar row segments
+
+template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE>
+__global__ void __launch_bounds__(kShiftThreads) dense_shift_kernel(const DenseParams p) {
+  using T = typename OutT<DTYPE>::type;
+  constexpr int ESZ = (int)sizeof(T);
+  constexpr int PX = 16 / ESZ;
+  constexpr int NW = PX / 4;
+  constexpr int UVB = FMT == B2_SRC_NV12 ? PX : PX / 2;
+  constexpr int UVW = (UVB + 3) / 4;
+  constexpr int KW = 3 * ESZ;  // interleaved output words per luma word
+  constexpr int CW = ESZ;      // planar output words per channel and luma word
+  extern __shared__ __align__(128) unsigned char shift_smem[];
+  const int lane = threadIdx.x & 31;
+  unsigned char* wsm = shift_smem + (threadIdx.x >> 5) * kShiftWarpSmem;
+
+  const int rp = blockIdx.y, n = blockIdx.z;
+  const int we = p.width & ~1;  // a trailing odd column is left untouched
+  const int wx0 = (blockIdx.x * (kShiftThreads / 32) + (threadIdx.x >> 5)) * 32 * PX;
+  if (wx0 >= we) return;  // the whole warp lies past the row end
+
   const uint8_t *yb, *ub, *vb = nullptr;
   if constexpr (TABLE) {
     yb = static_cast<const uint8_t*>(p.y_table[n]);
@@ -467,109 +583,78 @@ __global__ void __launch_bounds__(kRowsThreads) dense_rows_kernel(const DensePar
     ub = p.u + (long long)n * p.uv_frame_stride;
     if constexpr (FMT == B2_SRC_I420) vb = p.v + (long long)n * p.uv_frame_stride;
   }
-  rows_load(sy0, yb + (size_t)(2 * rp) * (unsigned)p.y_pitch, we, tid, kRowsThreads);
-  rows_load(sy1, yb + (size_t)(2 * rp + 1) * (unsigned)p.y_pitch, we, tid, kRowsThreads);
-  rows_load(su, ub + (size_t)rp * (unsigned)p.uv_pitch, FMT == B2_SRC_NV12 ? we : we / 2, tid,
-            kRowsThreads);
-  if constexpr (FMT == B2_SRC_I420)
-    rows_load(sv, vb + (size_t)rp * (unsigned)p.uv_pitch, we / 2, tid, kRowsThreads);
-  __syncthreads();
+  const uint8_t* y0 = yb + (size_t)(2 * rp) * (unsigned)p.y_pitch;
+  const uint8_t* y1 = y0 + p.y_pitch;
+  const uint8_t* u0 = ub + (size_t)rp * (unsigned)p.uv_pitch;
+  const uint8_t* v0 = FMT == B2_SRC_I420 ? vb + (size_t)rp * (unsigned)p.uv_pitch : nullptr;
 
-  const ColorMat& m = p.mat;
-  const int chunks = (we + PX - 1) / PX;
-  for (int c = tid; c < chunks; c += kRowsThreads) {
-    uint32_t yw[2][NW], uw[UVW], vw[UVW];
-    lds_words<NW>(sy0, c, yw[0]);
-    lds_words<NW>(sy1, c, yw[1]);
-    if constexpr (UVB >= 4) {
-      lds_words<UVW>(su, c, uw);
-      if constexpr (FMT == B2_SRC_I420) lds_words<UVW>(sv, c, vw);
-    } else {  // fp32 output from I420: two chroma bytes per plane and chunk
-      uw[0] = reinterpret_cast<const uint16_t*>(su)[c];
-      vw[0] = reinterpret_cast<const uint16_t*>(sv)[c];
-    }
-    (void)vw;
-    uint32_t out[2][12];
-    convert_chunk<FMT, LAYOUT, DTYPE, BGR>(m, p.sb, yw, uw, vw, out);
+  uint32_t yw[2][NW], uw[UVW], vw[UVW];
 #pragma unroll
-    for (int r = 0; r < 2; ++r)
+  for (int i = 0; i < UVW; ++i) uw[i] = vw[i] = 0u;
 #pragma unroll
-      for (int i = 0; i < 3; ++i) {
-        unsigned char* q = LAYOUT == B2_NHWC ? so + (size_t)r * plan.out_row + c * 48 + i * 16
-                                             : so + (size_t)(r * 3 + i) * plan.out_row + c * 16;
-        *reinterpret_cast<uint4*>(q) =
-            make_uint4(out[r][4 * i], out[r][4 * i + 1], out[r][4 * i + 2], out[r][4 * i + 3]);
+  for (int j = 0; j < NW; ++j) {
+    const int x = wx0 + 4 * (lane + 32 * j);  // first pixel of this lane's luma word j
+    yw[0][j] = yw[1][j] = 0u;
+    if (x < we) {
+      yw[0][j] = ldg_word_any(y0 + x, y0 + we);
+      yw[1][j] = ldg_word_any(y1 + x, y1 + we);
+      if constexpr (FMT == B2_SRC_NV12) {
+        uw[j] = ldg_word_any(u0 + x, u0 + we);
+      } else {  // two bytes per plane under four pixels
+        uw[j >> 1] |= (ldg_word_any(u0 + x / 2, u0 + we / 2) & 0xffffu) << (16 * (j & 1));
+        vw[j >> 1] |= (ldg_word_any(v0 + x / 2, v0 + we / 2) & 0xffffu) << (16 * (j & 1));
       }
+    }
   }
-  __syncthreads();
+  (void)vw;
+  uint32_t out[2][12];
+  convert_chunk<FMT, LAYOUT, DTYPE, BGR>(p.mat, p.sb, yw, uw, vw, out);
+#pragma unroll
+  for (int r = 0; r < 2; ++r)
+#pragma unroll
+    for (int j = 0; j < NW; ++j) {
+      const int word = lane + 32 * j;
+      if constexpr (LAYOUT == B2_NHWC) {
+        sts_words<KW>(wsm + r * 1536 + word * (KW * 4), &out[r][KW * j]);
+      } else {
+#pragma unroll
+        for (int s = 0; s < 3; ++s)
+          sts_words<CW>(wsm + (r * 3 + s) * 512 + word * (CW * 4), &out[r][4 * s + CW * j]);
+      }
+    }
+  __syncwarp();
 
+  const int px = we - wx0 < 32 * PX ? we - wx0 : 32 * PX;
   uint8_t* dst = reinterpret_cast<uint8_t*>(static_cast<T*>(p.dst) + (long long)n * p.dst_frame_stride);
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     const long long row = 2 * rp + r;
     if constexpr (LAYOUT == B2_NHWC) {
-      rows_store(dst + row * p.dst_row_pitch * (long long)sizeof(T), so + (size_t)r * plan.out_row,
-                 we * 3 * (int)sizeof(T), tid, kRowsThreads);
+      warp_store<1536>(dst + (row * p.dst_row_pitch + (long long)wx0 * 3) * ESZ, wsm + r * 1536,
+                       px * 3 * ESZ, lane);
     } else {
 #pragma unroll
       for (int s = 0; s < 3; ++s)
-        rows_store(dst + (s * p.dst_plane_stride + row * p.dst_row_pitch) * (long long)sizeof(T),
-                   so + (size_t)(r * 3 + s) * plan.out_row, we * (int)sizeof(T), tid, kRowsThreads);
+        warp_store<512>(dst + (s * p.dst_plane_stride + row * p.dst_row_pitch + wx0) * ESZ,
+                        wsm + (r * 3 + s) * 512, px * ESZ, lane);
     }
   }
 }
 
-// Any-shape path: one thread per 2x2 quad (color_conversion.cu:98-137 has the same ownership).
-template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE>
-__global__ void __launch_bounds__(256) dense_quad_kernel(const DenseParams p) {
-  using T = typename OutT<DTYPE>::type;
-  const int x = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
-  const int y = (blockIdx.y * blockDim.y + threadIdx.y) * 2;
-  const int n = blockIdx.z;
-  if (x + 1 >= p.width || y + 1 >= p.height) return;
-  const uint8_t *yb, *ub, *vb = nullptr;
-  if constexpr (TABLE) {
-    yb = static_cast<const uint8_t*>(p.y_table[n]);
-    ub = static_cast<const uint8_t*>(p.u_table[n]);
-    if constexpr (FMT == B2_SRC_I420) vb = static_cast<const uint8_t*>(p.v_table[n]);
-  } else {
-    yb = p.y + (long long)n * p.y_frame_stride;
-    ub = p.u + (long long)n * p.uv_frame_stride;
-    if constexpr (FMT == B2_SRC_I420) vb = p.v + (long long)n * p.uv_frame_stride;
-  }
-  int cu, cv;
-  if constexpr (FMT == B2_SRC_NV12) {
-    const uint8_t* q = ub + (long long)(y >> 1) * p.uv_pitch + x;
-    cu = q[0];
-    cv = q[1];
-  } else {
-    cu = ub[(long long)(y >> 1) * p.uv_pitch + (x >> 1)];
-    cv = vb[(long long)(y >> 1) * p.uv_pitch + (x >> 1)];
-  }
-  T* dst = static_cast<T*>(p.dst) + (long long)n * p.dst_frame_stride;
-#pragma unroll
-  for (int r = 0; r < 2; ++r)
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      int c[3];
-      pixel_u8(p.mat, yb[(long long)(y + r) * p.y_pitch + x + k], cu, cv, c[BGR ? 2 : 0], c[1],
-               c[BGR ? 0 : 2]);
-#pragma unroll
-      for (int s = 0; s < 3; ++s) {
-        const long long idx =
-            LAYOUT == B2_NCHW
-                ? s * p.dst_plane_stride + (long long)(y + r) * p.dst_row_pitch + x + k
-                : (long long)(y + r) * p.dst_row_pitch + (long long)(x + k) * 3 + s;
-        dst[idx] = finish<T>((float)c[s], p.sb.s[s], p.sb.b[s]);
-      }
-    }
-}
+inline bool mult(long long v, long long m) { return v % m == 0; }
 
 template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE>
 int launch_t(const DenseLaunch& L, const DenseParams& p, bool vec, cudaStream_t stream) {
   using T = typename OutT<DTYPE>::type;
   constexpr int PX = 16 / (int)sizeof(T);
   const int He = L.height & ~1;
+  // The window kernel needs destination rows that start on even element pairs (so that its chunk
+  // grid starts on a chroma pair) and, for planar output, planes that are equally aligned.
+  constexpr int kPair = 2 * (int)sizeof(T);
+  bool window = mult((long long)(uintptr_t)p.dst, kPair) &&
+                mult((long long)p.dst_row_pitch * (long long)sizeof(T), kPair) &&
+                mult(p.dst_frame_stride * (long long)sizeof(T), kPair);
+  if (LAYOUT == B2_NCHW) window = window && mult(p.dst_plane_stride * (long long)sizeof(T), 16);
   // gridDim.z is limited to 65535 frames per launch
   for (int n0 = 0; n0 < L.num_frames; n0 += 65535) {
     const int nn = L.num_frames - n0 < 65535 ? L.num_frames - n0 : 65535;
@@ -592,19 +677,18 @@ int launch_t(const DenseLaunch& L, const DenseParams& p, bool vec, cudaStream_t 
       dim3 block(bx, by), grid((chunks + bx - 1) / bx, (He / 2 + by - 1) / by, nn);
       const size_t smem = LAYOUT == B2_NHWC ? (size_t)(kDenseThreads / 32) * 2 * 32 * 48 : 0;
       dense_vec_kernel<FMT, LAYOUT, DTYPE, BGR, TABLE><<<grid, block, smem, stream>>>(q);
-    } else if (rows_plan<LAYOUT, DTYPE>(L.width).total <= 200 * 1024 && L.width >= 16) {
-      // unaligned rows: realign through shared memory, one CTA per row pair
+    } else if (window) {
       if (He < 2) continue;
-      auto kern = dense_rows_kernel<FMT, LAYOUT, DTYPE, BGR, TABLE>;
-      const int smem = rows_plan<LAYOUT, DTYPE>(L.width).total;
-      if (smem > 48 * 1024)
-        B2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
-                "raising the shared-memory limit of the rows kernel failed");
-      kern<<<dim3(He / 2, nn), kRowsThreads, smem, stream>>>(q);
+      const int chunks = ((L.width & ~1) + 2 * PX - 2) / PX;  // the grid slides by up to PX-1 pixels
+      dim3 grid((chunks + kWindowThreads - 1) / kWindowThreads, He, nn);
+      const size_t smem = LAYOUT == B2_NHWC ? (size_t)(kWindowThreads / 32) * 1536 : 0;
+      dense_window_kernel<FMT, LAYOUT, DTYPE, BGR, TABLE><<<grid, kWindowThreads, smem, stream>>>(q);
     } else {
-      dim3 block(32, 8), grid((L.width / 2 + 31) / 32, (He / 2 + 7) / 8, nn);
-      if (grid.x == 0 || grid.y == 0) continue;
-      dense_quad_kernel<FMT, LAYOUT, DTYPE, BGR, TABLE><<<grid, block, 0, stream>>>(q);
+      if (He < 2) continue;
+      const int per_cta = kShiftThreads * PX;  // pixels of a row per CTA
+      dim3 grid(((L.width & ~1) + per_cta - 1) / per_cta, He / 2, nn);
+      dense_shift_kernel<FMT, LAYOUT, DTYPE, BGR, TABLE>
+          <<<grid, kShiftThreads, (kShiftThreads / 32) * kShiftWarpSmem, stream>>>(q);
     }
     B2_CUDA(cudaPeekAtLastError(), "launch of the dense conversion kernel failed");
   }
@@ -627,8 +711,6 @@ int launch_fl(const DenseLaunch& L, const DenseParams& p, bool vec, cudaStream_t
     default: return launch_fld<FMT, LAYOUT, B2_BF16>(L, p, vec, s);
   }
 }
-
-inline bool mult(long long v, long long m) { return v % m == 0; }
 
 }  // namespace
 
