@@ -1,5 +1,5 @@
 """Frames whose rows start on arbitrary byte boundaries (widths that are not a multiple of 16):
-the realigning rows kernel against the oracle, at real-world sizes."""
+the window and shift kernels against the oracle, at real-world sizes."""
 
 import numpy as np
 import pytest
@@ -48,3 +48,68 @@ def test_unaligned_widths(cuda_cfg, w, h, fmt, layout, dtype):
         np.testing.assert_allclose(got, want, rtol=1e-6, atol=1e-6)
     else:
         assert (got.view(np.uint16) == want).all()
+
+
+@pytest.mark.parametrize("w,h", [(31, 6), (854, 10), (1918, 4), (50, 8)])
+@pytest.mark.parametrize("layout", ["NCHW", "NHWC"])
+@pytest.mark.parametrize("dtype", ["uint8", "bfloat16", "float32"])
+@pytest.mark.parametrize("dst_off", [1, 2])
+def test_destination_on_odd_elements(cuda_cfg, w, h, layout, dtype, dst_off):
+    """Through the C ABI with a destination that starts ``dst_off`` elements into its buffer
+    (odd: the general kernel; even but unaligned: the window kernel), odd widths included.  The
+    bytes around the output and the trailing odd column keep their sentinel value."""
+    import ctypes
+
+    import torch
+
+    from spdl_b200 import _lib
+
+    n = 2
+    esz = {"uint8": 1, "bfloat16": 2, "float32": 4}[dtype]
+    tdt = {"uint8": torch.uint8, "bfloat16": torch.int16, "float32": torch.int32}[dtype]
+    nv = synth.nv12_batch(n, w, h, config=9, index=w + dst_off, full_range=True)
+    src = torch.from_numpy(nv).cuda()
+    total = n * 3 * h * w
+    sentinel = {1: 0xA5, 2: 0x5A5A, 4: 0x5A5A5A5A}[esz]
+    buf = torch.full((total + 8,), sentinel, dtype=tdt, device="cuda")
+    a = _lib.DenseArgs()
+    a.struct_size = ctypes.sizeof(_lib.DenseArgs)
+    a.device = cuda_cfg.device_index
+    a.y, a.u = src.data_ptr(), src.data_ptr() + h * w
+    a.y_pitch = a.uv_pitch = w
+    a.y_frame_stride = a.uv_frame_stride = h * 3 // 2 * w
+    a.src_format, a.width, a.height, a.num_frames = _lib.NV12, w, h, n
+    a.matrix_coeff, a.full_range = 6, 1
+    a.dst = buf.data_ptr() + dst_off * esz
+    a.layout = _lib.NCHW if layout == "NCHW" else _lib.NHWC
+    a.dtype = {"uint8": _lib.U8, "bfloat16": _lib.BF16, "float32": _lib.F32}[dtype]
+    a.order = _lib.RGB
+    sb = oracle.scale_bias(MEAN, STD) if dtype != "uint8" else oracle.scale_bias()
+    a.scale = (ctypes.c_float * 3)(*[float(x) for x in sb[:3]])
+    a.bias = (ctypes.c_float * 3)(*[float(x) for x in sb[3:]])
+    stream = torch.cuda.current_stream().cuda_stream
+    _lib.check(_lib.lib().b2_convert_dense(ctypes.byref(a), stream))
+    torch.cuda.synchronize()
+    got = buf.cpu().numpy()
+    want = oracle.convert_dense(
+        nv, nv.reshape(-1)[h * w:], None, width=w, height=h, num_frames=n, y_pitch=w, uv_pitch=w,
+        y_frame_stride=h * 3 // 2 * w, uv_frame_stride=h * 3 // 2 * w, src_format=oracle.NV12,
+        layout=oracle.NCHW if layout == "NCHW" else oracle.NHWC,
+        dtype={"uint8": oracle.U8, "float32": oracle.F32, "bfloat16": oracle.BF16}[dtype],
+        coeff=6, full_range=True, sb=sb)
+    shape = (n, 3, h, w) if layout == "NCHW" else (n, h, w, 3)
+    body = got[dst_off:dst_off + total].reshape(shape)
+    we = w & ~1
+    cols = (slice(None),) * 3 + (slice(0, we),) if layout == "NCHW" else \
+        (slice(None), slice(None), slice(0, we))
+    if dtype == "uint8":
+        assert (body[cols] == want[cols]).all()
+    elif dtype == "bfloat16":
+        assert (body[cols].view(np.uint16) == want[cols]).all()
+    else:
+        np.testing.assert_allclose(body[cols].view(np.float32), want[cols], rtol=1e-6, atol=1e-6)
+    # nothing outside the even-width part of the frames was written
+    assert (got[:dst_off] == sentinel).all() and (got[dst_off + total:] == sentinel).all()
+    if w & 1:
+        tail = body[..., w - 1] if layout == "NCHW" else body[:, :, w - 1, :]
+        assert (tail == sentinel).all()
