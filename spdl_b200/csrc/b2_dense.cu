@@ -54,16 +54,28 @@ __device__ __forceinline__ void load_bytes(const uint8_t* p, uint32_t* w) {
     w[0] = __ldcs(reinterpret_cast<const uint16_t*>(p));
   }
 }
+// w = row[x .. x+NB) for any alignment; bytes outside [0, limit) of the row are not needed and
+// only aligned words that hold at least one byte of the row are read.
 template <int NB>
-__device__ __forceinline__ void load_bytes_any(const uint8_t* p, uint32_t* w, bool aligned) {
-  if (aligned) {
-    load_bytes<NB>(p, w);
+__device__ __forceinline__ void load_window(const uint8_t* row, int x, int limit, uint32_t* w) {
+  constexpr int NWD = (NB + 3) / 4;
+  const uint8_t* p = row + x;
+  const int a = (int)((uintptr_t)p & 3);
+  const uint32_t* q = reinterpret_cast<const uint32_t*>(p - a);
+  const int t = x - a;  // row index of the first byte of q[0]
+  uint32_t v[NWD + 1];
+  if (t >= 0 && t + 4 * (NWD + 1) <= limit) {
+#pragma unroll
+    for (int i = 0; i <= NWD; ++i) v[i] = __ldg(q + i);
   } else {
 #pragma unroll
-    for (int i = 0; i < (NB + 3) / 4; ++i) w[i] = 0;
-#pragma unroll
-    for (int i = 0; i < NB; ++i) w[i >> 2] |= (uint32_t)__ldcs(p + i) << (8 * (i & 3));
+    for (int i = 0; i <= NWD; ++i) {
+      const int b = t + 4 * i;
+      v[i] = (b + 3 >= 0 && b < limit) ? __ldg(q + i) : 0u;
+    }
   }
+#pragma unroll
+  for (int i = 0; i < NWD; ++i) w[i] = __funnelshift_r(v[i], v[i + 1], a * 8);
 }
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
@@ -118,20 +130,20 @@ __global__ void __launch_bounds__(kDenseThreads, kDenseMinBlocks) dense_vec_kern
       if constexpr (FMT == B2_SRC_I420) vb = p.v + (long long)n * p.uv_frame_stride;
     }
     uint32_t yw[2][NW], uw[UVW], vw[UVW];
-    const uint8_t* y0p = yb + (size_t)(2 * rp) * (unsigned)p.y_pitch + x0;
-    const uint8_t* up = ub + (size_t)rp * (unsigned)p.uv_pitch + (FMT == B2_SRC_NV12 ? x0 : x0 / 2);
-    if constexpr (TABLE) {
-      load_bytes_any<PX>(y0p, yw[0], aligned);
-      load_bytes_any<PX>(y0p + p.y_pitch, yw[1], aligned);
-      load_bytes_any<UVB>(up, uw, aligned);
-      if constexpr (FMT == B2_SRC_I420)
-        load_bytes_any<UVB>(vb + (size_t)rp * (unsigned)p.uv_pitch + x0 / 2, vw, aligned);
+    const uint8_t* yrow = yb + (size_t)(2 * rp) * (unsigned)p.y_pitch;
+    const uint8_t* urow = ub + (size_t)rp * (unsigned)p.uv_pitch;
+    const uint8_t* vrow = FMT == B2_SRC_I420 ? vb + (size_t)rp * (unsigned)p.uv_pitch : nullptr;
+    constexpr int CDIV = FMT == B2_SRC_NV12 ? 1 : 2;  // luma columns per chroma byte column
+    if (TABLE && !aligned) {  // surfaces on odd addresses: realign word by word
+      load_window<PX>(yrow, x0, p.width, yw[0]);
+      load_window<PX>(yrow + p.y_pitch, x0, p.width, yw[1]);
+      load_window<UVB>(urow, x0 / CDIV, p.width / CDIV, uw);
+      if constexpr (FMT == B2_SRC_I420) load_window<UVB>(vrow, x0 / CDIV, p.width / CDIV, vw);
     } else {
-      load_bytes<PX>(y0p, yw[0]);
-      load_bytes<PX>(y0p + p.y_pitch, yw[1]);
-      load_bytes<UVB>(up, uw);
-      if constexpr (FMT == B2_SRC_I420)
-        load_bytes<UVB>(vb + (size_t)rp * (unsigned)p.uv_pitch + x0 / 2, vw);
+      load_bytes<PX>(yrow + x0, yw[0]);
+      load_bytes<PX>(yrow + x0 + p.y_pitch, yw[1]);
+      load_bytes<UVB>(urow + x0 / CDIV, uw);
+      if constexpr (FMT == B2_SRC_I420) load_bytes<UVB>(vrow + x0 / CDIV, vw);
     }
     (void)vw;
 
@@ -357,30 +369,6 @@ __device__ __forceinline__ void convert_chunk(const ColorMat& m, const ScaleBias
 // that a chunk starts on a chroma pair, which holds when the destination rows start on even
 // element pairs; rows 2r and 2r+1 get different d, so each thread loads its own chroma.
 
-// w = row[x .. x+NB) for any alignment; bytes outside [0, limit) of the row are not needed and
-// only aligned words that hold at least one byte of the row are read.
-template <int NB>
-__device__ __forceinline__ void load_window(const uint8_t* row, int x, int limit, uint32_t* w) {
-  constexpr int NWD = (NB + 3) / 4;
-  const uint8_t* p = row + x;
-  const int a = (int)((uintptr_t)p & 3);
-  const uint32_t* q = reinterpret_cast<const uint32_t*>(p - a);
-  const int t = x - a;  // row index of the first byte of q[0]
-  uint32_t v[NWD + 1];
-  if (t >= 0 && t + 4 * (NWD + 1) <= limit) {
-#pragma unroll
-    for (int i = 0; i <= NWD; ++i) v[i] = __ldg(q + i);
-  } else {
-#pragma unroll
-    for (int i = 0; i <= NWD; ++i) {
-      const int b = t + 4 * i;
-      v[i] = (b + 3 >= 0 && b < limit) ? __ldg(q + i) : 0u;
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < NWD; ++i) w[i] = __funnelshift_r(v[i], v[i + 1], a * 8);
-}
-
 constexpr int kWindowThreads = 128;
 
 template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE>
@@ -468,17 +456,20 @@ __global__ void __launch_bounds__(kWindowThreads) dense_window_kernel(const Dens
     __syncwarp();
     // The warp's 1536-byte segment starts 16-byte aligned at gseg; bytes [s0, s1) of it lie in
     // the row.  Whole 16-byte pieces leave as one bulk copy, the ragged ends byte by byte.
-    const long long seg_off = (long long)wx0 * (3 * ESZ);
+    const int seg_off = wx0 * (3 * ESZ);  // rows are shorter than 2^31 bytes
     uint8_t* gseg = grow + seg_off;
-    const int s0 = seg_off < 0 ? (int)-seg_off : 0;
-    const long long left = (long long)we * (3 * ESZ) - seg_off;
-    const int s1 = left < 1536 ? (int)left : 1536;
-    const int b0 = (s0 + 15) & ~15, b1 = s1 & ~15;
-    const bool bulk = b1 > b0;
-    const int head_end = bulk ? b0 : s1;
-    if (s0 + lane < head_end) gseg[s0 + lane] = seg[s0 + lane];
-    if (bulk && b1 + lane < s1) gseg[b1 + lane] = seg[b1 + lane];
-    if (lane == 0 && bulk) {
+    const int left = we * (3 * ESZ) - seg_off;
+    int b0 = 0, b1 = 1536;
+    if (seg_off < 0 || left < 1536) {  // first or last segment of the row
+      const int s0 = seg_off < 0 ? -seg_off : 0;
+      const int s1 = left < 1536 ? left : 1536;
+      b0 = (s0 + 15) & ~15;
+      b1 = s1 & ~15;
+      const int head_end = b1 > b0 ? b0 : s1;
+      if (s0 + lane < head_end) gseg[s0 + lane] = seg[s0 + lane];
+      if (b1 > b0 && b1 + lane < s1) gseg[b1 + lane] = seg[b1 + lane];
+    }
+    if (lane == 0 && b1 > b0) {
       asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gseg + b0),
                    "r"(smem_addr(seg + b0)), "r"((uint32_t)(b1 - b0))
                    : "memory");
