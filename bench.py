@@ -552,6 +552,33 @@ def run_aux_workload(args) -> None:
         results["gather_kernel"] = {"ms": ms, "bytes": b, "gb_per_s": b / ms / 1e6,
                                     "frac": b / ms / 1e6 / peak,
                                     "what": "64 x 1080p NV12 surfaces, pitch 2048 -> packed"}
+        # 1b. the same surfaces converted straight through the pointer table (no gather pass)
+        rgb_out = torch.empty((n, h, w, 3), dtype=torch.uint8, device=dev)
+        tcalls = []
+        for c in range(2):
+            ytab = tabs[c][0]
+            utab = ytab + h * pitch
+            a = _lib.DenseArgs()
+            a.struct_size = ctypes.sizeof(_lib.DenseArgs)
+            a.device, a.y_table, a.u_table = 0, ytab.data_ptr(), utab.data_ptr()
+            a.y_pitch = a.uv_pitch = pitch
+            a.src_format, a.width, a.height, a.num_frames = _lib.NV12, w, h, n
+            a.matrix_coeff, a.dst = 1, rgb_out.data_ptr()
+            a.layout, a.dtype, a.order = _lib.NHWC, _lib.U8, _lib.RGB
+            a.scale = (ctypes.c_float * 3)(1, 1, 1)
+            tcalls.append((a, ytab, utab))
+        stream.synchronize()
+
+        def table_convert():
+            i[0] += 1
+            _lib.check(L.b2_convert_dense(ctypes.byref(tcalls[i[0] % 2][0]), stream.cuda_stream))
+
+        ms = timed(table_convert)
+        b = n * h * w * 9 // 2
+        results["dense_vec_kernel_pointer_table"] = {
+            "ms": ms, "bytes": b, "gb_per_s": b / ms / 1e6, "frac": b / ms / 1e6 / peak,
+            "what": "64 x 1080p NV12 surfaces, pitch 2048, through the pointer table -> NHWC u8"}
+        del rgb_out
         # 2. checksum of a 64 x 1080p RGB batch
         rgb = [torch.randint(0, 256, (n, h, w, 3), dtype=torch.uint8, device=dev)
                for _ in range(2)]
