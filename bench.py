@@ -386,6 +386,8 @@ def _tap_bytes(w, h, rw, rh, cx, cy, ow, oh, fmt) -> tuple[int, int]:
         return np.unique(np.concatenate([i0, np.minimum(i0 + 1, n_in - 1)]))
 
     xs, ys = taps(w, rw, cx, ow), taps(h, rh, cy, oh)
+    if fmt in ("rgb24", "rgb_planar"):
+        return 3 * len(xs) * len(ys), 3 * len(ys) * w
     ncx, ncy = len(np.unique(xs // 2)), len(np.unique(ys // 2))
     exact = len(xs) * len(ys) + 2 * ncx * ncy
     rows = len(ys) * w + ncy * (w if fmt == "nv12" else 2 * ((w + 1) // 2))
@@ -393,8 +395,9 @@ def _tap_bytes(w, h, rw, rh, cx, cy, ow, oh, fmt) -> tuple[int, int]:
 
 
 def run_resize_workload(args) -> None:
-    """``--workload c3|c4|c5``: one GPU, kernel-resident timing of the fused resize kernel on the
-    other benchmark configurations, with tap-exact and row-granular roofline figures."""
+    """``--workload c3|c4|c5|j5``: one GPU, kernel-resident timing of the fused resize kernel on
+    the other benchmark configurations (j5: the images of c5 as decoded RGB), with tap-exact and
+    row-granular roofline figures."""
     import torch
 
     import spdl_b200.io as io
@@ -422,6 +425,20 @@ def run_resize_workload(args) -> None:
                     name=f"{n} frames ({n // 16} clips x 16) 1280x720 NV12 -> 256x256 u8 "
                          f"N x T x C x H x W, BT.601")
         copies, nbytes = 2, n * w * h * 3 // 2
+    elif args.workload == "j5":
+        # the sizes of c5, but already decoded to interleaved RGB (what a JPEG decoder emits)
+        n = max(1, int(2048 * scale))
+        r = synth.rng_for(5, 0)
+        ws = (r.integers(128, 513, n) * 2).astype(np.int64)
+        hs = (r.integers(128, 513, n) * 2).astype(np.int64)
+        sizes = 3 * ws * hs
+        offs = np.concatenate([[0], np.cumsum(sizes)[:-1]]).astype(np.int64)
+        descs, out = io.make_image_descs(ws, hs, src_format="rgb24", offsets=offs,
+                                         resize_shorter=256, crop=(224, 224))
+        spec = dict(fmt="rgb24", layout=_lib.NCHW, dtype=_lib.F32, esz=4, coeff=1, full=0, norm=True,
+                    name=f"{n} ragged interleaved RGB images (256..1024) -> shorter side 256, "
+                         f"centre crop 224x224 fp32 NCHW, normalised")
+        copies, nbytes = 2, int(sizes.sum())
     else:
         n = max(1, int(2048 * scale))
         data, ws, hs, offs = synth.ragged_i420(n)
@@ -684,7 +701,7 @@ def main() -> None:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU legs (for profiler captures)")
-    ap.add_argument("--workload", choices=["c2", "c3", "c4", "c5", "aux"], default="c2",
+    ap.add_argument("--workload", choices=["c2", "c3", "c4", "c5", "j5", "aux"], default="c2",
                     help="c2 = the headline dense workload; c3/c4/c5 = fused resize workloads; "
                          "aux = gather, checksum and any-shape kernels (one GPU, informational)")
     ap.add_argument("--scale", default="1.0",
