@@ -397,3 +397,28 @@ def test_zero_sized_calls_are_no_ops(cuda_cfg):
     assert L.b2_gather_surfaces(None, None, 0, 16, 8, None, 0, cuda_cfg.stream) == 0
     assert L.b2_frame_checksum(None, 0, 0, None, 0, cuda_cfg.stream) == 0
     assert L.b2_transfer_h2d(None, None, 0, 1, 0, cuda_cfg.stream) == 0
+
+
+def test_cpu_runnable_config_i420_1080p(cuda_cfg):
+    """The CPU-runnable configuration (1920x1080 yuv420p frames, gradient luma, BT.709 limited,
+    interleaved RGB out): bit-exact against the oracle, and against libswscale -- the library the
+    reference's CPU route converts with -- at the tolerance two different fixed- and
+    floating-point implementations of one transform allow (mean |diff| < 1.5, max <= 8; the
+    reference kernel's table scales chroma slightly differently from the standard matrix)."""
+    import spdl_b200.io as io
+    from oracle import swscale_ref
+
+    n, w, h = 4, 1920, 1080
+    i420 = synth.i420_batch_gradient(n, w, h, config=1, index=0)
+    got = _fetch(io.convert_nv12(_to_dev(i420), device_config=cuda_cfg, src_format="i420",
+                                 layout="NHWC", sync=True), "uint8")
+    want = _oracle_dense(i420, "i420", "NHWC", "uint8", "rgb")
+    assert (got == want).all()
+    if not swscale_ref.available():
+        pytest.skip("no libswscale on this machine")
+    ref = np.empty((n, h, w, 3), np.uint8)
+    conv = swscale_ref.I420ToRGB(w, h)
+    for i in range(n):
+        conv(i420[i], ref[i])
+    d = np.abs(got.astype(np.int16) - ref)
+    assert d.mean() < 1.5 and d.max() <= 8
