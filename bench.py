@@ -325,6 +325,17 @@ def run_ours(args) -> None:
         torch.cuda.synchronize(dev)
         e2e_s = (time.perf_counter() - t0) / Ke  # seconds per end-to-end step
     assert sums.shape == (N_FRAMES,)
+    # the link's own rate for the same upload (pinned host -> device, nothing else running): the
+    # bound of the end-to-end figure
+    try:
+        t0 = time.perf_counter()
+        for i in range(8):
+            _lib.check(L.b2_transfer_h2d(inputs[i % ROTATE].data_ptr(), host[i % 2].data_ptr,
+                                         host[i % 2].nbytes, 1, info.local_rank, cfg.stream))
+        h2d_gbs = 8 * host[0].nbytes / (time.perf_counter() - t0) / 1e9
+    except Exception as exc:  # informational figure: never fail the run over it
+        print(f"link measurement skipped: {exc}", file=sys.stderr)
+        h2d_gbs = None
 
     # -- max over ranks ----------------------------------------------------------------------------
     per_rank = gather_stats([ms_total, e2e_s], device=dev)
@@ -349,6 +360,8 @@ def run_ours(args) -> None:
             "e2e": {"value": N_FRAMES * info.world_size / e2e_max, "unit": "frames/s",
                     "steps": min(K, 50),
                     "h2d_bytes_per_step": N_FRAMES * FRAME_IN, "d2h_bytes_per_step": N_FRAMES * 8,
+                    "h2d_gb_per_s": N_FRAMES * FRAME_IN / e2e_s / 1e9,
+                    "link_h2d_gb_per_s": h2d_gbs,
                     "note": "pinned NV12 -> transfer_buffer -> convert_nv12 -> frame_checksum -> "
                             "host, per step, two worker threads on private streams, host-timed"},
             "gpu_launches": timed_launches,

@@ -724,6 +724,8 @@ int launch_dense(const DenseLaunch& L, cudaStream_t stream) {
 
   // Can every access of the vector path be a naturally aligned 4/8/16-byte vector?
   const int esz = L.dtype == B2_U8 ? 1 : (L.dtype == B2_F32 ? 4 : 2);
+  if (L.dst_row_pitch * esz > 0x7fffffffLL || 3LL * L.width * esz > 0x7fffffffLL)
+    return fail(B2_ERR_LIMIT, "output row beyond 2^31-1 bytes");
   const int px = 16 / esz;
   const int uvb = L.src_format == B2_SRC_NV12 ? px : px / 2;
   const bool table = L.y_table != nullptr;

@@ -198,3 +198,48 @@ def test_unaligned_output_width(cuda_cfg):
     for layout, dtype in (("NCHW", "uint8"), ("NHWC", "uint8"), ("NHWC", "float32")):
         got, want = _run(cuda_cfg, nv.reshape(-1), descs, out, "nv12", layout, dtype)
         _compare(got, want, dtype)
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_sharded_ragged_batch_equals_whole(cuda_cfg, world):
+    """The ragged batch split over ``world`` ranks in contiguous blocks (descriptor table sliced,
+    offsets still relative to the shared buffer): the ranks' outputs, concatenated, are the
+    whole-batch output.  Ranks run one after the other on this GPU."""
+    import spdl_b200.io as io
+    from spdl_b200.sharding import shard_range
+
+    n = 24
+    data, ws, hs, offs = synth.ragged_i420(n, lo=64, hi=160, config=5, index=7)
+    descs, out = io.make_image_descs(ws, hs, src_format="i420", offsets=offs, resize_shorter=48,
+                                     crop=(40, 40))
+    whole, want = _run(cuda_cfg, data, descs, out, "i420", "NCHW", "float32", coeff=6,
+                       full_range=True, mean=MEAN, std=STD)
+    _compare(whole, want, "float32")
+    parts = []
+    for r in range(world):
+        lo, hi = shard_range(n, r, world)
+        got, _ = _run(cuda_cfg, data, descs[lo:hi].copy(), out, "i420", "NCHW", "float32", coeff=6,
+                      full_range=True, mean=MEAN, std=STD)
+        parts.append(got)
+    assert (np.concatenate(parts) == whole).all()
+
+
+def test_sharded_clips_equal_whole(cuda_cfg):
+    """Clips split over 4 ranks (whole clips per rank): N x T x C x H x W of the ranks,
+    concatenated along N, is the whole batch."""
+    import spdl_b200.io as io
+    from spdl_b200.sharding import shard_range
+
+    clips, t, w, h, world = 8, 4, 128, 72, 4
+    frames = np.concatenate([synth.nv12_clip(t, w, h, config=4, index=i) for i in range(clips)])
+    descs, out = io.make_image_descs([w] * clips * t, [h] * clips * t, resize=(32, 32))
+    whole, want = _run(cuda_cfg, frames.reshape(-1), descs, out, "nv12", "NCHW", "uint8", coeff=6)
+    assert (whole == want).all()
+    parts = []
+    for r in range(world):
+        lo, hi = shard_range(clips, r, world)
+        mine = frames[lo * t:hi * t]  # this rank's clips, resident on its own GPU
+        d, _ = io.make_image_descs([w] * (hi - lo) * t, [h] * (hi - lo) * t, resize=(32, 32))
+        got, _ = _run(cuda_cfg, mine.reshape(-1), d, out, "nv12", "NCHW", "uint8", coeff=6)
+        parts.append(got.reshape(hi - lo, t, 3, 32, 32))
+    assert (np.concatenate(parts) == whole.reshape(clips, t, 3, 32, 32)).all()
