@@ -296,6 +296,11 @@ def run_ours(args) -> None:
         emit({"kernel_only": True, "ms_per_launch": ms_total / K,
               "gb_per_s": N_FRAMES * ALGO_BYTES_PER_FRAME / (ms_total / K * 1e-3) / 1e9})
         return
+    # Pinned buffers and the worker threads that feed the GPU live on the GPU's NUMA node, so that
+    # uploads do not cross the socket interconnect (it matters once several ranks upload at once).
+    from spdl_b200.sharding import bind_to_gpu_node
+
+    numa = bind_to_gpu_node(info.local_rank) if not args.no_numa else None
     host = [io.CPUBuffer((N_FRAMES, H * 3 // 2, W), "u", 1,
                          io.cpu_storage(N_FRAMES * FRAME_IN, pin_memory=True)) for _ in range(2)]
     for hb, src in zip(host, inputs):
@@ -336,6 +341,8 @@ def run_ours(args) -> None:
     except Exception as exc:  # informational figure: never fail the run over it
         print(f"link measurement skipped: {exc}", file=sys.stderr)
         h2d_gbs = None
+    if numa is not None and numa["bound"]:
+        os.sched_setaffinity(0, numa["previous"])  # the CPU legs below use every core again
 
     # -- max over ranks ----------------------------------------------------------------------------
     per_rank = gather_stats([ms_total, e2e_s], device=dev)
@@ -362,6 +369,8 @@ def run_ours(args) -> None:
                     "h2d_bytes_per_step": N_FRAMES * FRAME_IN, "d2h_bytes_per_step": N_FRAMES * 8,
                     "h2d_gb_per_s": N_FRAMES * FRAME_IN / e2e_s / 1e9,
                     "link_h2d_gb_per_s": h2d_gbs,
+                    "host_binding": None if numa is None else
+                    {k: numa[k] for k in ("node", "cpus", "bound")},
                     "note": "pinned NV12 -> transfer_buffer -> convert_nv12 -> frame_checksum -> "
                             "host, per step, two worker threads on private streams, host-timed"},
             "gpu_launches": timed_launches,
@@ -719,6 +728,8 @@ def main() -> None:
                          "aux = gather, checksum and any-shape kernels (one GPU, informational)")
     ap.add_argument("--scale", default="1.0",
                     help="fraction of a resize workload's batch (for profiler captures)")
+    ap.add_argument("--no-numa", action="store_true",
+                    help="do not bind the end-to-end leg to the GPU's NUMA node")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
                     help="c2 only: weak = 64 frames per GPU (default); strong = 64 frames per step "
                          "split over the GPUs")

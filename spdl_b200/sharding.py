@@ -14,7 +14,8 @@ import os
 from dataclasses import dataclass
 from typing import Any, Sequence
 
-__all__ = ["RankInfo", "rank_info", "shard_range", "shard_indices", "ShardWorker", "gather_stats"]
+__all__ = ["RankInfo", "rank_info", "shard_range", "shard_indices", "ShardWorker", "gather_stats",
+           "parse_cpulist", "gpu_numa_node", "node_cpus", "bind_to_gpu_node"]
 
 
 @dataclass(frozen=True)
@@ -58,10 +59,79 @@ def shard_indices(total: int, rank: int, world_size: int, mode: str = "block") -
     raise RuntimeError(f"Unknown shard mode: {mode}")
 
 
+# ---- host locality: keep a rank's threads and pinned buffers on its GPU's NUMA node ---------------
+# Each rank uploads its own frames over its own PCIe link.  On a two-socket host a pinned buffer
+# that sits on the other socket makes every upload cross the socket interconnect, which then
+# bounds the aggregate upload rate of all ranks.  Binding the rank's process to the CPUs of the
+# GPU's node before it allocates pinned memory (pages are placed on the node of the allocating
+# thread) keeps uploads local.
+
+
+def parse_cpulist(text: str) -> list[int]:
+    """``"0-3,8,10-11"`` (the kernel's cpulist format) -> ``[0, 1, 2, 3, 8, 10, 11]``."""
+    cpus: list[int] = []
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.extend(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def gpu_numa_node(pci_bus_id: str, sysfs: str = "/sys") -> int | None:
+    """NUMA node of the PCI device ``"0000:1b:00.0"`` (None when the host does not say)."""
+    try:
+        with open(os.path.join(sysfs, "bus/pci/devices", pci_bus_id.lower(), "numa_node")) as f:
+            node = int(f.read().strip())
+    except (OSError, ValueError):
+        return None
+    return node if node >= 0 else None
+
+
+def node_cpus(node: int, sysfs: str = "/sys") -> list[int]:
+    try:
+        with open(os.path.join(sysfs, "devices/system/node", f"node{node}", "cpulist")) as f:
+            return parse_cpulist(f.read())
+    except (OSError, ValueError):
+        return []
+
+
+def _pci_bus_id(device_index: int) -> str | None:
+    import torch
+
+    p = torch.cuda.get_device_properties(device_index)
+    try:
+        return f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+    except AttributeError:
+        return None
+
+
+def bind_to_gpu_node(device_index: int, sysfs: str = "/sys", pci_bus_id: str | None = None) -> dict:
+    """Restrict this process to the CPUs of the NUMA node of GPU ``device_index`` (those of them
+    it is allowed to run on).  Returns ``{"node", "cpus", "bound", "previous"}``; ``previous`` is
+    the affinity to hand to ``os.sched_setaffinity`` to undo the binding.  Does nothing when the
+    node is unknown or none of its CPUs is available."""
+    allowed = sorted(os.sched_getaffinity(0))
+    out = {"node": None, "cpus": len(allowed), "bound": False, "previous": allowed}
+    bus = pci_bus_id or _pci_bus_id(device_index)
+    node = gpu_numa_node(bus, sysfs) if bus else None
+    if node is None:
+        return out
+    out["node"] = node
+    local = sorted(set(node_cpus(node, sysfs)) & set(allowed))
+    if not local or local == allowed:
+        return out
+    os.sched_setaffinity(0, local)
+    out.update(cpus=len(local), bound=True)
+    return out
+
+
 class ShardWorker:
     """The device, private stream and ``CUDAConfig`` of one rank."""
 
-    def __init__(self, info: RankInfo | None = None) -> None:
+    def __init__(self, info: RankInfo | None = None, bind_host: bool = False) -> None:
+        """``bind_host``: also restrict the process to the CPUs next to the rank's GPU (see
+        ``bind_to_gpu_node``); the result is kept in ``self.host_binding``."""
         import torch
 
         from . import _lib
@@ -75,6 +145,7 @@ class ShardWorker:
         _lib.check(_lib.lib().b2_init(self.info.local_rank))
         self.stream = torch.cuda.Stream(self.device)
         self.config = cuda_config(self.info.local_rank, stream=self.stream.cuda_stream)
+        self.host_binding = bind_to_gpu_node(self.info.local_rank) if bind_host else None
 
     def my_slice(self, total: int, mode: str = "block") -> range:
         return shard_indices(total, self.info.rank, self.info.world_size, mode)

@@ -145,3 +145,39 @@ def test_gather_survives_a_rank_that_left():
     strict, local = got[0]
     assert strict != "no error"        # the strict mode surfaces the failure
     assert local == [[7.0, 8.0]]       # the tolerant mode keeps this rank's own numbers
+
+
+def test_numa_helpers_against_a_fake_sysfs(tmp_path):
+    import os
+
+    from spdl_b200.sharding import bind_to_gpu_node, gpu_numa_node, node_cpus, parse_cpulist
+
+    assert parse_cpulist("0-3,8,10-11\n") == [0, 1, 2, 3, 8, 10, 11]
+    assert parse_cpulist("") == []
+    dev = tmp_path / "bus/pci/devices/0000:1b:00.0"
+    dev.mkdir(parents=True)
+    (dev / "numa_node").write_text("1\n")
+    unknown = tmp_path / "bus/pci/devices/0000:3c:00.0"
+    unknown.mkdir(parents=True)
+    (unknown / "numa_node").write_text("-1\n")
+    allowed = sorted(os.sched_getaffinity(0))
+    node = tmp_path / "devices/system/node/node1"
+    node.mkdir(parents=True)
+    # the node owns the first allowed CPU and one that does not exist here
+    (node / "cpulist").write_text(f"{allowed[0]},100000\n")
+    assert gpu_numa_node("0000:1B:00.0", str(tmp_path)) == 1
+    assert gpu_numa_node("0000:3c:00.0", str(tmp_path)) is None
+    assert gpu_numa_node("0000:ff:00.0", str(tmp_path)) is None
+    assert node_cpus(1, str(tmp_path)) == [allowed[0], 100000]
+    # unknown node: nothing changes
+    r = bind_to_gpu_node(0, str(tmp_path), pci_bus_id="0000:3c:00.0")
+    assert r["bound"] is False and sorted(os.sched_getaffinity(0)) == allowed
+    r = bind_to_gpu_node(0, str(tmp_path), pci_bus_id="0000:1b:00.0")
+    try:
+        assert r["node"] == 1 and r["previous"] == allowed
+        if len(allowed) > 1:
+            assert r["bound"] is True and sorted(os.sched_getaffinity(0)) == [allowed[0]]
+        else:
+            assert r["bound"] is False
+    finally:
+        os.sched_setaffinity(0, allowed)
