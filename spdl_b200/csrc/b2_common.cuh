@@ -155,6 +155,37 @@ __device__ __forceinline__ void pixel2_bits(const ColorMat& m, float2 by, const 
   g = x2_add_rz(x2_add(x2_fma(g2, fy, c.ug), c.vg), magic);
   b = x2_add_rz(x2_fma(g2, fy, c.ub), magic);
 }
+// The same two pixels for 8-bit output.  The last step of each channel is a multiply by 2^-149
+// with round-toward-zero: the result is the subnormal whose mantissa is trunc(|x|), so its BIT
+// PATTERN, read as a signed integer, is trunc(x) for x >= 0 and a negative number for x < 0
+// (sign bit set) -- exactly what a saturating integer pack needs (see pack4_sat).
+__device__ __forceinline__ float2 x2_mul_rz(float2 a, float2 b) {
+  unsigned long long d;
+  asm("mul.rz.f32x2 %0, %1, %2;" : "=l"(d) : "l"(pack2(a)), "l"(pack2(b)));
+  return unpack2(d);
+}
+__device__ __forceinline__ void pixel2_ints(const ColorMat& m, float2 by, const Chroma2& c,
+                                            float2& r, float2& g, float2& b) {
+  const float2 g2 = dup2(m.g), unit = dup2(__uint_as_float(1u));  // 2^-149
+  const float2 fy = x2_add(by, dup2(-m.y_bias));
+  const float2 ly = x2_fma(g2, fy, dup2(m.neg_zero));
+  r = x2_mul_rz(x2_add(ly, c.vr), unit);
+  g = x2_mul_rz(x2_add(x2_fma(g2, fy, c.ug), c.vg), unit);
+  b = x2_mul_rz(x2_fma(g2, fy, c.ub), unit);
+}
+// Truncate-and-clamp (color_conversion.cu:72-74) of four values produced by pixel2_ints and
+// pack them as bytes {v0, v1, v2, v3}, v0 lowest: two saturating packs (s32 -> u8: negative -> 0,
+// above 255 -> 255).
+__device__ __forceinline__ uint32_t pack4_sat(float v0, float v1, float v2, float v3) {
+  uint32_t hi, d;
+  asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;"
+      : "=r"(hi)
+      : "r"(__float_as_uint(v3)), "r"(__float_as_uint(v2)), "r"(0u));
+  asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;"
+      : "=r"(d)
+      : "r"(__float_as_uint(v1)), "r"(__float_as_uint(v0)), "r"(hi));
+  return d;
+}
 // Clamp two magic-added values (as produced by pixel2_bits) to 0..255 in two 16-bit lanes.
 __device__ __forceinline__ uint32_t clamp2_bits(float a, float b) {
   return __vimin_s16x2_relu(__byte_perm(__float_as_uint(a), __float_as_uint(b), 0x5410u),

@@ -167,8 +167,9 @@ __global__ void __launch_bounds__(kDenseThreads, kDenseMinBlocks) dense_vec_kern
 #pragma unroll
         for (int k = 0; k < 2; ++k) {  // pixels k and k+2 share one packed instruction stream
           float2 cr, cg, cb;
-          pixel2_bits(m, make_float2(biased_byte(yw[r][j], k), biased_byte(yw[r][j], k + 2)), c, cr,
-                      cg, cb);
+          const float2 by = make_float2(biased_byte(yw[r][j], k), biased_byte(yw[r][j], k + 2));
+          if constexpr (DTYPE == B2_U8) pixel2_ints(m, by, c, cr, cg, cb);
+          else pixel2_bits(m, by, c, cr, cg, cb);
           ch[BGR ? 2 : 0][k] = cr.x; ch[BGR ? 2 : 0][k + 2] = cr.y;
           ch[1][k] = cg.x;           ch[1][k + 2] = cg.y;
           ch[BGR ? 0 : 2][k] = cb.x; ch[BGR ? 0 : 2][k + 2] = cb.y;
@@ -177,11 +178,11 @@ __global__ void __launch_bounds__(kDenseThreads, kDenseMinBlocks) dense_vec_kern
           if constexpr (LAYOUT == B2_NCHW) {
 #pragma unroll
             for (int s = 0; s < 3; ++s)
-              out[r][4 * s + j] = bytes4(clamp2_bits(ch[s][0], ch[s][1]), clamp2_bits(ch[s][2], ch[s][3]));
+              out[r][4 * s + j] = pack4_sat(ch[s][0], ch[s][1], ch[s][2], ch[s][3]);
           } else {
-            out[r][3 * j + 0] = bytes4(clamp2_bits(ch[0][0], ch[1][0]), clamp2_bits(ch[2][0], ch[0][1]));
-            out[r][3 * j + 1] = bytes4(clamp2_bits(ch[1][1], ch[2][1]), clamp2_bits(ch[0][2], ch[1][2]));
-            out[r][3 * j + 2] = bytes4(clamp2_bits(ch[2][2], ch[0][3]), clamp2_bits(ch[1][3], ch[2][3]));
+            out[r][3 * j + 0] = pack4_sat(ch[0][0], ch[1][0], ch[2][0], ch[0][1]);
+            out[r][3 * j + 1] = pack4_sat(ch[1][1], ch[2][1], ch[0][2], ch[1][2]);
+            out[r][3 * j + 2] = pack4_sat(ch[2][2], ch[0][3], ch[1][3], ch[2][3]);
             if (j >= 1) stage_piece(r, j - 1);  // piece i needs the luma words up to i + 1
           }
         } else {
@@ -302,8 +303,9 @@ __device__ __forceinline__ void convert_chunk(const ColorMat& m, const ScaleBias
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
         float2 cr, cg, cb;
-        pixel2_bits(m, make_float2(biased_byte(yw[r][j], k), biased_byte(yw[r][j], k + 2)), c, cr,
-                    cg, cb);
+        const float2 by = make_float2(biased_byte(yw[r][j], k), biased_byte(yw[r][j], k + 2));
+        if constexpr (DTYPE == B2_U8) pixel2_ints(m, by, c, cr, cg, cb);
+        else pixel2_bits(m, by, c, cr, cg, cb);
         ch[BGR ? 2 : 0][k] = cr.x; ch[BGR ? 2 : 0][k + 2] = cr.y;
         ch[1][k] = cg.x;           ch[1][k + 2] = cg.y;
         ch[BGR ? 0 : 2][k] = cb.x; ch[BGR ? 0 : 2][k + 2] = cb.y;
@@ -312,12 +314,11 @@ __device__ __forceinline__ void convert_chunk(const ColorMat& m, const ScaleBias
         if constexpr (LAYOUT == B2_NCHW) {
 #pragma unroll
           for (int s = 0; s < 3; ++s)
-            out[r][4 * s + j] =
-                bytes4(clamp2_bits(ch[s][0], ch[s][1]), clamp2_bits(ch[s][2], ch[s][3]));
+            out[r][4 * s + j] = pack4_sat(ch[s][0], ch[s][1], ch[s][2], ch[s][3]);
         } else {
-          out[r][3 * j + 0] = bytes4(clamp2_bits(ch[0][0], ch[1][0]), clamp2_bits(ch[2][0], ch[0][1]));
-          out[r][3 * j + 1] = bytes4(clamp2_bits(ch[1][1], ch[2][1]), clamp2_bits(ch[0][2], ch[1][2]));
-          out[r][3 * j + 2] = bytes4(clamp2_bits(ch[2][2], ch[0][3]), clamp2_bits(ch[1][3], ch[2][3]));
+          out[r][3 * j + 0] = pack4_sat(ch[0][0], ch[1][0], ch[2][0], ch[0][1]);
+          out[r][3 * j + 1] = pack4_sat(ch[1][1], ch[2][1], ch[0][2], ch[1][2]);
+          out[r][3 * j + 2] = pack4_sat(ch[2][2], ch[0][3], ch[1][3], ch[2][3]);
         }
       } else {
         float f[3][4];
