@@ -42,8 +42,8 @@ ROTATE = 4  # distinct input batches cycled through, so no step finds its input 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dense kernel on this workload,
 # from an ncu capture of this very workload (summary kept under profiles/)
-# (199,078,144 read + 359,220,224 written; part of the 398 MB output is still in L2 at kernel end).
-NCU_TRAFFIC_BYTES_PER_LAUNCH: int | None = 558_298_368
+# (199,076,864 read + 345,854,976 written; part of the 398 MB output is still in L2 at kernel end).
+NCU_TRAFFIC_BYTES_PER_LAUNCH: int | None = 544_931_840
 
 
 def measured_peak() -> tuple[float, str]:

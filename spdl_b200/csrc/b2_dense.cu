@@ -162,14 +162,13 @@ __global__ void __launch_bounds__(kDenseThreads, kDenseMinBlocks) dense_vec_kern
       }
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
-        // ch[slot][pixel]: channel value + 1.5*2^23, truncated (floor in the low mantissa bits)
+        // ch[slot][pixel]: the truncated channel value as a subnormal bit pattern (pixel2_ints)
         float ch[3][4];
 #pragma unroll
         for (int k = 0; k < 2; ++k) {  // pixels k and k+2 share one packed instruction stream
           float2 cr, cg, cb;
           const float2 by = make_float2(biased_byte(yw[r][j], k), biased_byte(yw[r][j], k + 2));
-          if constexpr (DTYPE == B2_U8) pixel2_ints(m, by, c, cr, cg, cb);
-          else pixel2_bits(m, by, c, cr, cg, cb);
+          pixel2_ints(m, by, c, cr, cg, cb);
           ch[BGR ? 2 : 0][k] = cr.x; ch[BGR ? 2 : 0][k + 2] = cr.y;
           ch[1][k] = cg.x;           ch[1][k + 2] = cg.y;
           ch[BGR ? 0 : 2][k] = cb.x; ch[BGR ? 0 : 2][k + 2] = cb.y;
@@ -189,12 +188,12 @@ __global__ void __launch_bounds__(kDenseThreads, kDenseMinBlocks) dense_vec_kern
           float f[3][4];
 #pragma unroll
           for (int s = 0; s < 3; ++s) {
-            const uint32_t q01 = clamp2_bits(ch[s][0], ch[s][1]), q23 = clamp2_bits(ch[s][2], ch[s][3]);
+            const uint32_t q = pack4_sat(ch[s][0], ch[s][1], ch[s][2], ch[s][3]);
             // exact 0..255 floats of two pixels, then value * scale + bias, two lanes at a time
             const float2 sc = dup2(p.sb.s[s]), bi = dup2(p.sb.b[s]), off = dup2(-kTwo23);
-            const float2 a = x2_fma(x2_add(make_float2(biased_byte(q01, 0), biased_byte(q01, 2)), off),
+            const float2 a = x2_fma(x2_add(make_float2(biased_byte(q, 0), biased_byte(q, 1)), off),
                                     sc, bi);
-            const float2 b = x2_fma(x2_add(make_float2(biased_byte(q23, 0), biased_byte(q23, 2)), off),
+            const float2 b = x2_fma(x2_add(make_float2(biased_byte(q, 2), biased_byte(q, 3)), off),
                                     sc, bi);
             f[s][0] = a.x; f[s][1] = a.y; f[s][2] = b.x; f[s][3] = b.y;
           }
@@ -304,8 +303,7 @@ __device__ __forceinline__ void convert_chunk(const ColorMat& m, const ScaleBias
       for (int k = 0; k < 2; ++k) {
         float2 cr, cg, cb;
         const float2 by = make_float2(biased_byte(yw[r][j], k), biased_byte(yw[r][j], k + 2));
-        if constexpr (DTYPE == B2_U8) pixel2_ints(m, by, c, cr, cg, cb);
-        else pixel2_bits(m, by, c, cr, cg, cb);
+        pixel2_ints(m, by, c, cr, cg, cb);
         ch[BGR ? 2 : 0][k] = cr.x; ch[BGR ? 2 : 0][k + 2] = cr.y;
         ch[1][k] = cg.x;           ch[1][k + 2] = cg.y;
         ch[BGR ? 0 : 2][k] = cb.x; ch[BGR ? 0 : 2][k + 2] = cb.y;
@@ -324,12 +322,12 @@ __device__ __forceinline__ void convert_chunk(const ColorMat& m, const ScaleBias
         float f[3][4];
 #pragma unroll
         for (int s = 0; s < 3; ++s) {
-          const uint32_t q01 = clamp2_bits(ch[s][0], ch[s][1]), q23 = clamp2_bits(ch[s][2], ch[s][3]);
+          const uint32_t q = pack4_sat(ch[s][0], ch[s][1], ch[s][2], ch[s][3]);
           const float2 sc = dup2(sb.s[s]), bi = dup2(sb.b[s]), off = dup2(-kTwo23);
           const float2 a = x2_fma(
-              x2_add(make_float2(biased_byte(q01, 0), biased_byte(q01, 2)), off), sc, bi);
+              x2_add(make_float2(biased_byte(q, 0), biased_byte(q, 1)), off), sc, bi);
           const float2 b = x2_fma(
-              x2_add(make_float2(biased_byte(q23, 0), biased_byte(q23, 2)), off), sc, bi);
+              x2_add(make_float2(biased_byte(q, 2), biased_byte(q, 3)), off), sc, bi);
           f[s][0] = a.x; f[s][1] = a.y; f[s][2] = b.x; f[s][3] = b.y;
         }
         if constexpr (DTYPE == B2_F32) {
