@@ -297,30 +297,32 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
     // ---- finish and store four pixels -------------------------------------------------------
     const bool full4 = p.vec_store && ox0 + 4 <= p.out_w;
     if constexpr (DTYPE == B2_U8) {
-      float q[4][3];  // floor(val + 0.5) in the low mantissa bits (see quant2)
+      // floor(val + 0.5) as a subnormal bit pattern (val >= 0): see pack4_sat
+      float q[4][3];
 #pragma unroll
       for (int k = 0; k < 4; ++k)
 #pragma unroll
         for (int s = 0; s < 3; ++s)
-          q[k][s] = __fadd_rz(__fmaf_rn(val[k][s], kTapScale, 0.5f), kQuantMagic);
+          q[k][s] = __fmul_rz(__fmaf_rn(val[k][s], kTapScale, 0.5f), __uint_as_float(1u));
       if (full4) {
         if constexpr (LAYOUT == B2_NCHW) {
 #pragma unroll
           for (int s = 0; s < 3; ++s)
             *reinterpret_cast<uint32_t*>(dst + ((long long)s * p.out_h + oy) * p.out_w + ox0) =
-                bytes4(clamp2_bits(q[0][s], q[1][s]), clamp2_bits(q[2][s], q[3][s]));
+                pack4_sat(q[0][s], q[1][s], q[2][s], q[3][s]);
         } else {
           uint32_t* o = reinterpret_cast<uint32_t*>(dst + ((long long)oy * p.out_w + ox0) * 3);
-          o[0] = bytes4(clamp2_bits(q[0][0], q[0][1]), clamp2_bits(q[0][2], q[1][0]));
-          o[1] = bytes4(clamp2_bits(q[1][1], q[1][2]), clamp2_bits(q[2][0], q[2][1]));
-          o[2] = bytes4(clamp2_bits(q[2][2], q[3][0]), clamp2_bits(q[3][1], q[3][2]));
+          o[0] = pack4_sat(q[0][0], q[0][1], q[0][2], q[1][0]);
+          o[1] = pack4_sat(q[1][1], q[1][2], q[2][0], q[2][1]);
+          o[2] = pack4_sat(q[2][2], q[3][0], q[3][1], q[3][2]);
         }
         continue;
       }
 #pragma unroll
       for (int k = 0; k < 4; ++k)
 #pragma unroll
-        for (int s = 0; s < 3; ++s) val[k][s] = (float)(clamp2_bits(q[k][s], q[k][s]) & 0xFFFFu);
+        for (int s = 0; s < 3; ++s)
+          val[k][s] = (float)(pack4_sat(q[k][s], q[k][s], q[k][s], q[k][s]) & 0xFFu);
     } else {
 #pragma unroll
       for (int k = 0; k < 4; ++k)
