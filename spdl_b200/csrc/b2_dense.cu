@@ -59,9 +59,9 @@ __device__ __forceinline__ void load_bytes(const uint8_t* p, uint32_t* w) {
 template <int NB>
 __device__ __forceinline__ void load_window(const uint8_t* row, int x, int limit, uint32_t* w) {
   constexpr int NWD = (NB + 3) / 4;
-  const uint8_t* p = row + x;
-  const int a = (int)((uintptr_t)p & 3);
-  const uint32_t* q = reinterpret_cast<const uint32_t*>(p - a);
+  const uintptr_t addr = (uintptr_t)row + (intptr_t)x;  // x may be negative (before the row)
+  const int a = (int)(addr & 3);
+  const uint32_t* q = reinterpret_cast<const uint32_t*>(addr - a);
   const int t = x - a;  // row index of the first byte of q[0]
   uint32_t v[NWD + 1];
   if (t >= 0 && t + 4 * (NWD + 1) <= limit) {

@@ -113,3 +113,52 @@ def test_destination_on_odd_elements(cuda_cfg, w, h, layout, dtype, dst_off):
     if w & 1:
         tail = body[..., w - 1] if layout == "NCHW" else body[:, :, w - 1, :]
         assert (tail == sentinel).all()
+
+
+@pytest.mark.parametrize("w", [64, 50])
+@pytest.mark.parametrize("src_pad", [0, 16, 6])
+@pytest.mark.parametrize("dst_gap", [0, 16, 7])
+@pytest.mark.parametrize("layout", ["NCHW", "NHWC"])
+def test_pitched_source_and_strided_destination(cuda_cfg, w, src_pad, dst_gap, layout):
+    """Source rows with a pitch wider than the row and frames spaced apart in the destination
+    (``dst_frame_stride``), aligned and not: results equal the packed case and the padding keeps
+    its sentinel value."""
+    import ctypes
+
+    import torch
+
+    from spdl_b200 import _lib
+
+    n, h = 3, 12
+    h2 = h * 3 // 2
+    pitch = w + src_pad
+    nv = synth.nv12_batch(n, w, h, config=9, index=w + src_pad + dst_gap)
+    pitched = np.full((n, h2, pitch), 0x77, np.uint8)
+    pitched[:, :, :w] = nv
+    src = torch.from_numpy(pitched).cuda()
+    frame = 3 * h * w
+    stride = frame + dst_gap
+    buf = torch.full((n * stride + 16,), 0xA5, dtype=torch.uint8, device="cuda")
+    a = _lib.DenseArgs()
+    a.struct_size = ctypes.sizeof(_lib.DenseArgs)
+    a.device = cuda_cfg.device_index
+    a.y, a.u = src.data_ptr(), src.data_ptr() + h * pitch
+    a.y_pitch = a.uv_pitch = pitch
+    a.y_frame_stride = a.uv_frame_stride = h2 * pitch
+    a.src_format, a.width, a.height, a.num_frames = _lib.NV12, w, h, n
+    a.matrix_coeff = 1
+    a.dst, a.dst_frame_stride = buf.data_ptr(), stride
+    a.layout = _lib.NCHW if layout == "NCHW" else _lib.NHWC
+    a.dtype, a.order = _lib.U8, _lib.BGR
+    a.scale = (ctypes.c_float * 3)(1, 1, 1)
+    _lib.check(_lib.lib().b2_convert_dense(ctypes.byref(a), torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    got = buf.cpu().numpy()
+    want = oracle.convert_dense(
+        nv, nv.reshape(-1)[h * w:], None, width=w, height=h, num_frames=n, y_pitch=w, uv_pitch=w,
+        y_frame_stride=h2 * w, uv_frame_stride=h2 * w, src_format=oracle.NV12,
+        layout=oracle.NCHW if layout == "NCHW" else oracle.NHWC, order=oracle.BGR)
+    for i in range(n):
+        assert (got[i * stride:i * stride + frame] == want[i].reshape(-1)).all()
+        assert (got[i * stride + frame:(i + 1) * stride] == 0xA5).all()
+    assert (got[n * stride:] == 0xA5).all()
