@@ -36,7 +36,7 @@ def _check(got, want, dtype):
                                    oracle.bf16_to_f32(want), rtol=2 ** -7, atol=1e-6)
 
 
-@pytest.mark.parametrize("seed", range(40))
+@pytest.mark.parametrize("seed", range(64))
 def test_dense_random_cases(cuda_cfg, seed):
     import spdl_b200.io as io
 
@@ -49,8 +49,8 @@ def test_dense_random_cases(cuda_cfg, seed):
     full = bool(r.integers(0, 2))
     n = int(r.integers(1, 5))
     # widths that hit the vector path (multiples of 16/8/4) and the any-shape path
-    w = int(r.choice([16, 32, 48, 64, 200, 328, 1000, 18, 22, 50, 2])) if fmt == "nv12" \
-        else int(r.choice([16, 32, 64, 200, 328, 18, 50, 2]))
+    w = int(r.choice([16, 32, 48, 64, 200, 328, 1000, 18, 22, 50, 2, 854, 426, 130])) \
+        if fmt == "nv12" else int(r.choice([16, 32, 64, 200, 328, 18, 50, 2, 854, 426, 130]))
     h = int(r.integers(1, 20)) * 2
     nv = synth.nv12_batch(n, w, h, config=9, index=seed, full_range=True)
     norm = dict(mean=MEAN, std=STD) if dtype != "uint8" and r.integers(0, 2) else {}
@@ -72,7 +72,7 @@ def test_dense_random_cases(cuda_cfg, seed):
     _check(got, want, dtype)
 
 
-@pytest.mark.parametrize("seed", range(40))
+@pytest.mark.parametrize("seed", range(64))
 def test_resize_random_cases(cuda_cfg, seed):
     import spdl_b200.io as io
 
