@@ -7,7 +7,8 @@
 //   top = fma(wx1, t01, wx0*t00); bot = fma(wx1, t11, wx0*t10); val = fma(wy1, bot, wy0*top)
 //   u8 output: floor(val + 0.5) clamped to 0..255; float outputs: fma(val, scale, bias).
 //
-// One CTA produces kRows output rows of one image.
+// One CTA produces 4 output rows of one image (2 when the staged rows of 4 would leave few CTAs
+// per SM).
 //   Stage:   for each output row the CTA needs two luma rows and one or two chroma rows (two
 //            planes for I420).  Warp 0 works out the distinct row spans (rows shared between
 //            neighbouring output rows are fetched once), and each lane hands its span to the
@@ -37,9 +38,10 @@ struct ResizeParams {
   ScaleBias sb;
   int span_cap;   // bytes reserved per staged row span (multiple of 16)
   int vec_store;  // 1: out_w % 4 == 0 and the destination is 16-byte aligned
+  int rows;       // output rows per CTA: kRows, or 2 for wide sources
 };
 
-constexpr int kRows = 4;  // output rows per CTA
+constexpr int kRows = 4;  // output rows per CTA, at most
 constexpr int kResizeThreads = 128;
 // 128-thread CTAs, 8 resident per SM (32 warps, 63 registers, no spills): measured best; larger
 // CTAs or tighter register caps (more warps, spills) were slower.
@@ -103,7 +105,7 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
   __shared__ __align__(8) unsigned long long bar;
 
   const int n = blockIdx.y;
-  const int oy0 = blockIdx.x * kRows;
+  const int oy0 = blockIdx.x * p.rows;
   const int tid = threadIdx.x;
   if (tid < 16)
     reinterpret_cast<uint32_t*>(&sd)[tid] =
@@ -131,7 +133,7 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
   // is skipped (its output is left untouched) rather than allowed to write out of bounds.
   if (bhi - blo + 15 > p.span_cap || cxhi - cxlo + 15 > p.span_cap) return;
 
-  const int rows_here = min(kRows, p.out_h - oy0);
+  const int rows_here = min(p.rows, p.out_h - oy0);
   if (tid < 32) {
     const int lane = tid;
     const int nspans = rows_here * kPlanes;
@@ -182,7 +184,7 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
   // While the copies are in flight: one table entry per output column (the horizontal taps are
   // the same for every row of the image).  {x0 | x1 << 16, c0 | c1 << 16, wx1, -}: byte offsets
   // of the two tap columns in a staged first-plane row and in a staged second/third-plane row.
-  uint4* xtab = reinterpret_cast<uint4*>(smem + (size_t)kRows * kPlanes * p.span_cap);
+  uint4* xtab = reinterpret_cast<uint4*>(smem + (size_t)p.rows * kPlanes * p.span_cap);
   const int tab_groups = (p.out_w + 3) >> 2;
   for (int ox = tid; ox < p.out_w; ox += kResizeThreads) {
     const Axis ax = axis_of(d.scale_x, (float)(d.crop_x + ox), d.src_w);
@@ -384,7 +386,7 @@ int launch_t(const b2_resize_args& a, const ResizeParams& p, size_t smem, cudaSt
   if (smem > 48 * 1024)
     B2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
             "raising the shared-memory limit of the resize kernel failed");
-  const int row_blocks = (a.out_h + kRows - 1) / kRows;
+  const int row_blocks = (a.out_h + p.rows - 1) / p.rows;
   for (int n0 = 0; n0 < a.num_images; n0 += 65535) {
     const int nn = a.num_images - n0 < 65535 ? a.num_images - n0 : 65535;
     ResizeParams q = p;
@@ -437,7 +439,11 @@ int launch_resize(const b2_resize_args& a, cudaStream_t stream) {
   const int row_bytes = a.src_format == B2_SRC_RGB_INTERLEAVED ? 3 * a.max_src_w : a.max_src_w;
   p.span_cap = ((row_bytes + 2 + 15 + 15) / 16) * 16;
   const int planes = a.src_format == B2_SRC_NV12 ? 4 : (a.src_format == B2_SRC_RGB_INTERLEAVED ? 2 : 6);
-  const size_t smem = (size_t)kRows * planes * p.span_cap + (size_t)((a.out_w + 3) / 4) * 64;
+  const size_t table = (size_t)((a.out_w + 3) / 4) * 64;
+  // Four output rows per CTA amortise the per-CTA work best; wide sources (4K rows) take two,
+  // which halves the staging buffer and lets more CTAs share an SM.
+  p.rows = (size_t)kRows * planes * p.span_cap + table > 40 * 1024 ? 2 : kRows;
+  const size_t smem = (size_t)p.rows * planes * p.span_cap + table;
   if (p.span_cap >= 65536 || smem > 200 * 1024)
     return fail(B2_ERR_LIMIT, "max_src_w %d needs %zu bytes of staging; the limit is %d bytes",
                 a.max_src_w, smem, 200 * 1024);
