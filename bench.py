@@ -180,15 +180,15 @@ def make_cpu_runner(frames: int):
                          f"unavailable on this box), {frames} frames 1920x1080 per step")
 
 
-def time_cpu(frames: int, steps: int, warmup: int, budget_s: float = 60.0) -> dict:
+def time_cpu(frames: int, steps: int, warmup: int, limit_s: float = 60.0) -> dict:
     """Time ``steps`` steps of the CPU path.  A step is at most ``frames`` frames; it is cut down
-    (never below 8) so that all steps together take about ``budget_s`` seconds."""
+    (never below 8) so that all steps together take about ``limit_s`` seconds."""
     probe, _, _ = make_cpu_runner(8)
     probe()
     t0 = time.perf_counter()
     probe()
     rate = 8 / (time.perf_counter() - t0)
-    frames = int(max(8, min(frames, budget_s * rate / max(steps, 1))))
+    frames = int(max(8, min(frames, limit_s * rate / max(steps, 1))))
     run, kind, desc = make_cpu_runner(frames)
     for _ in range(warmup):
         run()
