@@ -1,15 +1,32 @@
 """Zero-copy casts of buffers to array libraries.
 
-Mirrors ``spdl.io.to_numpy`` / ``spdl.io.to_torch`` (``src/spdl/io/_convert.py:100-153``).
+Mirrors ``spdl.io.to_numpy`` / ``to_torch`` / ``to_numba`` / ``to_jax`` and the two protocol
+classes of ``src/spdl/io/_convert.py:28-200``.
 """
 
 from __future__ import annotations
 
-from typing import Any
+from typing import Any, Protocol, runtime_checkable
 
 import numpy as np
 
-__all__ = ["to_numpy", "to_torch"]
+__all__ = ["to_numpy", "to_torch", "to_numba", "to_jax", "ArrayInterface", "CUDAArrayInterface"]
+
+
+@runtime_checkable
+class ArrayInterface(Protocol):
+    """Objects that expose host memory through ``__array_interface__`` (NumPy's protocol)."""
+
+    @property
+    def __array_interface__(self) -> dict[str, Any]: ...
+
+
+@runtime_checkable
+class CUDAArrayInterface(Protocol):
+    """Objects that expose device memory through ``__cuda_array_interface__``."""
+
+    @property
+    def __cuda_array_interface__(self) -> dict[str, Any]: ...
 
 
 def to_numpy(buffer: Any) -> np.ndarray:
@@ -47,3 +64,21 @@ def to_torch(buffer: Any, dtype: Any = None):
     if dtype is not None and tensor.dtype != dtype:
         tensor = tensor.view(dtype)
     return tensor
+
+
+def to_numba(buffer: Any):
+    """A Numba ``DeviceNDArray`` over a CUDA buffer, or a NumPy array over a host buffer, without
+    copying (``src/spdl/io/_convert.py:156-173``).  Numba is imported on first use."""
+    if hasattr(buffer, "__cuda_array_interface__"):
+        from numba import cuda  # raises ImportError where Numba is not installed
+
+        return cuda.as_cuda_array(buffer)
+    return to_numpy(buffer)
+
+
+def to_jax(buffer: Any):
+    """A JAX array over a host buffer (``src/spdl/io/_convert.py:176-186``).  JAX is imported on
+    first use."""
+    import jax
+
+    return jax.numpy.array(to_numpy(buffer), copy=False)

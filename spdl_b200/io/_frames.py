@@ -16,7 +16,7 @@ import numpy as np
 
 from ._types import CPUBuffer, CPUStorage
 
-__all__ = ["Frames", "convert_frames"]
+__all__ = ["Frames", "convert_frames", "convert_array"]
 
 # pix_fmt -> (kind, channels/planes)
 _INTERLEAVED = {"rgb24": 3, "bgr24": 3, "rgba": 4, "bgra": 4, "gray8": 1, "gray": 1}
@@ -144,4 +144,20 @@ def convert_frames(frames: Frames | Sequence[Frames],
     if single:
         shape = shape[1:]
     buf.shape = tuple(shape)
+    return buf
+
+
+def convert_array(vals: np.ndarray, storage: CPUStorage | None = None) -> CPUBuffer:
+    """Copy an int64 array (class labels and the like) into a ``CPUBuffer``, optionally backed by
+    pinned ``storage`` so that its upload can overlap kernels
+    (``src/spdl/io/_core.py:1045-1062``, ``src/spdl/io/lib/core/conversion.cpp:70-93``).
+    An empty array is an error; other element types are rejected as the binding does."""
+    arr = np.asarray(vals)
+    if arr.dtype != np.int64:
+        raise TypeError(f"convert_array takes an int64 array, got {arr.dtype}")
+    if arr.size == 0:
+        raise RuntimeError("The array be empty.")
+    arr = np.ascontiguousarray(arr)
+    buf = CPUBuffer(arr.shape, "i", 8, storage)
+    np.array(buf, copy=False)[...] = arr
     return buf

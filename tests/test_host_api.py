@@ -280,3 +280,26 @@ def test_call_counters_and_tracing_switch():
         with utils.trace_event("b2::convert_dense"):
             pass
     assert pushed == ["b2::convert_dense"] and fake.range_pop.call_count == 1
+
+
+def test_convert_array_and_protocols():
+    """convert_array copies int64 labels into a (pinned, when storage is given) CPUBuffer; the
+    protocol classes recognise the buffers (the reference's tests/cuda/pin_memory_test.py:77-98
+    checks the pinned round trip and the too-small storage)."""
+    import spdl_b200.io as io
+
+    vals = np.arange(-5, 19, dtype=np.int64).reshape(4, 6)
+    buf = io.convert_array(vals)
+    assert buf.shape == (4, 6) and isinstance(buf, io.ArrayInterface)
+    assert not isinstance(buf, io.CUDAArrayInterface)
+    out = io.to_numpy(buf)
+    assert out.dtype == np.int64 and (out == vals).all()
+    assert io.to_numba(buf).tolist() == vals.tolist()  # host buffers need no Numba
+    # non-contiguous input is copied in C order
+    assert (io.to_numpy(io.convert_array(vals.T)) == vals.T).all()
+    with pytest.raises(RuntimeError):
+        io.convert_array(np.zeros((0,), np.int64))
+    with pytest.raises(TypeError):
+        io.convert_array(np.zeros((3,), np.int32))
+    with pytest.raises(RuntimeError):  # storage too small
+        io.convert_array(vals, storage=io.cpu_storage(8, pin_memory=False))

@@ -281,3 +281,22 @@ def test_frame_stage_from_worker_threads():
         dense(np.zeros((2, 7, 8), np.uint8))
     with pytest.raises(RuntimeError):
         io.FrameStage(crop=(8, 8))
+
+
+def test_convert_array_through_pinned_storage_to_the_gpu(cuda_cfg):
+    """tests/cuda/pin_memory_test.py:77-98 of the reference: int64 labels -> pinned CPUBuffer ->
+    transfer_buffer -> tensor on the device; a storage that is too small is an error."""
+    import torch
+
+    import spdl_b200.io as io
+
+    vals = np.arange(0, 10)
+    storage = io.cpu_storage(vals.nbytes, pin_memory=True)
+    buffer = io.convert_array(vals, storage=storage)
+    assert buffer.is_pinned()
+    tensor = io.to_torch(io.transfer_buffer(buffer, device_config=cuda_cfg))
+    assert tensor.shape == (10,) and tensor.dtype == torch.int64
+    assert tensor.device == torch.device(f"cuda:{cuda_cfg.device_index}")
+    assert (vals == tensor.cpu().numpy()).all()
+    with pytest.raises(RuntimeError):
+        io.convert_array(vals, storage=io.cpu_storage(vals.nbytes // 2, pin_memory=True))
