@@ -65,32 +65,8 @@ __device__ __forceinline__ float biased_byte(uint32_t w, int k) {
 // -- the first product pair fused, the last add not.  With the table's zeros this is
 //     R = g*fy + vr*fv          G = fma(g, fy, ug*fu) + vg*fv          B = fma(g, fy, ub*fu)
 // and the four chroma products are shared by the 2x2 quad that shares the chroma sample.
-struct Chroma {
-  float vr, ug, vg, ub;  // vr*fv, ug*fu, vg*fv, ub*fu, each rounded once
-};
-// bu, bv: 2^23 + U, 2^23 + V
-__device__ __forceinline__ Chroma chroma_of(const ColorMat& m, float bu, float bv) {
-  const float fu = __fsub_rn(bu, kTwo23 + 128.0f);
-  const float fv = __fsub_rn(bv, kTwo23 + 128.0f);
-  Chroma c;
-  c.vr = __fmul_rn(m.vr, fv);
-  c.ug = __fmul_rn(m.ug, fu);
-  c.vg = __fmul_rn(m.vg, fv);
-  c.ub = __fmul_rn(m.ub, fu);
-  return c;
-}
-
-// One pixel: the three channel values as fp32, bit-for-bit what the reference kernel holds
-// before its clamp.  `by` is 2^23 + Y.
-__device__ __forceinline__ void pixel_f32(const ColorMat& m, float by, const Chroma& c, float& r,
-                                          float& g, float& b) {
-  const float fy = __fsub_rn(by, m.y_bias);
-  r = __fadd_rn(__fmul_rn(m.g, fy), c.vr);
-  g = __fadd_rn(__fmaf_rn(m.g, fy, c.ug), c.vg);
-  b = __fmaf_rn(m.g, fy, c.ub);
-}
-
-// ---- the same arithmetic, two pixels per instruction -------------------------------------------
+//
+// ---- two pixels per instruction ------------------------------------------------------------------
 // sm_100 has packed fp32 instructions (add/fma on two fp32 lanes of a 64-bit register pair), each
 // lane IEEE-rounded exactly like the scalar instruction.  The vector kernel pairs pixel k of a
 // luma word with pixel k+2: lane x then belongs to the first 2x2 quad under the word, lane y to
@@ -145,7 +121,7 @@ __device__ __forceinline__ Chroma2 chroma2_of(const ColorMat& m, float2 bu, floa
   return c;
 }
 // Two pixels (one per quad): by = {2^23 + Y, 2^23 + Y'}.  Results are the channel values plus
-// 1.5*2^23 rounded toward zero, i.e. floor(x) sits in the low 16 mantissa bits (see quant2).
+// 1.5*2^23 rounded toward zero, i.e. floor(x) sits in the low 16 mantissa bits as a signed halfword (see clamp2_bits).
 __device__ __forceinline__ void pixel2_bits(const ColorMat& m, float2 by, const Chroma2& c,
                                             float2& r, float2& g, float2& b) {
   const float2 g2 = dup2(m.g), magic = dup2(kQuantMagic);
@@ -190,46 +166,6 @@ __device__ __forceinline__ uint32_t pack4_sat(float v0, float v1, float v2, floa
 __device__ __forceinline__ uint32_t clamp2_bits(float a, float b) {
   return __vimin_s16x2_relu(__byte_perm(__float_as_uint(a), __float_as_uint(b), 0x5410u),
                             0x00FF00FFu);
-}
-
-// Truncate-and-clamp of two channel values at once (color_conversion.cu:72-74):
-// x<0 -> 0, x>255 -> 255, else (uint8)x.  Adding 1.5*2^23 with round-toward-zero leaves
-// floor(x) in the low 16 mantissa bits as a signed halfword; one packed min-with-relu clamps
-// both halfwords.  Returns {lo: q(a), hi: q(b)} as two 16-bit lanes holding 0..255.
-__device__ __forceinline__ uint32_t quant2(float a, float b) {
-  const uint32_t qa = __float_as_uint(__fadd_rz(a, kQuantMagic));
-  const uint32_t qb = __float_as_uint(__fadd_rz(b, kQuantMagic));
-  return __vimin_s16x2_relu(__byte_perm(qa, qb, 0x5410u), 0x00FF00FFu);
-}
-// Four bytes from two quant2 results: {p.lo, p.hi, q.lo, q.hi}.
-__device__ __forceinline__ uint32_t bytes4(uint32_t p, uint32_t q) {
-  return __byte_perm(p, q, 0x6420u);
-}
-// One pixel straight to three integers (scalar path of the generic kernels).
-__device__ __forceinline__ void pixel_u8(const ColorMat& m, int y, int u, int v, int& r, int& g,
-                                         int& b) {
-  Chroma c = chroma_of(m, kTwo23 + (float)u, kTwo23 + (float)v);
-  float fr, fg, fb;
-  pixel_f32(m, kTwo23 + (float)y, c, fr, fg, fb);
-  const uint32_t rg = quant2(fr, fg), bb = quant2(fb, fb);
-  r = rg & 0xFFFF;
-  g = rg >> 16;
-  b = bb & 0xFFFF;
-}
-
-template <typename T>
-__device__ __forceinline__ T finish(float v, float s, float b);
-template <>
-__device__ __forceinline__ float finish<float>(float v, float s, float b) {
-  return __fmaf_rn(v, s, b);
-}
-template <>
-__device__ __forceinline__ __nv_bfloat16 finish<__nv_bfloat16>(float v, float s, float b) {
-  return __float2bfloat16_rn(__fmaf_rn(v, s, b));
-}
-template <>
-__device__ __forceinline__ uint8_t finish<uint8_t>(float v, float, float) {
-  return (uint8_t)(int)v;
 }
 
 template <int DTYPE>

@@ -84,7 +84,7 @@ constexpr float kTapScale = 16777216.0f;  // 2^24
 __device__ __forceinline__ float2 halves_to_float2(uint32_t lanes) {
   return __half22float2(*reinterpret_cast<const __half2*>(&lanes));
 }
-// {row0, row1} channel values after the truncating clamp (see quant2), scaled by 2^-24.
+// {row0, row1} channel values after the truncating clamp (see clamp2_bits), scaled by 2^-24.
 __device__ __forceinline__ float2 clamp_to_float2(float2 bits) {
   return halves_to_float2(clamp2_bits(bits.x, bits.y));
 }
