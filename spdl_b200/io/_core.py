@@ -349,6 +349,60 @@ def convert_resize(base: Any, descs: Any, *, out_size: tuple[int, int], max_src_
     return out
 
 
+class _DeviceSpan:
+    """A bare device address range, for ``convert_resize`` over images that live in separate
+    allocations (their descriptors hold offsets from the lowest address)."""
+
+    def __init__(self, ptr: int, nbytes: int, device_index: int) -> None:
+        self.device_index = device_index
+        self.__cuda_array_interface__ = {"version": 2, "shape": (int(nbytes),), "typestr": "|u1",
+                                         "data": (int(ptr), False), "strides": None}
+
+
+def resize_image_list(images: Sequence[Any], *, device_config: CUDAConfig,
+                      src_format: str = "rgb24", resize: tuple[int, int] | None = None,
+                      resize_shorter: int | None = None, crop: tuple[int, int] | None = None,
+                      layout: str = "NCHW", dtype: str = "uint8", order: str = "rgb", mean=None,
+                      std=None, sync: bool = False) -> CUDABuffer:
+    """Resize, crop and normalise a list of decoded images of different sizes in one launch.
+
+    ``images`` are device arrays (anything with ``__cuda_array_interface__``: the buffers a JPEG
+    decoder returns, torch tensors), each C-contiguous ``uint8``: ``[H, W, 3]`` for
+    ``src_format="rgb24"``, ``[3, H, W]`` for ``"rgb_planar"``.  They are read where they lie
+    -- nothing is packed or copied -- and the result is one ``[N,3,h,w]`` / ``[N,h,w,3]`` batch.
+    This is what follows the decoder in the reference's ``load_image_batch_nvjpeg``
+    (``src/spdl/io/_composite.py:486-524``: decode, resize one image at a time with NPP, stack).
+    """
+    fmt = src_format.lower()
+    if fmt not in ("rgb24", "rgb_planar"):
+        raise RuntimeError(f"Unsupported source format for an image list: {src_format}")
+    if len(images) == 0:
+        raise RuntimeError("The image list is empty.")
+    ptrs, ws, hs = [], [], []
+    for img in images:
+        ptr, shape, typestr = _cai(img)
+        if typestr not in ("|u1", "<u1", "=u1") or len(shape) != 3:
+            raise RuntimeError(f"Images must be 3-D uint8 arrays, got {typestr} {tuple(shape)}")
+        h, w, c = shape if fmt == "rgb24" else (shape[1], shape[2], shape[0])
+        if c != 3:
+            raise RuntimeError(f"Images must have three channels, got shape {tuple(shape)}")
+        _device_of(img, device_config)
+        ptrs.append(ptr)
+        ws.append(w)
+        hs.append(h)
+    base = min(ptrs)
+    end = max(p + 3 * w * h for p, w, h in zip(ptrs, ws, hs))
+    descs, out_size = make_image_descs(ws, hs, src_format=fmt, offsets=[p - base for p in ptrs],
+                                       resize=resize, resize_shorter=resize_shorter, crop=crop)
+    table = transfer_buffer(descs.view(np.uint8), device_config=device_config)
+    out = convert_resize(_DeviceSpan(base, end - base, device_config.device_index), table,
+                         out_size=out_size, max_src_w=max(ws), device_config=device_config,
+                         src_format=fmt, layout=layout, dtype=dtype, order=order, mean=mean,
+                         std=std, sync=sync)
+    out._owner = (list(images), table)  # inputs must outlive the queued kernel
+    return out
+
+
 # ---- transfer ----------------------------------------------------------------------------------
 
 _NP_CLASS = {"u": "u", "i": "i", "f": "f", "b": "u"}

@@ -243,3 +243,32 @@ def test_sharded_clips_equal_whole(cuda_cfg):
         got, _ = _run(cuda_cfg, mine.reshape(-1), d, out, "nv12", "NCHW", "uint8", coeff=6)
         parts.append(got.reshape(hi - lo, t, 3, 32, 32))
     assert (np.concatenate(parts) == whole.reshape(clips, t, 3, 32, 32)).all()
+
+
+@pytest.mark.parametrize("fmt", ["rgb24", "rgb_planar"])
+def test_resize_image_list_reads_images_where_they_lie(cuda_cfg, fmt):
+    """Separately allocated device images of different sizes (a decoder's output list) go through
+    one launch without being packed; the result equals the oracle on a packed copy."""
+    import torch
+
+    import spdl_b200.io as io
+
+    rng = np.random.default_rng(33)
+    ws, hs = rng.integers(40, 160, 7), rng.integers(40, 160, 7)
+    host = [rng.integers(0, 256, (h, w, 3) if fmt == "rgb24" else (3, h, w), dtype=np.uint8)
+            for w, h in zip(ws, hs)]
+    images = [torch.from_numpy(a).cuda() for a in host]
+    got = io.to_torch(io.resize_image_list(images, device_config=cuda_cfg, src_format=fmt,
+                                           resize_shorter=48, crop=(40, 32), dtype="float32",
+                                           mean=MEAN, std=STD, sync=True)).cpu().numpy()
+    packed = np.concatenate([a.reshape(-1) for a in host])
+    descs, out = io.make_image_descs(ws, hs, src_format=fmt, resize_shorter=48, crop=(40, 32))
+    want = oracle.convert_resize(packed, descs, out_w=out[0], out_h=out[1],
+                                 src_format=oracle.RGBI if fmt == "rgb24" else oracle.RGBP,
+                                 dtype=oracle.F32, sb=oracle.scale_bias(MEAN, STD))
+    _compare(got, want, "float32")
+    with pytest.raises(RuntimeError):
+        io.resize_image_list([], device_config=cuda_cfg, resize=(8, 8))
+    with pytest.raises(RuntimeError):
+        io.resize_image_list([images[0][..., :2].contiguous()], device_config=cuda_cfg,
+                             resize=(8, 8))
