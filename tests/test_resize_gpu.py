@@ -272,3 +272,80 @@ def test_resize_image_list_reads_images_where_they_lie(cuda_cfg, fmt):
     with pytest.raises(RuntimeError):
         io.resize_image_list([images[0][..., :2].contiguous()], device_config=cuda_cfg,
                              resize=(8, 8))
+
+
+def _sample_against_oracle(got, base_host, descs, picks, out, fmt, dtype, **kw):
+    """Oracle on a few images of a large batch: their descriptors still point into the shared
+    buffer, so the oracle reads exactly the bytes the kernel read."""
+    sub = descs[picks].copy()
+    want = oracle.convert_resize(
+        base_host, sub, out_w=out[0], out_h=out[1],
+        src_format={"nv12": oracle.NV12, "i420": oracle.I420}[fmt], dtype=_O_DT[dtype], **kw)
+    _compare(got[picks], want, dtype)
+
+
+def test_full_size_ragged_i420_batch(cuda_cfg):
+    """2048 ragged I420 images (256..1024, full-range BT.601) -> shorter side 256, centre crop
+    224x224, fp32 normalised: a sample of images against the oracle, and the whole batch against
+    itself run as 8 contiguous shards."""
+    import spdl_b200.io as io
+    from spdl_b200.sharding import shard_range
+
+    n = 2048
+    data, ws, hs, offs = synth.ragged_i420(n)
+    descs, out = io.make_image_descs(ws, hs, src_format="i420", offsets=offs,
+                                     resize_shorter=256, crop=(224, 224))
+    assert out == (224, 224)
+    base = _dev(data)
+    kw = dict(out_size=out, max_src_w=int(ws.max()), device_config=cuda_cfg, src_format="i420",
+              coeff=6, full_range=True, dtype="float32", mean=MEAN, std=STD, sync=True)
+    whole = io.to_torch(io.convert_resize(base, _dev(descs.view(np.uint8)), **kw))
+    picks = np.array([0, 1, 511, 1024, 2047, int(np.argmax(ws)), int(np.argmin(hs))])
+    _sample_against_oracle(whole.cpu().numpy(), data, descs, picks, out, "i420", "float32",
+                           coeff=6, full_range=True, sb=oracle.scale_bias(MEAN, STD))
+    for r in range(8):
+        lo, hi = shard_range(n, r, 8)
+        part = io.to_torch(io.convert_resize(base, _dev(descs[lo:hi].copy().view(np.uint8)), **kw))
+        assert bool((part == whole[lo:hi]).all())
+
+
+def test_full_size_clip_batch(cuda_cfg):
+    """64 clips x 16 frames of 1280x720 NV12 -> 256x256 u8, BT.601, stacked N x T x C x H x W:
+    sampled frames against the oracle (bit-exact) and clip 8r..8r+8 of rank r against the whole."""
+    import torch
+
+    import spdl_b200.io as io
+
+    clips, t, w, h = 64, 16, 1280, 720
+    g = torch.Generator(device="cuda").manual_seed(4000)
+    src = torch.randint(16, 236, (clips * t, h * 3 // 2, w), dtype=torch.uint8, device="cuda",
+                        generator=g)
+    descs, out = io.make_image_descs([w] * clips * t, [h] * clips * t, resize=(256, 256))
+    kw = dict(out_size=out, max_src_w=w, device_config=cuda_cfg, src_format="nv12", coeff=6,
+              sync=True)
+    whole = io.to_torch(io.convert_resize(src, _dev(descs.view(np.uint8)), **kw))
+    assert tuple(whole.reshape(clips, t, 3, 256, 256).shape) == (clips, t, 3, 256, 256)
+    picks = np.array([0, 17, 500, 1023])
+    frames = src[torch.from_numpy(picks).cuda()].cpu().numpy()
+    d4, _ = io.make_image_descs([w] * 4, [h] * 4, resize=(256, 256))
+    want = oracle.convert_resize(frames.reshape(-1), d4, out_w=256, out_h=256, coeff=6)
+    assert (whole[torch.from_numpy(picks).cuda()].cpu().numpy() == want).all()
+    per = clips // 8 * t  # frames per rank
+    d_rank, _ = io.make_image_descs([w] * per, [h] * per, resize=(256, 256))
+    d_rank_dev = _dev(d_rank.view(np.uint8))
+    for r in (0, 3, 7):
+        part = io.to_torch(io.convert_resize(src[r * per:(r + 1) * per], d_rank_dev, **kw))
+        assert bool((part == whole[r * per:(r + 1) * per]).all())
+
+
+def test_full_size_4k_batch(cuda_cfg):
+    """16 x 3840x2160 NV12 -> 224x224 bf16 NCHW normalised (BGR planes): every image against the
+    oracle."""
+    import spdl_b200.io as io
+
+    n, w, h = 16, 3840, 2160
+    nv = synth.nv12_batch(n, w, h, config=3)
+    descs, out = io.make_image_descs([w] * n, [h] * n, resize=(224, 224))
+    got, want = _run(cuda_cfg, nv.reshape(-1), descs, out, "nv12", "NCHW", "bfloat16", order="bgr",
+                     mean=MEAN[::-1], std=STD[::-1])
+    _compare(got, want, "bfloat16")
