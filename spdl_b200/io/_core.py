@@ -229,7 +229,9 @@ def convert_nv12(buffers: Any, *, device_config: CUDAConfig, coeff: int = 1,
 def make_image_descs(widths: Sequence[int], heights: Sequence[int], *, src_format: str = "nv12",
                      offsets: Sequence[int] | None = None, resize: tuple[int, int] | None = None,
                      resize_shorter: int | None = None, crop: tuple[int, int] | None = None,
-                     out_size: tuple[int, int] | None = None) -> tuple[np.ndarray, tuple[int, int]]:
+                     out_size: tuple[int, int] | None = None,
+                     src_crop: tuple[int, int, int, int] | None = None
+                     ) -> tuple[np.ndarray, tuple[int, int]]:
     """Build the descriptor table of a (possibly ragged) packed batch.
 
     Images are packed back to back (``offsets[i]`` = byte offset of image ``i``; computed when
@@ -239,6 +241,10 @@ def make_image_descs(widths: Sequence[int], heights: Sequence[int], *, src_forma
     Geometry: ``resize=(w, h)`` stretches every image to that size; ``resize_shorter=s`` scales
     the shorter side to ``s`` and the longer to ``int(s * long / short)``; then
     ``crop=(w, h)`` takes the centre window with offset ``int(round((dim - crop) / 2))``.
+    ``src_crop=(left, top, right, bottom)`` first cuts that many pixels off each side of every
+    source image, the order of the reference's decoder options (crop, then scale:
+    ``src/libspdl/cuda/nvdec/detail/utils.cpp:133-220``); for NV12/I420 the four values must be
+    even, as the decoder requires (``src/libspdl/cuda/nvdec/decoder.cpp:29-64``).
     Returns ``(descs, (out_w, out_h))``.
     """
     w = np.asarray(widths, np.int64)
@@ -251,6 +257,12 @@ def make_image_descs(widths: Sequence[int], heights: Sequence[int], *, src_forma
     n = len(w)
     cw, chh = (w + 1) // 2, (h + 1) // 2
     frame_bytes = 3 * w * h if fmt in (RGB_PLANAR, RGB_INTERLEAVED) else w * h + 2 * cw * chh
+    w0, h0 = w, h  # full image size: fixes the plane layout; (w, h) below is the source window
+    if src_crop is not None:
+        w = w0 - int(src_crop[0]) - int(src_crop[2])
+        h = h0 - int(src_crop[1]) - int(src_crop[3])
+        if np.any(w < 1) or np.any(h < 1):
+            raise RuntimeError("src_crop leaves nothing of an image")
     if offsets is None:
         off = np.concatenate([[0], np.cumsum(frame_bytes)[:-1]]) if n else np.zeros(0, np.int64)
     else:
@@ -281,20 +293,46 @@ def make_image_descs(widths: Sequence[int], heights: Sequence[int], *, src_forma
         raise RuntimeError(f"out_size {out_size} does not match the geometry {(ow, oh)}")
     d = np.zeros(n, DESC_DTYPE)
     d["y_off"] = off
-    d["u_off"] = off + w * h
-    d["y_pitch"] = w
+    d["u_off"] = off + w0 * h0
+    d["y_pitch"] = w0
     if fmt == NV12:
         d["uv_pitch"] = 2 * cw
     elif fmt == I420:
-        d["v_off"] = off + w * h + cw * chh
+        d["v_off"] = off + w0 * h0 + cw * chh
         d["uv_pitch"] = cw
     elif fmt == RGB_PLANAR:
-        d["v_off"] = off + 2 * w * h
-        d["uv_pitch"] = w
+        d["v_off"] = off + 2 * w0 * h0
+        d["uv_pitch"] = w0
     else:
         d["u_off"] = 0
-        d["y_pitch"] = 3 * w
+        d["y_pitch"] = 3 * w0
     d["src_w"], d["src_h"] = w, h
+    if src_crop is not None:
+        left, top, right, bottom = (int(v) for v in src_crop)
+        if min(left, top, right, bottom) < 0:
+            raise RuntimeError("src_crop values must be non-negative")
+        yuv = fmt in (NV12, I420)
+        if yuv and any(v % 2 for v in (left, top, right, bottom)):
+            raise RuntimeError("src_crop values must be even for NV12/I420 sources")
+        if np.any(w0 - left - right < 1) or np.any(h0 - top - bottom < 1):
+            raise RuntimeError("src_crop leaves nothing of an image")
+        # move the plane origins to the window's top-left corner; pitches stay those of the
+        # full image
+        def shift(name: str, delta) -> None:
+            d[name] = d[name].astype(np.int64) + np.asarray(delta, np.int64)
+
+        if fmt == RGB_INTERLEAVED:
+            shift("y_off", top * 3 * w0 + 3 * left)
+        else:
+            shift("y_off", top * w0 + left)
+        if fmt == NV12:
+            shift("u_off", (top // 2) * 2 * cw + left)
+        elif fmt == I420:
+            shift("u_off", (top // 2) * cw + left // 2)
+            shift("v_off", (top // 2) * cw + left // 2)
+        elif fmt == RGB_PLANAR:
+            shift("u_off", top * w0 + left)
+            shift("v_off", top * w0 + left)
     d["crop_x"], d["crop_y"] = cx, cy
     d["scale_x"] = w.astype(np.float32) / rw.astype(np.float32)
     d["scale_y"] = h.astype(np.float32) / rh.astype(np.float32)

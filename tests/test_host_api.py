@@ -303,3 +303,30 @@ def test_convert_array_and_protocols():
         io.convert_array(np.zeros((3,), np.int32))
     with pytest.raises(RuntimeError):  # storage too small
         io.convert_array(vals, storage=io.cpu_storage(8, pin_memory=False))
+
+
+def test_source_window_of_make_image_descs():
+    """``src_crop`` cuts the source first (the decoder's crop-then-scale order): through the oracle
+    the result equals resizing a cropped copy; odd values are refused for YUV sources."""
+    import oracle
+    import spdl_b200.io as io
+    from tests import synth
+
+    w, h, crop = 96, 64, (8, 4, 12, 6)
+    nv = synth.nv12_batch(2, w, h, config=9, index=3)
+    d, out = io.make_image_descs([w, w], [h, h], resize=(40, 30), src_crop=crop)
+    assert out == (40, 30) and d["src_w"].tolist() == [76, 76] and d["src_h"].tolist() == [54, 54]
+    assert d["y_pitch"].tolist() == [w, w]
+    got = oracle.convert_resize(nv.reshape(-1), d, out_w=40, out_h=30)
+    cropped = np.concatenate([np.concatenate([f[:h][4:h - 6, 8:w - 12].reshape(-1),
+                                              f[h:][2:(h - 6) // 2, 8:w - 12].reshape(-1)])
+                              for f in nv])
+    d2, _ = io.make_image_descs([76, 76], [54, 54], resize=(40, 30))
+    assert (got == oracle.convert_resize(cropped, d2, out_w=40, out_h=30)).all()
+    with pytest.raises(RuntimeError):
+        io.make_image_descs([w], [h], resize=(8, 8), src_crop=(1, 0, 0, 0))
+    with pytest.raises(RuntimeError):
+        io.make_image_descs([w], [h], resize=(8, 8), src_crop=(48, 0, 48, 0))
+    # RGB sources take any window
+    d3, _ = io.make_image_descs([w], [h], src_format="rgb24", resize=(8, 8), src_crop=(1, 3, 5, 7))
+    assert int(d3["y_off"][0]) == 3 * 3 * w + 3 and int(d3["src_w"][0]) == w - 6

@@ -349,3 +349,28 @@ def test_full_size_4k_batch(cuda_cfg):
     got, want = _run(cuda_cfg, nv.reshape(-1), descs, out, "nv12", "NCHW", "bfloat16", order="bgr",
                      mean=MEAN[::-1], std=STD[::-1])
     _compare(got, want, "bfloat16")
+
+
+@pytest.mark.parametrize("fmt", ["nv12", "i420", "rgb24", "rgb_planar"])
+def test_source_window_then_resize(cuda_cfg, fmt):
+    """Crop the source, then scale (the decoder's order): kernel against the oracle through the
+    same descriptors."""
+    import spdl_b200.io as io
+
+    rng = np.random.default_rng(44)
+    n = 5
+    ws, hs = rng.integers(30, 100, n) * 2, rng.integers(30, 100, n) * 2
+    yuv = fmt in ("nv12", "i420")
+    sizes = ws * hs * 3 // 2 if yuv else 3 * ws * hs
+    data = rng.integers(0, 256, int(sizes.sum()), dtype=np.uint8)
+    descs, out = io.make_image_descs(ws, hs, src_format=fmt, resize=(48, 36),
+                                     src_crop=(6, 2, 10, 4), crop=(40, 30))
+    buf = io.convert_resize(_dev(data), _dev(descs.view(np.uint8)), out_size=out,
+                            max_src_w=int(ws.max()), device_config=cuda_cfg, src_format=fmt,
+                            layout="NHWC", sync=True)
+    got = io.to_torch(buf).cpu().numpy()
+    want = oracle.convert_resize(
+        data, descs, out_w=out[0], out_h=out[1], layout=oracle.NHWC,
+        src_format={"nv12": oracle.NV12, "i420": oracle.I420, "rgb24": oracle.RGBI,
+                    "rgb_planar": oracle.RGBP}[fmt])
+    assert (got == want).all()
