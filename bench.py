@@ -433,7 +433,7 @@ def run_ours(args) -> None:
             "clocks": clocks.summary() if clocks is not None else None,
         }
         if info.world_size == 1:
-            line["cpu_baseline"] = {k: v for k, v in time_cpu(N_FRAMES, 5, 1, 15.0).items()
+            line["cpu_baseline"] = {k: v for k, v in time_cpu(N_FRAMES, 200, 2, 20.0).items()
                                     if k not in ("ms_per_step", "frames_per_step")}
             ref = reference_kernel_fps(torch, inputs[0], cfg)
             if ref is not None:
