@@ -5,6 +5,8 @@ channel order, matrix, range, odd and unaligned sizes, up- and down-scaling, cro
 per case so a failure can be replayed.
 """
 
+import os
+
 import numpy as np
 import pytest
 
@@ -115,3 +117,14 @@ def test_resize_random_cases(cuda_cfg, seed):
         dtype=_O_DT[dtype], order=oracle.RGB if order == "rgb" else oracle.BGR,
         sb=oracle.scale_bias(MEAN, STD) if norm else None)
     _check(got, want, dtype)
+
+
+@pytest.mark.skipif(not os.environ.get("B2_FUZZ_SWEEP"),
+                    reason="set B2_FUZZ_SWEEP=first:last to run the long sweep")
+def test_long_sweep(cuda_cfg):
+    """The two sweeps above over an arbitrary seed range, e.g. ``B2_FUZZ_SWEEP=64:30000`` (about
+    0.7 ms per case on a B200)."""
+    first, last = (int(v) for v in os.environ["B2_FUZZ_SWEEP"].split(":"))
+    for seed in range(first, last):
+        test_dense_random_cases(cuda_cfg, seed)
+        test_resize_random_cases(cuda_cfg, seed)
