@@ -128,3 +128,96 @@ def test_long_sweep(cuda_cfg):
     for seed in range(first, last):
         test_dense_random_cases(cuda_cfg, seed)
         test_resize_random_cases(cuda_cfg, seed)
+        test_dense_random_memory_layouts(cuda_cfg, seed)
+
+
+@pytest.mark.parametrize("seed", range(48))
+def test_dense_random_memory_layouts(cuda_cfg, seed):
+    """Through the C ABI with surfaces at random byte offsets behind a pointer table or a random
+    source pitch, and a destination at a random element offset with a random frame stride: every
+    alignment path of the dense kernels against the oracle, with sentinel checks around the
+    output."""
+    import ctypes
+
+    import torch
+
+    from spdl_b200 import _lib
+
+    r = np.random.default_rng(12000 + seed)
+    n = int(r.integers(1, 4))
+    w = int(r.choice([16, 32, 48, 64, 100, 130, 200, 31, 854]))
+    h = int(r.integers(1, 9)) * 2
+    h2 = h * 3 // 2
+    layout = str(r.choice(["NCHW", "NHWC"]))
+    dtype = str(r.choice(["uint8", "float32", "bfloat16"]))
+    esz = {"uint8": 1, "bfloat16": 2, "float32": 4}[dtype]
+    table = bool(r.integers(0, 2))
+    pitch = w + int(r.choice([0, 0, 16, 6, 1]))
+    nv = synth.nv12_batch(n, w, h, config=9, index=seed, full_range=True)
+    pitched = np.full((n, h2, pitch), 0x33, np.uint8)
+    pitched[:, :, :w] = nv
+    a = _lib.DenseArgs()
+    a.struct_size = ctypes.sizeof(_lib.DenseArgs)
+    a.device = cuda_cfg.device_index
+    keep = []
+    if table:
+        ptrs = []
+        for i in range(n):
+            off = int(r.integers(0, 16))
+            t = torch.zeros(h2 * pitch + 32, dtype=torch.uint8, device="cuda")
+            t[off:off + h2 * pitch] = torch.from_numpy(pitched[i].reshape(-1)).cuda()
+            keep.append(t)
+            ptrs.append(t.data_ptr() + off)
+        ytab = torch.tensor(ptrs, dtype=torch.int64, device="cuda")
+        utab = ytab + h * pitch
+        keep += [ytab, utab]
+        a.y_table, a.u_table = ytab.data_ptr(), utab.data_ptr()
+    else:
+        off = int(r.integers(0, 16))
+        t = torch.zeros(pitched.size + 32, dtype=torch.uint8, device="cuda")
+        t[off:off + pitched.size] = torch.from_numpy(pitched.reshape(-1)).cuda()
+        keep.append(t)
+        a.y, a.u = t.data_ptr() + off, t.data_ptr() + off + h * pitch
+        a.y_frame_stride = a.uv_frame_stride = h2 * pitch
+    a.y_pitch = a.uv_pitch = pitch
+    a.src_format, a.width, a.height, a.num_frames = _lib.NV12, w, h, n
+    a.matrix_coeff, a.full_range = 1, int(r.integers(0, 2))
+    frame = 3 * h * w
+    stride = frame + int(r.choice([0, 0, 16, 7, 2]))
+    dst_off = int(r.integers(0, 4))
+    tdt = {"uint8": torch.uint8, "bfloat16": torch.int16, "float32": torch.int32}[dtype]
+    sentinel = {1: 0xA5, 2: 0x5A5A, 4: 0x5A5A5A5A}[esz]
+    buf = torch.full((dst_off + n * stride + 8,), sentinel, dtype=tdt, device="cuda")
+    a.dst, a.dst_frame_stride = buf.data_ptr() + dst_off * esz, stride
+    a.layout = _lib.NCHW if layout == "NCHW" else _lib.NHWC
+    a.dtype = {"uint8": _lib.U8, "bfloat16": _lib.BF16, "float32": _lib.F32}[dtype]
+    a.order = _lib.RGB
+    sb = oracle.scale_bias(MEAN, STD) if dtype != "uint8" else oracle.scale_bias()
+    a.scale = (ctypes.c_float * 3)(*[float(x) for x in sb[:3]])
+    a.bias = (ctypes.c_float * 3)(*[float(x) for x in sb[3:]])
+    _lib.check(_lib.lib().b2_convert_dense(ctypes.byref(a), torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    got = buf.cpu().numpy()
+    want = oracle.convert_dense(
+        nv, nv.reshape(-1)[h * w:], None, width=w, height=h, num_frames=n, y_pitch=w, uv_pitch=w,
+        y_frame_stride=h2 * w, uv_frame_stride=h2 * w, src_format=oracle.NV12,
+        layout=oracle.NCHW if layout == "NCHW" else oracle.NHWC, dtype=_O_DT[dtype],
+        full_range=bool(a.full_range), sb=sb)
+    we = w & ~1
+    shape = (3, h, w) if layout == "NCHW" else (h, w, 3)
+    cols = (slice(None), slice(None), slice(0, we)) if layout == "NCHW" else \
+        (slice(None), slice(0, we))
+    assert (got[:dst_off] == sentinel).all()
+    for i in range(n):
+        lo = dst_off + i * stride
+        body = got[lo:lo + frame].reshape(shape)
+        if dtype == "float32":
+            np.testing.assert_allclose(body[cols].view(np.float32), want[i][cols], rtol=1e-6,
+                                       atol=1e-6)
+        else:
+            assert (body[cols].view(want.dtype) == want[i][cols]).all()
+        if w & 1:
+            tail = body[..., w - 1] if layout == "NCHW" else body[:, w - 1]
+            assert (tail == sentinel).all()
+        assert (got[lo + frame:lo + stride] == sentinel).all()
+    assert (got[dst_off + n * stride:] == sentinel).all()
