@@ -1,6 +1,8 @@
 """Benchmark of the post-decode frame path: 1080p NV12 -> interleaved RGB, frames/s.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--scaling weak|strong] [--workload c2|c3|c4|c5|j5|aux] [--scale F]
+                    [--kernel-only] [--no-numa]
 
 One "step" converts one batch of 64 synthetic 1920x1080 NV12 frames (BT.709 limited range) to
 interleaved RGB u8 with a single kernel launch.  Inputs are seeded synthetic frames with the
