@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define B2_ABI_VERSION 1
+#define B2_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define B2_API __attribute__((visibility("default")))
@@ -55,6 +55,17 @@ enum b2_src_format {
 enum b2_layout { B2_NCHW = 0, B2_NHWC = 1 };
 enum b2_dtype { B2_U8 = 0, B2_F32 = 1, B2_BF16 = 2 };
 enum b2_order { B2_RGB = 0, B2_BGR = 1 };
+/* Which arithmetic turns (Y,U,V) into 8-bit RGB.
+ *   B2_ARITH_REFERENCE  the reference's CUDA kernel: fp32 matrix product, truncation
+ *                       (src/libspdl/cuda/detail/color_conversion.cu:20-86).  The default.
+ *   B2_ARITH_SWSCALE    the reference's CPU route: the integer arithmetic of libswscale's
+ *                       unscaled yuv420p -> rgb24 converter, which the filter graph built by
+ *                       src/libspdl/core/detail/ffmpeg/filter_graph.cpp:50-65 from
+ *                       "format=pix_fmts=rgb24" (src/spdl/io/_preprocessing.py:250-251) ends in.
+ *                       matrix_coeff is then the colourspace number sws_getCoefficients() takes
+ *                       (1 BT.709, 4 FCC, 5/6 BT.601, 7 SMPTE 240M, 9/10 BT.2020, anything else
+ *                       BT.601) and full_range its srcRange. */
+enum b2_arith { B2_ARITH_REFERENCE = 0, B2_ARITH_SWSCALE = 1 };
 
 /* Message for the last failure on the calling thread ("" if none). */
 B2_API const char* b2_last_error(void);
@@ -126,6 +137,11 @@ typedef struct b2_dense_args {
   int64_t dst_frame_stride; /* elements between frames; 0 = packed (3*height*width)         */
   int32_t layout, dtype, order;
   float scale[3], bias[3];
+  int32_t reserved0;        /* tail padding of the version-1 struct; ignored                */
+  /* --- fields of ABI version 2: a caller whose struct_size is that of version 1 (168) gets
+   *     zeros for them --- */
+  int32_t arith;            /* b2_arith                                                      */
+  int32_t reserved1;
 } b2_dense_args;
 
 B2_API int b2_convert_dense(const b2_dense_args* args, void* stream);
@@ -148,9 +164,13 @@ typedef struct b2_image_desc {
   uint64_t y_off, u_off, v_off; /* byte offsets of the planes from `base`                   */
   int32_t y_pitch, uv_pitch;
   int32_t src_w, src_h;
-  int32_t crop_x, crop_y;       /* where output (0,0) sits in the resized grid              */
+  int32_t crop_x, crop_y;       /* where output (0,0) sits in the resized grid; negative when
+                                 * the resized image is smaller than the output (letterbox)  */
   float scale_x, scale_y;       /* source size / resized size                               */
-  int32_t reserved[2];
+  int32_t resized_w, resized_h; /* size of the resized grid; output pixels that fall outside
+                                 * it take args->pad_value.  0 = unbounded (version 1: these
+                                 * were reserved zeros), every output pixel maps into the
+                                 * image with edge clamping                                  */
 } b2_image_desc;                /* 64 bytes */
 
 typedef struct b2_resize_args {
@@ -166,7 +186,40 @@ typedef struct b2_resize_args {
   void* dst;
   int64_t dst_image_stride;     /* elements; 0 = packed                                     */
   float scale[3], bias[3];
+  /* --- fields of ABI version 2: a caller whose struct_size is that of version 1 (104) gets
+   *     zeros for them --- */
+  int32_t arith;                /* b2_arith (YUV sources)                                   */
+  /* Clip stacking.  With frames_per_group = T > 1, image i is frame t = i % T of group
+   * g = i / T and starts at element g * dst_group_stride + t * dst_image_stride; with
+   * dst_plane_stride (NCHW: elements between the colour planes of one image; 0 = out_h*out_w)
+   * this writes the [N, C, T, H, W] layout of examples/video_classification/utils/pipeline.py:137
+   * directly (image stride H*W, plane stride T*H*W, group stride 3*T*H*W). */
+  int32_t frames_per_group;
+  int64_t dst_plane_stride;
+  int64_t dst_group_stride;
+  /* Letterbox colour as R, G, B on the 0..255 scale, for output pixels outside an image's
+   * resized grid (see b2_image_desc.resized_w); it passes through the same rounding /
+   * scale / bias as every other pixel.  The reference pads with a colour name
+   * (src/spdl/io/_preprocessing.py:220-223), black by default. */
+  float pad_value[3];
+  int32_t debug_flags;          /* B2_DEBUG_*; 0 in production                               */
+  /* Optional device word (may be null).  The kernel ORs B2_STATUS_* bits into it when it leaves
+   * an image or a tile of output rows unwritten; the caller clears it before the call and reads
+   * it after the stream has run.  The call itself still returns B2_OK: the host cannot see the
+   * descriptor table, which lives in device memory. */
+  int32_t* status;
 } b2_resize_args;
+
+enum b2_resize_status_bits {
+  B2_STATUS_IMAGE_TOO_WIDE = 1, /* a descriptor needs more staging than max_src_w provides:
+                                 * the image was skipped                                     */
+  B2_STATUS_WAIT_EXPIRED = 2,   /* a bounded wait for staged rows ran out: the tile was skipped */
+  B2_STATUS_BAD_GEOMETRY = 4    /* src_w/src_h < 1 or a non-positive / non-finite scale: skipped */
+};
+/* B2_DEBUG_EXPIRE_WAIT: after its rows have arrived, every tile also waits (bounded, a few
+ * polls) on a barrier that nothing completes, so that the give-up path can be tested without
+ * any copy in flight.  Outputs stay untouched and B2_STATUS_WAIT_EXPIRED is reported. */
+enum b2_debug_flags { B2_DEBUG_EXPIRE_WAIT = 1 };
 
 B2_API int b2_convert_resize(const b2_resize_args* args, void* stream);
 

@@ -29,6 +29,8 @@ NCHW, NHWC = 0, 1
 U8, F32, BF16 = 0, 1, 2
 RGB, BGR = 0, 1
 FMA_NONE, FMA_LUMA_FIRST, FMA_CHROMA_FIRST, FMA_DEVICE = 0, 1, 2, 4
+#: which arithmetic converts a pixel: the reference's CUDA kernel, or libswscale's integers
+ARITH_REFERENCE, ARITH_SWSCALE = 0, 1
 
 #: The fusion order that reproduces the reference kernel as nvcc compiles it for
 #: sm_100a (checked on a B200 over all 256^3 inputs; see tests/golden).
@@ -65,6 +67,7 @@ class _DenseArgs(ctypes.Structure):
         ("dst", ctypes.c_void_p), ("dst_frame_stride", ctypes.c_int64),
         ("layout", ctypes.c_int32), ("dtype", ctypes.c_int32), ("order", ctypes.c_int32),
         ("scale_bias", ctypes.c_float * 6),
+        ("arith", ctypes.c_int32),
     ]
 
 
@@ -77,14 +80,14 @@ class ImageDesc(ctypes.Structure):
         ("src_w", ctypes.c_int32), ("src_h", ctypes.c_int32),
         ("crop_x", ctypes.c_int32), ("crop_y", ctypes.c_int32),
         ("scale_x", ctypes.c_float), ("scale_y", ctypes.c_float),
-        ("reserved", ctypes.c_int32 * 2),
+        ("resized_w", ctypes.c_int32), ("resized_h", ctypes.c_int32),
     ]
 
 
 DESC_DTYPE = np.dtype(
     [("y_off", "<u8"), ("u_off", "<u8"), ("v_off", "<u8"), ("y_pitch", "<i4"), ("uv_pitch", "<i4"),
      ("src_w", "<i4"), ("src_h", "<i4"), ("crop_x", "<i4"), ("crop_y", "<i4"),
-     ("scale_x", "<f4"), ("scale_y", "<f4"), ("reserved", "<i4", (2,))]
+     ("scale_x", "<f4"), ("scale_y", "<f4"), ("resized_w", "<i4"), ("resized_h", "<i4")]
 )
 assert DESC_DTYPE.itemsize == 64 == ctypes.sizeof(ImageDesc)
 
@@ -98,6 +101,9 @@ class _ResizeArgs(ctypes.Structure):
         ("layout", ctypes.c_int32), ("dtype", ctypes.c_int32), ("order", ctypes.c_int32),
         ("dst", ctypes.c_void_p), ("dst_image_stride", ctypes.c_int64),
         ("scale_bias", ctypes.c_float * 6),
+        ("arith", ctypes.c_int32), ("frames_per_group", ctypes.c_int32),
+        ("dst_plane_stride", ctypes.c_int64), ("dst_group_stride", ctypes.c_int64),
+        ("pad_value", ctypes.c_float * 3),
     ]
 
 
@@ -123,13 +129,31 @@ def pixel_exact(y: int, u: int, v: int, coeff: int = 1) -> tuple[int, int, int]:
     return tuple(out)
 
 
-def exhaustive(coeff: int = 1, full_range: bool = False, mode: int | None = None) -> np.ndarray:
+def exhaustive(coeff: int = 1, full_range: bool = False, mode: int | None = None,
+               arith: int = ARITH_REFERENCE) -> np.ndarray:
     """``[256,256,256,3]`` u8: converted bytes for every (y,u,v)."""
     out = np.empty((256, 256, 256, 3), np.uint8)
-    lib().orc_exhaustive(int(coeff), int(bool(full_range)),
-                         DEVICE_FMA_MODE if mode is None else mode,
-                         out.ctypes.data_as(ctypes.c_void_p))
+    if arith == ARITH_SWSCALE:
+        lib().orc_sws_exhaustive(int(coeff), int(bool(full_range)),
+                                 out.ctypes.data_as(ctypes.c_void_p))
+    else:
+        lib().orc_exhaustive(int(coeff), int(bool(full_range)),
+                             DEVICE_FMA_MODE if mode is None else mode,
+                             out.ctypes.data_as(ctypes.c_void_p))
     return out
+
+
+def sws_coeffs(cs: int = 1, full_range: bool = False) -> dict[str, int]:
+    """libswscale's 16-bit converter constants for colourspace number ``cs``."""
+    out = (ctypes.c_int * 6)()
+    lib().orc_sws_coeffs(int(cs), int(bool(full_range)), out)
+    return dict(zip(("yc", "vr", "ug", "vg", "ub", "yo"), out))
+
+
+def sws_pixel(y: int, u: int, v: int, cs: int = 1, full_range: bool = False) -> tuple[int, int, int]:
+    out = (ctypes.c_uint8 * 3)()
+    lib().orc_sws_pixel(int(y), int(u), int(v), int(cs), int(bool(full_range)), out)
+    return tuple(out)
 
 
 _NP_OUT = {U8: np.uint8, F32: np.float32, BF16: np.uint16}
@@ -150,7 +174,7 @@ def convert_dense(y: np.ndarray, u: np.ndarray, v: np.ndarray | None, *, width: 
                   uv_frame_stride: int, src_format: int = NV12, coeff: int = 1,
                   full_range: bool = False, layout: int = NCHW, dtype: int = U8, order: int = RGB,
                   sb: np.ndarray | None = None, mode: int | None = None,
-                  out: np.ndarray | None = None) -> np.ndarray:
+                  out: np.ndarray | None = None, arith: int = ARITH_REFERENCE) -> np.ndarray:
     """General dense conversion over raw planes (u8 numpy arrays, any shape, C-contiguous)."""
     shape = (num_frames, 3, height, width) if layout == NCHW else (num_frames, height, width, 3)
     if out is None:
@@ -167,6 +191,7 @@ def convert_dense(y: np.ndarray, u: np.ndarray, v: np.ndarray | None, *, width: 
     a.layout, a.dtype, a.order = layout, dtype, order
     sb = scale_bias() if sb is None else np.asarray(sb, np.float32)
     a.scale_bias = (ctypes.c_float * 6)(*sb.tolist())
+    a.arith = int(arith)
     lib().orc_convert_dense(ctypes.byref(a))
     return out
 
@@ -189,13 +214,22 @@ def nv12_to_planar(nv12: np.ndarray, coeff: int = 1, order: int = RGB, **kw) -> 
 def convert_resize(base: np.ndarray, descs: np.ndarray, *, out_w: int, out_h: int,
                    src_format: int = NV12, coeff: int = 1, full_range: bool = False,
                    layout: int = NCHW, dtype: int = U8, order: int = RGB,
-                   sb: np.ndarray | None = None, mode: int | None = None) -> np.ndarray:
-    """Fused convert -> bilinear -> crop -> scale/bias over a packed byte buffer and a
-    descriptor table (``DESC_DTYPE``)."""
-    assert descs.dtype == DESC_DTYPE and descs.flags.c_contiguous
+                   sb: np.ndarray | None = None, mode: int | None = None,
+                   arith: int = ARITH_REFERENCE, pad_value=(0.0, 0.0, 0.0),
+                   clip_frames: int = 0, out: np.ndarray | None = None) -> np.ndarray:
+    """Fused convert -> bilinear -> crop / letterbox -> scale/bias over a packed byte buffer and
+    a descriptor table (``DESC_DTYPE``).  ``clip_frames=T`` writes ``[N/T, 3, T, h, w]`` (planar
+    only).  ``out`` may be a pre-filled array of the result's shape (images with nonsensical
+    descriptors are left untouched in it)."""
+    assert descs.dtype.itemsize == 64 and descs.flags.c_contiguous
     n = len(descs)
     shape = (n, 3, out_h, out_w) if layout == NCHW else (n, out_h, out_w, 3)
-    out = np.zeros(shape, _NP_OUT[dtype])
+    if clip_frames:
+        assert layout == NCHW and n % clip_frames == 0
+        shape = (n // clip_frames, 3, clip_frames, out_h, out_w)
+    if out is None:
+        out = np.zeros(shape, _NP_OUT[dtype])
+    assert out.shape == shape and out.flags.c_contiguous
     a = _ResizeArgs()
     a.base, a.descs = base.ctypes.data, descs.ctypes.data
     a.num_images, a.src_format, a.out_w, a.out_h = n, src_format, out_w, out_h
@@ -205,6 +239,12 @@ def convert_resize(base: np.ndarray, descs: np.ndarray, *, out_w: int, out_h: in
     a.dst, a.dst_image_stride = out.ctypes.data, 0
     sb = scale_bias() if sb is None else np.asarray(sb, np.float32)
     a.scale_bias = (ctypes.c_float * 6)(*sb.tolist())
+    a.arith = int(arith)
+    a.pad_value = (ctypes.c_float * 3)(*[float(v) for v in pad_value])
+    if clip_frames:
+        plane = out_h * out_w
+        a.frames_per_group, a.dst_image_stride = int(clip_frames), plane
+        a.dst_plane_stride, a.dst_group_stride = clip_frames * plane, 3 * clip_frames * plane
     lib().orc_convert_resize(ctypes.byref(a))
     return out
 

@@ -17,6 +17,19 @@
  *                        and src/libspdl/cuda/color_conversion.cpp:34-54 (shapes)
  *   orc_gather_frames    src/libspdl/cuda/nvdec/detail/buffer.cpp:31-74
  *                        (pitched surface -> packed [N, H*3/2, W] slot)
+ *   orc_sws_coeffs /     the reference's CPU route: "format=pix_fmts=rgb24"
+ *   orc_sws_pixel        (src/spdl/io/_preprocessing.py:250-251) run by the filter graph of
+ *                        src/libspdl/core/detail/ffmpeg/filter_graph.cpp:50-65,154-173, i.e. by
+ *                        FFmpeg's libswscale.  libswscale is a third-party dependency whose
+ *                        source is NOT under the reference tree (the reference loads FFmpeg 4-8
+ *                        at run time); the arithmetic restated here is that of its unscaled
+ *                        yuv420p -> rgb24 converter on x86 (libswscale/x86/yuv_2_rgb.asm, 16-bit
+ *                        lanes) with the constants of ff_yuv2rgb_c_init_tables
+ *                        (libswscale/yuv2rgb.c) and the colourspace table behind
+ *                        sws_getCoefficients.  Pinned against libswscale 9.1.100 (FFmpeg 8) as
+ *                        bundled with the opencv wheel: identical over all 2^24 (Y,U,V) for
+ *                        BT.709 and BT.601, limited and full range (tests/golden/sws_golden.json,
+ *                        tests/test_swscale_oracle.py).
  *
  * Parity status.  The limited-range planar u8 conversion is pinned by the three
  * known-answer triplets of tests/cuda/nvdec_video_decoding_test.py:335-348 and
@@ -39,6 +52,9 @@ enum { ORC_NV12 = 0, ORC_I420 = 1, ORC_RGBP = 2, ORC_RGBI = 3 };
 enum { ORC_NCHW = 0, ORC_NHWC = 1 };
 enum { ORC_U8 = 0, ORC_F32 = 1, ORC_BF16 = 2 };
 enum { ORC_RGB = 0, ORC_BGR = 1 };
+/* Which arithmetic converts a pixel: the reference's CUDA kernel (fp32, default) or the integer
+ * arithmetic of libswscale, the reference's CPU route. */
+enum { ORC_ARITH_REFERENCE = 0, ORC_ARITH_SWSCALE = 1 };
 /* How the three products of one output channel are combined in fp32.
  * The reference source writes  m0*fy + m1*fu + m2*fv ; nvcc fuses multiplies
  * and adds by default, so the device result depends on which products are
@@ -162,6 +178,93 @@ ORC_EXPORT void orc_pixel_exact(int y, int u, int v, int coeff, uint8_t* rgb) {
   }
 }
 
+/* ---- libswscale's integer arithmetic ----------------------------------------------------- */
+
+/* The table behind sws_getCoefficients(): 16.16 fixed point {V->R, U->B, -(U->G), -(V->G)},
+ * indexed by SWS_CS_*; 8 and out-of-range numbers select the BT.601 row, as that function does. */
+static const int k_sws_table[11][4] = {
+    {104597, 132201, 25675, 53279}, {117489, 138438, 13975, 34925},
+    {104597, 132201, 25675, 53279}, {104597, 132201, 25675, 53279},
+    {104448, 132798, 24759, 53109}, {104597, 132201, 25675, 53279},
+    {104597, 132201, 25675, 53279}, {117579, 136230, 16907, 35559},
+    {104597, 132201, 25675, 53279}, {110013, 140363, 12277, 42626},
+    {110013, 140363, 12277, 42626},
+};
+
+typedef struct { int yc, vr, ug, vg, ub, yo; } orc_sws;
+
+static inline int orc_round16(int64_t f) {  /* roundToInt16 of yuv2rgb.c */
+  int64_t r = (f + (1 << 15)) >> 16;
+  return (int)(r < -0x8000 ? -0x8000 : (r > 0x7FFF ? 0x7FFF : r));
+}
+
+/* 16-bit SIMD constants for colourspace `cs`, default brightness/contrast/saturation.
+ * out: {yCoeff, vrCoeff, ugCoeff, vgCoeff, ubCoeff, yOffset}. */
+ORC_EXPORT void orc_sws_coeffs(int cs, int full_range, int* out) {
+  if (cs < 0 || cs > 10) cs = 5;
+  int64_t crv = k_sws_table[cs][0], cbu = k_sws_table[cs][1];
+  int64_t cgu = -k_sws_table[cs][2], cgv = -k_sws_table[cs][3];
+  int64_t cy = 1 << 16, oy = 0;
+  if (!full_range) {
+    cy = (cy * 255) / 219;
+    oy = 16 << 16;
+  } else {
+    crv = (crv * 224) / 255;
+    cbu = (cbu * 224) / 255;
+    cgu = (cgu * 224) / 255;
+    cgv = (cgv * 224) / 255;
+  }
+  out[0] = orc_round16(cy * 8192);
+  out[1] = orc_round16(crv * 8192);
+  out[2] = orc_round16(cgu * 8192);
+  out[3] = orc_round16(cgv * 8192);
+  out[4] = orc_round16(cbu * 8192);
+  out[5] = orc_round16(oy * 8);
+}
+
+static inline int orc_sat16(int v) { return v < -32768 ? -32768 : (v > 32767 ? 32767 : v); }
+static inline uint8_t orc_satu8(int v) { return (uint8_t)(v < 0 ? 0 : (v > 255 ? 255 : v)); }
+
+/* One pixel as the 16-bit lanes compute it: x' = (byte << 3) - offset, products keep the high
+ * 16 bits of the signed 32-bit product, sums saturate to 16 bits, the pack saturates to 8. */
+static inline void orc_sws_pixel_impl(int y, int u, int v, const orc_sws* k, uint8_t* rgb) {
+  const int ys = (int16_t)((y << 3) - k->yo), us = (int16_t)((u << 3) - 1024),
+            vs = (int16_t)((v << 3) - 1024);
+  const int ym = (ys * k->yc) >> 16;
+  const int ub = (us * k->ub) >> 16, ug = (us * k->ug) >> 16;
+  const int vr = (vs * k->vr) >> 16, vg = (vs * k->vg) >> 16;
+  rgb[0] = orc_satu8(orc_sat16(ym + vr));
+  rgb[1] = orc_satu8(orc_sat16(ym + orc_sat16(ug + vg)));
+  rgb[2] = orc_satu8(orc_sat16(ym + ub));
+}
+
+static inline orc_sws orc_sws_of(int cs, int full_range) {
+  int c[6];
+  orc_sws_coeffs(cs, full_range, c);
+  orc_sws k = {c[0], c[1], c[2], c[3], c[4], c[5]};
+  return k;
+}
+
+ORC_EXPORT void orc_sws_pixel(int y, int u, int v, int cs, int full_range, uint8_t* rgb) {
+  const orc_sws k = orc_sws_of(cs, full_range);
+  orc_sws_pixel_impl(y, u, v, &k, rgb);
+}
+
+/* The pixel converter both batch functions call. */
+typedef struct { float m[9]; int y_off, fma_mode, arith; orc_sws sws; } orc_conv;
+static inline orc_conv orc_conv_of(int coeff, int full_range, int fma_mode, int arith) {
+  orc_conv c;
+  orc_matrix(coeff, full_range, c.m, &c.y_off);
+  c.fma_mode = fma_mode;
+  c.arith = arith;
+  c.sws = orc_sws_of(coeff, full_range);
+  return c;
+}
+static inline void orc_convert_pixel(const orc_conv* c, int y, int u, int v, uint8_t* rgb) {
+  if (c->arith == ORC_ARITH_SWSCALE) orc_sws_pixel_impl(y, u, v, &c->sws, rgb);
+  else orc_pixel_impl(y, u, v, c->m, c->y_off, c->fma_mode, rgb);
+}
+
 static inline uint16_t orc_f32_to_bf16(float f) {
   uint32_t b; memcpy(&b, &f, 4);
   if ((b & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((b >> 16) | 0x40);
@@ -194,11 +297,11 @@ typedef struct {
   int64_t dst_frame_stride;   /* in elements; 0 = packed (3*H*W)                     */
   int32_t layout, dtype, order;
   float scale_bias[6];        /* scale[3], bias[3] per OUTPUT channel slot            */
+  int32_t arith;              /* ORC_ARITH_*                                          */
 } orc_dense_args;
 
 #define ORC_DENSE_BODY                                                                          \
-  float m[9]; int y_off;                                                                        \
-  orc_matrix(a->coeff, a->full_range, m, &y_off);                                               \
+  const orc_conv cv = orc_conv_of(a->coeff, a->full_range, a->fma_mode, a->arith);              \
   const int W = a->width, H = a->height;                                                        \
   const int We = W & ~1, He = H & ~1;                                                           \
   const int64_t fstride = a->dst_frame_stride ? a->dst_frame_stride : (int64_t)3 * H * W;       \
@@ -213,11 +316,11 @@ typedef struct {
                                 : NULL;                                                         \
       char* dbase = (char*)a->dst + (size_t)n * fstride * esz;                                  \
       for (int x = 0; x < We; ++x) {                                                            \
-        int cu, cv;                                                                             \
-        if (a->src_format == ORC_I420) { cu = urow[x >> 1]; cv = vrow[x >> 1]; }                \
-        else { cu = urow[x & ~1]; cv = urow[(x & ~1) + 1]; }                                    \
+        int cu, cv_;                                                                            \
+        if (a->src_format == ORC_I420) { cu = urow[x >> 1]; cv_ = vrow[x >> 1]; }               \
+        else { cu = urow[x & ~1]; cv_ = urow[(x & ~1) + 1]; }                                   \
         uint8_t rgb[3];                                                                         \
-        orc_pixel_impl(yrow[x], cu, cv, m, y_off, a->fma_mode, rgb);                            \
+        orc_convert_pixel(&cv, yrow[x], cu, cv_, rgb);                                          \
         for (int s = 0; s < 3; ++s) {                                                           \
           int ch = a->order == ORC_BGR ? 2 - s : s;                                             \
           size_t idx = a->layout == ORC_NCHW ? ((size_t)s * H + y) * W + x                      \
@@ -250,7 +353,8 @@ typedef struct {
   int32_t src_w, src_h;
   int32_t crop_x, crop_y;       /* position of output (0,0) in the resized grid        */
   float scale_x, scale_y;       /* source size / resized size, computed in fp32        */
-  int32_t reserved[2];
+  int32_t resized_w, resized_h; /* size of the resized grid (0 = unbounded): output pixels
+                                 * outside it take the pad colour (letterbox)          */
 } orc_image_desc;               /* 64 bytes, same layout as the C-ABI descriptor       */
 
 typedef struct {
@@ -263,6 +367,11 @@ typedef struct {
   void* dst;
   int64_t dst_image_stride;     /* elements; 0 = packed 3*out_h*out_w                  */
   float scale_bias[6];
+  int32_t arith;                /* ORC_ARITH_*                                         */
+  int32_t frames_per_group;     /* T > 1: image i starts at (i / T) * group + (i % T) * image */
+  int64_t dst_plane_stride;     /* NCHW: elements between colour planes; 0 = out_h*out_w */
+  int64_t dst_group_stride;
+  float pad_value[3];           /* R, G, B (0..255) of pixels outside the resized grid  */
 } orc_resize_args;
 
 static inline void orc_axis(float scale, int g, int n_in, int* i0, int* i1, float* w1) {
@@ -276,26 +385,37 @@ static inline void orc_axis(float scale, int g, int n_in, int* i0, int* i1, floa
   *w1 = s - (float)a;
 }
 
+/* An image whose descriptor makes no sense (empty source, non-positive or non-finite scale) is
+ * left untouched, like the kernel does (it reports a status bit instead). */
 #define ORC_RESIZE_BODY                                                                         \
-  float m[9]; int y_off;                                                                        \
-  orc_matrix(a->coeff, a->full_range, m, &y_off);                                               \
+  const orc_conv cv = orc_conv_of(a->coeff, a->full_range, a->fma_mode, a->arith);              \
   const int OW = a->out_w, OH = a->out_h;                                                       \
   const int64_t istride = a->dst_image_stride ? a->dst_image_stride : (int64_t)3 * OH * OW;     \
+  const int64_t pstride = a->dst_plane_stride ? a->dst_plane_stride : (int64_t)OH * OW;         \
   const size_t esz = a->dtype == ORC_U8 ? 1 : (a->dtype == ORC_F32 ? 4 : 2);                    \
   _Pragma("omp parallel for collapse(2) schedule(dynamic, 8)")                                  \
   for (int n = 0; n < a->num_images; ++n) {                                                     \
     for (int oy = 0; oy < OH; ++oy) {                                                           \
       const orc_image_desc* d = &a->descs[n];                                                   \
-      char* dbase = (char*)a->dst + (size_t)n * istride * esz;                                  \
+      if (d->src_w < 1 || d->src_h < 1 || !(d->scale_x > 0.0f) || !(d->scale_y > 0.0f)) continue; \
+      int64_t ioff = (int64_t)n * istride;                                                      \
+      if (a->frames_per_group > 1)                                                              \
+        ioff = (int64_t)(n / a->frames_per_group) * a->dst_group_stride +                       \
+               (int64_t)(n % a->frames_per_group) * istride;                                    \
+      char* dbase = (char*)a->dst + (size_t)ioff * esz;                                         \
+      const int gy = d->crop_y + oy;                                                            \
+      const int row_out = d->resized_h > 0 && (gy < 0 || gy >= d->resized_h);                   \
       int ys[2]; float wy1;                                                                     \
-      orc_axis(d->scale_y, d->crop_y + oy, d->src_h, &ys[0], &ys[1], &wy1);                     \
+      orc_axis(d->scale_y, gy, d->src_h, &ys[0], &ys[1], &wy1);                                 \
       float wy0 = 1.0f - wy1;                                                                   \
       for (int ox = 0; ox < OW; ++ox) {                                                         \
+        const int gx = d->crop_x + ox;                                                          \
+        const int outside = row_out || (d->resized_w > 0 && (gx < 0 || gx >= d->resized_w));    \
         int xs[2]; float wx1;                                                                   \
-        orc_axis(d->scale_x, d->crop_x + ox, d->src_w, &xs[0], &xs[1], &wx1);                   \
+        orc_axis(d->scale_x, gx, d->src_w, &xs[0], &xs[1], &wx1);                               \
         float wx0 = 1.0f - wx1;                                                                 \
         uint8_t tap[2][2][3];                                                                   \
-        for (int j = 0; j < 2; ++j)                                                             \
+        for (int j = 0; j < 2 && !outside; ++j)                                                 \
           for (int i = 0; i < 2; ++i) {                                                         \
             int sx = xs[i], sy = ys[j];                                                         \
             if (a->src_format == ORC_RGBP) {                                                    \
@@ -310,26 +430,31 @@ static inline void orc_axis(float scale, int g, int n_in, int* i0, int* i1, floa
               continue;                                                                         \
             }                                                                                   \
             int Y = a->base[d->y_off + (uint64_t)sy * d->y_pitch + sx];                         \
-            int cu, cv;                                                                         \
+            int cu, cv_;                                                                        \
             if (a->src_format == ORC_I420) {                                                    \
               cu = a->base[d->u_off + (uint64_t)(sy >> 1) * d->uv_pitch + (sx >> 1)];           \
-              cv = a->base[d->v_off + (uint64_t)(sy >> 1) * d->uv_pitch + (sx >> 1)];           \
+              cv_ = a->base[d->v_off + (uint64_t)(sy >> 1) * d->uv_pitch + (sx >> 1)];          \
             } else {                                                                            \
               const uint8_t* p = a->base + d->u_off + (uint64_t)(sy >> 1) * d->uv_pitch + (sx & ~1); \
-              cu = p[0]; cv = p[1];                                                             \
+              cu = p[0]; cv_ = p[1];                                                            \
             }                                                                                   \
-            orc_pixel_impl(Y, cu, cv, m, y_off, a->fma_mode, tap[j][i]);                        \
+            orc_convert_pixel(&cv, Y, cu, cv_, tap[j][i]);                                      \
           }                                                                                     \
         for (int s = 0; s < 3; ++s) {                                                           \
           int ch = a->order == ORC_BGR ? 2 - s : s;                                             \
-          float top = ORC_FMA(wx1, (float)tap[0][1][ch], wx0 * (float)tap[0][0][ch]);           \
-          float bot = ORC_FMA(wx1, (float)tap[1][1][ch], wx0 * (float)tap[1][0][ch]);           \
-          float val = ORC_FMA(wy1, bot, wy0 * top);                                             \
+          float val;                                                                            \
+          if (outside) {                                                                        \
+            val = a->pad_value[ch];                                                             \
+          } else {                                                                              \
+            float top = ORC_FMA(wx1, (float)tap[0][1][ch], wx0 * (float)tap[0][0][ch]);         \
+            float bot = ORC_FMA(wx1, (float)tap[1][1][ch], wx0 * (float)tap[1][0][ch]);         \
+            val = ORC_FMA(wy1, bot, wy0 * top);                                                 \
+          }                                                                                     \
           if (a->dtype == ORC_U8) {                                                             \
             float q = floorf(val + 0.5f);                                                       \
             val = q < 0.0f ? 0.0f : (q > 255.0f ? 255.0f : q);                                  \
           }                                                                                     \
-          size_t idx = a->layout == ORC_NCHW ? ((size_t)s * OH + oy) * OW + ox                  \
+          size_t idx = a->layout == ORC_NCHW ? (size_t)s * pstride + (size_t)oy * OW + ox       \
                                              : ((size_t)oy * OW + ox) * 3 + s;                  \
           orc_store(dbase, idx, a->dtype, val, a->scale_bias, s);                               \
         }                                                                                       \
@@ -359,6 +484,16 @@ ORC_EXPORT void orc_exhaustive(int coeff, int full_range, int mode, uint8_t* out
     for (int u = 0; u < 256; ++u)
       for (int v = 0; v < 256; ++v)
         orc_pixel_impl(y, u, v, m, y_off, mode, out + 3 * (((size_t)y * 256 + u) * 256 + v));
+}
+
+/* The same table for libswscale's arithmetic (colourspace number `cs`). */
+ORC_EXPORT void orc_sws_exhaustive(int cs, int full_range, uint8_t* out) {
+  const orc_sws k = orc_sws_of(cs, full_range);
+#pragma omp parallel for schedule(static)
+  for (int y = 0; y < 256; ++y)
+    for (int u = 0; u < 256; ++u)
+      for (int v = 0; v < 256; ++v)
+        orc_sws_pixel_impl(y, u, v, &k, out + 3 * (((size_t)y * 256 + u) * 256 + v));
 }
 
 /* Pitched decoder surfaces (one pointer each) -> packed [N, H*3/2, W] batch. */

@@ -19,6 +19,9 @@ NV12, I420 = 0, 1
 NCHW, NHWC = 0, 1
 U8, F32, BF16 = 0, 1, 2
 RGB, BGR = 0, 1
+ARITH_REFERENCE, ARITH_SWSCALE = 0, 1
+STATUS_IMAGE_TOO_WIDE, STATUS_WAIT_EXPIRED, STATUS_BAD_GEOMETRY = 1, 2, 4
+DEBUG_EXPIRE_WAIT = 1
 
 #: every symbol include/b2frames.h declares
 EXPORTS = (
@@ -41,6 +44,7 @@ class DenseArgs(Structure):
         ("dst", c_void_p), ("dst_frame_stride", c_int64),
         ("layout", c_int32), ("dtype", c_int32), ("order", c_int32),
         ("scale", c_float * 3), ("bias", c_float * 3),
+        ("reserved0", c_int32), ("arith", c_int32), ("reserved1", c_int32),
     ]
 
 
@@ -49,7 +53,7 @@ class ImageDesc(Structure):
         ("y_off", c_uint64), ("u_off", c_uint64), ("v_off", c_uint64),
         ("y_pitch", c_int32), ("uv_pitch", c_int32), ("src_w", c_int32), ("src_h", c_int32),
         ("crop_x", c_int32), ("crop_y", c_int32), ("scale_x", c_float), ("scale_y", c_float),
-        ("reserved", c_int32 * 2),
+        ("resized_w", c_int32), ("resized_h", c_int32),
     ]
 
 
@@ -64,6 +68,10 @@ class ResizeArgs(Structure):
         ("max_src_w", c_int32),
         ("dst", c_void_p), ("dst_image_stride", c_int64),
         ("scale", c_float * 3), ("bias", c_float * 3),
+        ("arith", c_int32), ("frames_per_group", c_int32),
+        ("dst_plane_stride", c_int64), ("dst_group_stride", c_int64),
+        ("pad_value", c_float * 3), ("debug_flags", c_int32),
+        ("status", c_void_p),
     ]
 
 

@@ -1,5 +1,6 @@
 // extern "C" surface of libb2frames.so: argument validation, device selection, error messages.
 #include <cstdarg>
+#include <cstddef>
 #include <cstdio>
 #include <cstring>
 
@@ -70,7 +71,54 @@ static const float kFull[10][5] = {
     {1.0f, 1.474600f, -0.164553f, -0.571353f, 1.881400f},
 };
 
-ColorMat color_matrix(int k, int full_range) {
+// libswscale's colourspace table (the values sws_getCoefficients() returns, 16.16 fixed point:
+// V->R, U->B, -U->G, -V->G), indexed by its SWS_CS_* number; 8 and anything outside 0..10 fall
+// back to the BT.601 row, as that function does.  FFmpeg's source is not part of the reference
+// tree; the numbers are pinned against the loaded library by the test-suite.
+static const int kSwsTable[11][4] = {
+    {104597, 132201, 25675, 53279},  // 0 default
+    {117489, 138438, 13975, 34925},  // 1 ITU-R BT.709
+    {104597, 132201, 25675, 53279},  // 2 unspecified
+    {104597, 132201, 25675, 53279},  // 3 reserved
+    {104448, 132798, 24759, 53109},  // 4 FCC
+    {104597, 132201, 25675, 53279},  // 5 ITU-R BT.601 (624)
+    {104597, 132201, 25675, 53279},  // 6 SMPTE 170M
+    {117579, 136230, 16907, 35559},  // 7 SMPTE 240M
+    {104597, 132201, 25675, 53279},  // 8 (no entry of its own)
+    {110013, 140363, 12277, 42626},  // 9 BT.2020 non-constant luminance
+    {110013, 140363, 12277, 42626},  // 10 BT.2020 constant luminance
+};
+
+// The 16-bit coefficients of libswscale's SIMD converter for default brightness, contrast and
+// saturation: round(c * 2^13) of the 16.16 table entries, luma gain 255/219 and chroma as
+// tabulated for limited-range sources, luma gain 1 and chroma scaled by 224/255 for full-range
+// ones (integer arithmetic throughout, as the library computes them).
+static ColorMat sws_matrix(int k, int full_range) {
+  if (k < 0 || k > 10) k = 5;
+  long long crv = kSwsTable[k][0], cbu = kSwsTable[k][1], cgu = -kSwsTable[k][2],
+            cgv = -kSwsTable[k][3], cy = 1 << 16;
+  if (!full_range) {
+    cy = cy * 255 / 219;
+  } else {
+    crv = crv * 224 / 255;
+    cbu = cbu * 224 / 255;
+    cgu = cgu * 224 / 255;
+    cgv = cgv * 224 / 255;
+  }
+  auto coeff = [](long long c) {  // round(c * 2^13 / 2^16) clipped to 16 bits, then / 2^13
+    long long r = (c * 8192 + 32768) >> 16;
+    r = r < -32768 ? -32768 : (r > 32767 ? 32767 : r);
+    return (float)r / 8192.0f;
+  };
+  ColorMat m;
+  m.g = coeff(cy); m.vr = coeff(crv); m.ug = coeff(cgu); m.vg = coeff(cgv); m.ub = coeff(cbu);
+  m.y_bias = 8388608.0f + (full_range ? 0.0f : 16.0f);
+  m.neg_zero = -0.0f;
+  return m;
+}
+
+ColorMat color_matrix(int k, int full_range, int arith) {
+  if (arith == B2_ARITH_SWSCALE) return sws_matrix(k, full_range);
   if (k <= 0 || k > 10) k = 1;  // color_conversion.cu:120-123
   const float* r = full_range ? kFull[k - 1] : kLimited[k - 1];
   ColorMat m;
@@ -158,12 +206,18 @@ B2_API int b2_nv12_to_planar_bgr(void* stream, const uint8_t* src, int src_pitch
                       B2_BGR);
 }
 
-B2_API int b2_convert_dense(const b2_dense_args* a, void* stream) {
+B2_API int b2_convert_dense(const b2_dense_args* args, void* stream) {
   clear_error();
-  if (!a) return fail(B2_ERR_INVALID, "null argument struct");
-  if (a->struct_size != sizeof(b2_dense_args))
-    return fail(B2_ERR_INVALID, "b2_dense_args.struct_size is %u, this library expects %zu",
-                a->struct_size, sizeof(b2_dense_args));
+  if (!args) return fail(B2_ERR_INVALID, "null argument struct");
+  // version 1 of the struct ended (with its tail padding) where `arith` starts now
+  constexpr size_t kV1 = offsetof(b2_dense_args, arith);
+  if (args->struct_size != sizeof(b2_dense_args) && args->struct_size != kV1)
+    return fail(B2_ERR_INVALID, "b2_dense_args.struct_size is %u, this library expects %zu (or %zu)",
+                args->struct_size, sizeof(b2_dense_args), kV1);
+  b2_dense_args local{};
+  memcpy(&local, args, args->struct_size);
+  const b2_dense_args* a = &local;
+  if (!valid_enum(a->arith, 1)) return fail(B2_ERR_INVALID, "unknown arith (%d)", a->arith);
   if (!valid_enum(a->src_format, 1) || !valid_enum(a->layout, 1) || !valid_enum(a->dtype, 2) ||
       !valid_enum(a->order, 1))
     return fail(B2_ERR_INVALID, "unknown src_format/layout/dtype/order (%d, %d, %d, %d)",
@@ -201,7 +255,8 @@ B2_API int b2_convert_dense(const b2_dense_args* a, void* stream) {
   L.y_frame_stride = a->y_frame_stride; L.uv_frame_stride = a->uv_frame_stride;
   L.src_format = a->src_format;
   L.width = a->width; L.height = a->height; L.num_frames = a->num_frames;
-  L.mat = color_matrix(a->matrix_coeff, a->full_range);
+  L.mat = color_matrix(a->matrix_coeff, a->full_range, a->arith);
+  L.arith = a->arith;
   L.dst = a->dst;
   L.layout = a->layout; L.dtype = a->dtype; L.order = a->order;
   L.dst_row_pitch = a->layout == B2_NCHW ? a->width : 3LL * a->width;
@@ -211,16 +266,21 @@ B2_API int b2_convert_dense(const b2_dense_args* a, void* stream) {
   return launch_dense(L, static_cast<cudaStream_t>(stream));
 }
 
-B2_API int b2_convert_resize(const b2_resize_args* a, void* stream) {
+B2_API int b2_convert_resize(const b2_resize_args* args, void* stream) {
   clear_error();
-  if (!a) return fail(B2_ERR_INVALID, "null argument struct");
-  if (a->struct_size != sizeof(b2_resize_args))
-    return fail(B2_ERR_INVALID, "b2_resize_args.struct_size is %u, this library expects %zu",
-                a->struct_size, sizeof(b2_resize_args));
+  if (!args) return fail(B2_ERR_INVALID, "null argument struct");
+  constexpr size_t kV1 = offsetof(b2_resize_args, arith);  // where version 1 of the struct ended
+  if (args->struct_size != sizeof(b2_resize_args) && args->struct_size != kV1)
+    return fail(B2_ERR_INVALID,
+                "b2_resize_args.struct_size is %u, this library expects %zu (or %zu)",
+                args->struct_size, sizeof(b2_resize_args), kV1);
+  b2_resize_args local{};
+  memcpy(&local, args, args->struct_size);
+  const b2_resize_args* a = &local;
   if (!valid_enum(a->src_format, 3) || !valid_enum(a->layout, 1) || !valid_enum(a->dtype, 2) ||
-      !valid_enum(a->order, 1))
-    return fail(B2_ERR_INVALID, "unknown src_format/layout/dtype/order (%d, %d, %d, %d)",
-                a->src_format, a->layout, a->dtype, a->order);
+      !valid_enum(a->order, 1) || !valid_enum(a->arith, 1))
+    return fail(B2_ERR_INVALID, "unknown src_format/layout/dtype/order/arith (%d, %d, %d, %d, %d)",
+                a->src_format, a->layout, a->dtype, a->order, a->arith);
   if (a->num_images < 0 || a->out_w < 0 || a->out_h < 0 || a->max_src_w < 0)
     return fail(B2_ERR_INVALID, "negative size: num_images %d, out %dx%d, max_src_w %d",
                 a->num_images, a->out_w, a->out_h, a->max_src_w);
@@ -228,9 +288,26 @@ B2_API int b2_convert_resize(const b2_resize_args* a, void* stream) {
   if (!a->base || !a->descs || !a->dst)
     return fail(B2_ERR_INVALID, "null base, descs or dst pointer");
   if (a->max_src_w < 1) return fail(B2_ERR_INVALID, "max_src_w must be at least 1");
-  if (a->dst_image_stride != 0 && a->dst_image_stride < 3LL * a->out_w * a->out_h)
+  const long long plane = (long long)a->out_w * a->out_h;
+  if (a->dst_plane_stride != 0) {
+    if (a->layout != B2_NCHW)
+      return fail(B2_ERR_INVALID, "dst_plane_stride needs the planar (NCHW) layout");
+    if (a->dst_plane_stride < plane)
+      return fail(B2_ERR_INVALID, "dst_plane_stride %lld is smaller than one plane",
+                  (long long)a->dst_plane_stride);
+    if (a->dst_image_stride != 0 && a->dst_image_stride < plane)
+      return fail(B2_ERR_INVALID, "dst_image_stride %lld is smaller than one plane",
+                  (long long)a->dst_image_stride);
+  } else if (a->dst_image_stride != 0 && a->dst_image_stride < 3 * plane) {
     return fail(B2_ERR_INVALID, "dst_image_stride %lld is smaller than one image",
                 (long long)a->dst_image_stride);
+  }
+  if (a->frames_per_group < 0 || (a->frames_per_group > 1 && a->dst_group_stride <= 0))
+    return fail(B2_ERR_INVALID, "frames_per_group %d needs a positive dst_group_stride (%lld)",
+                a->frames_per_group, (long long)a->dst_group_stride);
+  for (int i = 0; i < 3; ++i)
+    if (!(a->pad_value[i] >= 0.0f && a->pad_value[i] <= 255.0f))
+      return fail(B2_ERR_INVALID, "pad_value[%d] = %g is outside 0..255", i, a->pad_value[i]);
   DeviceGuard g(a->device);
   B2_CUDA(g.status(), "selecting the device failed");
   return launch_resize(*a, static_cast<cudaStream_t>(stream));

@@ -43,7 +43,9 @@ struct ColorMat {
   float y_bias;
   float neg_zero;  // always -0.0f; a run-time value so that the compiler cannot fold it away
 };
-ColorMat color_matrix(int matrix_coeff, int full_range);
+// arith = B2_ARITH_SWSCALE fills the same struct with libswscale's 16-bit coefficients divided
+// by 2^13 (exact in fp32) and vg unused; see sws_chroma2_of.
+ColorMat color_matrix(int matrix_coeff, int full_range, int arith = B2_ARITH_REFERENCE);
 
 struct ScaleBias {
   float s[3], b[3];
@@ -106,11 +108,21 @@ __device__ __forceinline__ float2 x2_fma(float2 a, float2 b, float2 c) {
 }
 __device__ __forceinline__ float2 dup2(float a) { return make_float2(a, a); }
 
+__device__ __forceinline__ float2 x2_fma_rm(float2 a, float2 b, float2 c) {
+  unsigned long long d;
+  asm("fma.rm.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(pack2(a)), "l"(pack2(b)), "l"(pack2(c)));
+  return unpack2(d);
+}
+
 struct Chroma2 {
   float2 vr, ug, vg, ub;  // lane x: first quad, lane y: second quad
 };
 // bu, bv: {2^23 + U, 2^23 + V} of the two quads
-__device__ __forceinline__ Chroma2 chroma2_of(const ColorMat& m, float2 bu, float2 bv) {
+template <int ARITH = B2_ARITH_REFERENCE>
+__device__ __forceinline__ Chroma2 chroma2_of(const ColorMat& m, float2 bu, float2 bv);
+template <>
+__device__ __forceinline__ Chroma2 chroma2_of<B2_ARITH_REFERENCE>(const ColorMat& m, float2 bu,
+                                                                  float2 bv) {
   const float2 nz = dup2(m.neg_zero), off = dup2(-(kTwo23 + 128.0f));
   const float2 fu = x2_add(bu, off), fv = x2_add(bv, off);
   Chroma2 c;
@@ -120,10 +132,50 @@ __device__ __forceinline__ Chroma2 chroma2_of(const ColorMat& m, float2 bu, floa
   c.ub = x2_fma(dup2(m.ub), fu, nz);
   return c;
 }
+// ---- libswscale's arithmetic -----------------------------------------------------------------
+// The x86 SIMD converter libswscale uses for unscaled yuv420p -> rgb24 works on 16-bit lanes:
+//     y' = (Y << 3) - yOffset          u' = (U << 3) - 1024          v' = (V << 3) - 1024
+//     each product = (x' * coeff) >> 16                   (signed high half: a floor)
+//     R = y'' + vr'',   G = y'' + (ug'' + vg''),   B = y'' + ub'',   saturated to 0..255
+// with coeff = round(c * 2^13) from its colourspace table.  yOffset is 128 or 0, so every x' is
+// 8 * (byte - k) and a product is floor((byte - k) * coeff / 2^13).  (byte - k) * coeff stays
+// below 2^23, so fp32 holds it exactly, and ONE fused multiply-add that adds 1.5 * 2^23 and rounds
+// toward minus infinity leaves 1.5 * 2^23 + floor(product): no integer instruction is needed.
+// ColorMat carries coeff / 2^13 for this arithmetic (exact: a 16-bit integer times 2^-13).
+// Chroma2.ug holds ug'' + vg''; Chroma2.vg is unused.
+template <>
+__device__ __forceinline__ Chroma2 chroma2_of<B2_ARITH_SWSCALE>(const ColorMat& m, float2 bu,
+                                                                float2 bv) {
+  const float2 off = dup2(-(kTwo23 + 128.0f)), magic = dup2(kQuantMagic);
+  const float2 fu = x2_add(bu, off), fv = x2_add(bv, off);
+  Chroma2 c;
+  c.vr = x2_add(x2_fma_rm(dup2(m.vr), fv, magic), dup2(-kQuantMagic));
+  c.ub = x2_add(x2_fma_rm(dup2(m.ub), fu, magic), dup2(-kQuantMagic));
+  c.ug = x2_add(x2_fma_rm(dup2(m.ug), fu, magic),
+                x2_add(x2_fma_rm(dup2(m.vg), fv, magic), dup2(-2.0f * kQuantMagic)));
+  c.vg = dup2(0.0f);
+  return c;
+}
+
 // Two pixels (one per quad): by = {2^23 + Y, 2^23 + Y'}.  Results are the channel values plus
 // 1.5*2^23 rounded toward zero, i.e. floor(x) sits in the low 16 mantissa bits as a signed halfword (see clamp2_bits).
+template <int ARITH = B2_ARITH_REFERENCE>
 __device__ __forceinline__ void pixel2_bits(const ColorMat& m, float2 by, const Chroma2& c,
-                                            float2& r, float2& g, float2& b) {
+                                            float2& r, float2& g, float2& b);
+template <>
+__device__ __forceinline__ void pixel2_bits<B2_ARITH_SWSCALE>(const ColorMat& m, float2 by,
+                                                              const Chroma2& c, float2& r,
+                                                              float2& g, float2& b) {
+  const float2 fy = x2_add(by, dup2(-m.y_bias));
+  const float2 lm = x2_fma_rm(dup2(m.g), fy, dup2(kQuantMagic));  // 1.5*2^23 + y''
+  r = x2_add(lm, c.vr);  // sums of small integers and the magic constant: exact
+  g = x2_add(lm, c.ug);
+  b = x2_add(lm, c.ub);
+}
+template <>
+__device__ __forceinline__ void pixel2_bits<B2_ARITH_REFERENCE>(const ColorMat& m, float2 by,
+                                                                const Chroma2& c, float2& r,
+                                                                float2& g, float2& b) {
   const float2 g2 = dup2(m.g), magic = dup2(kQuantMagic);
   const float2 fy = x2_add(by, dup2(-m.y_bias));
   const float2 ly = x2_fma(g2, fy, dup2(m.neg_zero));
@@ -140,8 +192,24 @@ __device__ __forceinline__ float2 x2_mul_rz(float2 a, float2 b) {
   asm("mul.rz.f32x2 %0, %1, %2;" : "=l"(d) : "l"(pack2(a)), "l"(pack2(b)));
   return unpack2(d);
 }
+template <int ARITH = B2_ARITH_REFERENCE>
 __device__ __forceinline__ void pixel2_ints(const ColorMat& m, float2 by, const Chroma2& c,
-                                            float2& r, float2& g, float2& b) {
+                                            float2& r, float2& g, float2& b);
+template <>
+__device__ __forceinline__ void pixel2_ints<B2_ARITH_SWSCALE>(const ColorMat& m, float2 by,
+                                                              const Chroma2& c, float2& r,
+                                                              float2& g, float2& b) {
+  const float2 unit = dup2(__uint_as_float(1u));  // 2^-149
+  const float2 fy = x2_add(by, dup2(-m.y_bias));
+  const float2 ly = x2_add(x2_fma_rm(dup2(m.g), fy, dup2(kQuantMagic)), dup2(-kQuantMagic));
+  r = x2_mul_rz(x2_add(ly, c.vr), unit);  // integer-valued floats: the subnormal's bits are the value
+  g = x2_mul_rz(x2_add(ly, c.ug), unit);
+  b = x2_mul_rz(x2_add(ly, c.ub), unit);
+}
+template <>
+__device__ __forceinline__ void pixel2_ints<B2_ARITH_REFERENCE>(const ColorMat& m, float2 by,
+                                                                const Chroma2& c, float2& r,
+                                                                float2& g, float2& b) {
   const float2 g2 = dup2(m.g), unit = dup2(__uint_as_float(1u));  // 2^-149
   const float2 fy = x2_add(by, dup2(-m.y_bias));
   const float2 ly = x2_fma(g2, fy, dup2(m.neg_zero));
@@ -196,6 +264,7 @@ struct DenseLaunch {
   int64_t dst_frame_stride;  // elements
   int layout, dtype, order;
   ScaleBias sb;
+  int arith;  // b2_arith; `mat` must come from color_matrix(..., arith)
 };
 int launch_dense(const DenseLaunch& L, cudaStream_t stream);
 

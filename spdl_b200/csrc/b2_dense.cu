@@ -87,7 +87,7 @@ constexpr int kDenseThreads = 128;
 // or 256 slower); caps the kernel at 40 registers per thread.
 constexpr int kDenseMinBlocks = 12;
 
-template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE>
+template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE, int ARITH>
 __global__ void __launch_bounds__(kDenseThreads, kDenseMinBlocks) dense_vec_kernel(const DenseParams p) {
   using T = typename OutT<DTYPE>::type;
   constexpr int PX = 16 / (int)sizeof(T);  // pixels per thread per row
@@ -153,11 +153,11 @@ __global__ void __launch_bounds__(kDenseThreads, kDenseMinBlocks) dense_vec_kern
       // chroma of the two 2x2 quads under luma word j: lane x = first quad, lane y = second
       Chroma2 c;
       if constexpr (FMT == B2_SRC_NV12) {
-        c = chroma2_of(m, make_float2(biased_byte(uw[j], 0), biased_byte(uw[j], 2)),
+        c = chroma2_of<ARITH>(m, make_float2(biased_byte(uw[j], 0), biased_byte(uw[j], 2)),
                        make_float2(biased_byte(uw[j], 1), biased_byte(uw[j], 3)));
       } else {
         const int w = j >> 1, b = (j & 1) * 2;
-        c = chroma2_of(m, make_float2(biased_byte(uw[w], b), biased_byte(uw[w], b + 1)),
+        c = chroma2_of<ARITH>(m, make_float2(biased_byte(uw[w], b), biased_byte(uw[w], b + 1)),
                        make_float2(biased_byte(vw[w], b), biased_byte(vw[w], b + 1)));
       }
 #pragma unroll
@@ -168,7 +168,7 @@ __global__ void __launch_bounds__(kDenseThreads, kDenseMinBlocks) dense_vec_kern
         for (int k = 0; k < 2; ++k) {  // pixels k and k+2 share one packed instruction stream
           float2 cr, cg, cb;
           const float2 by = make_float2(biased_byte(yw[r][j], k), biased_byte(yw[r][j], k + 2));
-          pixel2_ints(m, by, c, cr, cg, cb);
+          pixel2_ints<ARITH>(m, by, c, cr, cg, cb);
           ch[BGR ? 2 : 0][k] = cr.x; ch[BGR ? 2 : 0][k + 2] = cr.y;
           ch[1][k] = cg.x;           ch[1][k + 2] = cg.y;
           ch[BGR ? 0 : 2][k] = cb.x; ch[BGR ? 0 : 2][k + 2] = cb.y;
@@ -279,7 +279,7 @@ __global__ void __launch_bounds__(kDenseThreads, kDenseMinBlocks) dense_vec_kern
 // One thread's block of ROWS (1 or 2) rows x PX pixels under one chroma row: luma words yw,
 // chroma words uw (and vw for I420) in, 48 bytes per row out, already in destination order (interleaved: linear; planar: 16 bytes per
 // output slot).  The same arithmetic as the vector kernel's inner loop.
-template <int FMT, int LAYOUT, int DTYPE, bool BGR, int NW, int UVW, int ROWS>
+template <int FMT, int LAYOUT, int DTYPE, bool BGR, int ARITH, int NW, int UVW, int ROWS>
 __device__ __forceinline__ void convert_chunk(const ColorMat& m, const ScaleBias& sb,
                                               const uint32_t (&yw)[ROWS][NW],
                                               const uint32_t (&uw)[UVW],
@@ -289,11 +289,11 @@ __device__ __forceinline__ void convert_chunk(const ColorMat& m, const ScaleBias
   for (int j = 0; j < NW; ++j) {
     Chroma2 c;
     if constexpr (FMT == B2_SRC_NV12) {
-      c = chroma2_of(m, make_float2(biased_byte(uw[j], 0), biased_byte(uw[j], 2)),
+      c = chroma2_of<ARITH>(m, make_float2(biased_byte(uw[j], 0), biased_byte(uw[j], 2)),
                      make_float2(biased_byte(uw[j], 1), biased_byte(uw[j], 3)));
     } else {
       const int w = j >> 1, b = (j & 1) * 2;
-      c = chroma2_of(m, make_float2(biased_byte(uw[w], b), biased_byte(uw[w], b + 1)),
+      c = chroma2_of<ARITH>(m, make_float2(biased_byte(uw[w], b), biased_byte(uw[w], b + 1)),
                      make_float2(biased_byte(vw[w], b), biased_byte(vw[w], b + 1)));
     }
 #pragma unroll
@@ -303,7 +303,7 @@ __device__ __forceinline__ void convert_chunk(const ColorMat& m, const ScaleBias
       for (int k = 0; k < 2; ++k) {
         float2 cr, cg, cb;
         const float2 by = make_float2(biased_byte(yw[r][j], k), biased_byte(yw[r][j], k + 2));
-        pixel2_ints(m, by, c, cr, cg, cb);
+        pixel2_ints<ARITH>(m, by, c, cr, cg, cb);
         ch[BGR ? 2 : 0][k] = cr.x; ch[BGR ? 2 : 0][k + 2] = cr.y;
         ch[1][k] = cg.x;           ch[1][k + 2] = cg.y;
         ch[BGR ? 0 : 2][k] = cb.x; ch[BGR ? 0 : 2][k + 2] = cb.y;
@@ -370,7 +370,7 @@ __device__ __forceinline__ void convert_chunk(const ColorMat& m, const ScaleBias
 
 constexpr int kWindowThreads = 128;
 
-template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE>
+template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE, int ARITH>
 __global__ void __launch_bounds__(kWindowThreads) dense_window_kernel(const DenseParams p) {
   using T = typename OutT<DTYPE>::type;
   constexpr int ESZ = (int)sizeof(T);
@@ -418,7 +418,7 @@ __global__ void __launch_bounds__(kWindowThreads) dense_window_kernel(const Dens
       load_window<UVB>(vb + uv_off, x0 / 2, we / 2, vw);
     }
     (void)vw;
-    convert_chunk<FMT, LAYOUT, DTYPE, BGR>(p.mat, p.sb, yw, uw, vw, out);
+    convert_chunk<FMT, LAYOUT, DTYPE, BGR, ARITH>(p.mat, p.sb, yw, uw, vw, out);
   }
 
   if constexpr (LAYOUT == B2_NCHW) {
@@ -544,7 +544,7 @@ __device__ __forceinline__ void warp_store(uint8_t* g, const unsigned char* s, i
 constexpr int kShiftThreads = 128;
 constexpr int kShiftWarpSmem = 2 * 1536 + 16;  // two interleaved or six planar row segments
 
-template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE>
+template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE, int ARITH>
 __global__ void __launch_bounds__(kShiftThreads) dense_shift_kernel(const DenseParams p) {
   using T = typename OutT<DTYPE>::type;
   constexpr int ESZ = (int)sizeof(T);
@@ -598,7 +598,7 @@ __global__ void __launch_bounds__(kShiftThreads) dense_shift_kernel(const DenseP
   }
   (void)vw;
   uint32_t out[2][12];
-  convert_chunk<FMT, LAYOUT, DTYPE, BGR>(p.mat, p.sb, yw, uw, vw, out);
+  convert_chunk<FMT, LAYOUT, DTYPE, BGR, ARITH>(p.mat, p.sb, yw, uw, vw, out);
 #pragma unroll
   for (int r = 0; r < 2; ++r)
 #pragma unroll
@@ -633,7 +633,7 @@ __global__ void __launch_bounds__(kShiftThreads) dense_shift_kernel(const DenseP
 
 inline bool mult(long long v, long long m) { return v % m == 0; }
 
-template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE>
+template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE, int ARITH>
 int launch_t(const DenseLaunch& L, const DenseParams& p, bool vec, cudaStream_t stream) {
   using T = typename OutT<DTYPE>::type;
   constexpr int PX = 16 / (int)sizeof(T);
@@ -666,18 +666,18 @@ int launch_t(const DenseLaunch& L, const DenseParams& p, bool vec, cudaStream_t 
       const int by = kDenseThreads / bx;
       dim3 block(bx, by), grid((chunks + bx - 1) / bx, (He / 2 + by - 1) / by, nn);
       const size_t smem = LAYOUT == B2_NHWC ? (size_t)(kDenseThreads / 32) * 2 * 32 * 48 : 0;
-      dense_vec_kernel<FMT, LAYOUT, DTYPE, BGR, TABLE><<<grid, block, smem, stream>>>(q);
+      dense_vec_kernel<FMT, LAYOUT, DTYPE, BGR, TABLE, ARITH><<<grid, block, smem, stream>>>(q);
     } else if (window) {
       if (He < 2) continue;
       const int chunks = ((L.width & ~1) + 2 * PX - 2) / PX;  // the grid slides by up to PX-1 pixels
       dim3 grid((chunks + kWindowThreads - 1) / kWindowThreads, He, nn);
       const size_t smem = LAYOUT == B2_NHWC ? (size_t)(kWindowThreads / 32) * 1536 : 0;
-      dense_window_kernel<FMT, LAYOUT, DTYPE, BGR, TABLE><<<grid, kWindowThreads, smem, stream>>>(q);
+      dense_window_kernel<FMT, LAYOUT, DTYPE, BGR, TABLE, ARITH><<<grid, kWindowThreads, smem, stream>>>(q);
     } else {
       if (He < 2) continue;
       const int per_cta = kShiftThreads * PX;  // pixels of a row per CTA
       dim3 grid(((L.width & ~1) + per_cta - 1) / per_cta, He / 2, nn);
-      dense_shift_kernel<FMT, LAYOUT, DTYPE, BGR, TABLE>
+      dense_shift_kernel<FMT, LAYOUT, DTYPE, BGR, TABLE, ARITH>
           <<<grid, kShiftThreads, (kShiftThreads / 32) * kShiftWarpSmem, stream>>>(q);
     }
     B2_CUDA(cudaPeekAtLastError(), "launch of the dense conversion kernel failed");
@@ -685,21 +685,26 @@ int launch_t(const DenseLaunch& L, const DenseParams& p, bool vec, cudaStream_t 
   return B2_OK;
 }
 
-template <int FMT, int LAYOUT, int DTYPE>
+template <int FMT, int LAYOUT, int DTYPE, int ARITH>
 int launch_fld(const DenseLaunch& L, const DenseParams& p, bool vec, cudaStream_t s) {
   const bool bgr = L.order == B2_BGR, table = L.y_table != nullptr;
-  if (bgr) return table ? launch_t<FMT, LAYOUT, DTYPE, true, true>(L, p, vec, s)
-                        : launch_t<FMT, LAYOUT, DTYPE, true, false>(L, p, vec, s);
-  return table ? launch_t<FMT, LAYOUT, DTYPE, false, true>(L, p, vec, s)
-               : launch_t<FMT, LAYOUT, DTYPE, false, false>(L, p, vec, s);
+  if (bgr) return table ? launch_t<FMT, LAYOUT, DTYPE, true, true, ARITH>(L, p, vec, s)
+                        : launch_t<FMT, LAYOUT, DTYPE, true, false, ARITH>(L, p, vec, s);
+  return table ? launch_t<FMT, LAYOUT, DTYPE, false, true, ARITH>(L, p, vec, s)
+               : launch_t<FMT, LAYOUT, DTYPE, false, false, ARITH>(L, p, vec, s);
+}
+template <int FMT, int LAYOUT, int ARITH>
+int launch_fla(const DenseLaunch& L, const DenseParams& p, bool vec, cudaStream_t s) {
+  switch (L.dtype) {
+    case B2_U8: return launch_fld<FMT, LAYOUT, B2_U8, ARITH>(L, p, vec, s);
+    case B2_F32: return launch_fld<FMT, LAYOUT, B2_F32, ARITH>(L, p, vec, s);
+    default: return launch_fld<FMT, LAYOUT, B2_BF16, ARITH>(L, p, vec, s);
+  }
 }
 template <int FMT, int LAYOUT>
 int launch_fl(const DenseLaunch& L, const DenseParams& p, bool vec, cudaStream_t s) {
-  switch (L.dtype) {
-    case B2_U8: return launch_fld<FMT, LAYOUT, B2_U8>(L, p, vec, s);
-    case B2_F32: return launch_fld<FMT, LAYOUT, B2_F32>(L, p, vec, s);
-    default: return launch_fld<FMT, LAYOUT, B2_BF16>(L, p, vec, s);
-  }
+  return L.arith == B2_ARITH_SWSCALE ? launch_fla<FMT, LAYOUT, B2_ARITH_SWSCALE>(L, p, vec, s)
+                                     : launch_fla<FMT, LAYOUT, B2_ARITH_REFERENCE>(L, p, vec, s);
 }
 
 }  // namespace

@@ -19,17 +19,20 @@ with the permute / float / normalise / resize steps that reference users run as 
 from __future__ import annotations
 
 import ctypes
+import threading
 from typing import Any, Sequence
 
 import numpy as np
 
 from .. import _lib
-from .._lib import BF16, BGR, F32, I420, NCHW, NHWC, NV12, RGB, U8
+from .._lib import (ARITH_REFERENCE, ARITH_SWSCALE, BF16, BGR, F32, I420, NCHW, NHWC, NV12, RGB,
+                    U8)
 from ._types import CPUBuffer, CUDABuffer, CUDAConfig, cuda_buffer
 from .utils import _tracing
 
 __all__ = [
     "nv12_to_rgb", "nv12_to_bgr", "convert_nv12", "convert_resize", "make_image_descs",
+    "check_resize_status",
     "transfer_buffer", "transfer_buffer_cpu", "synchronize_stream", "FrameBatcher",
     "frame_checksum", "DESC_DTYPE",
 ]
@@ -38,7 +41,7 @@ __all__ = [
 DESC_DTYPE = np.dtype(
     [("y_off", "<u8"), ("u_off", "<u8"), ("v_off", "<u8"), ("y_pitch", "<i4"), ("uv_pitch", "<i4"),
      ("src_w", "<i4"), ("src_h", "<i4"), ("crop_x", "<i4"), ("crop_y", "<i4"),
-     ("scale_x", "<f4"), ("scale_y", "<f4"), ("reserved", "<i4", (2,))]
+     ("scale_x", "<f4"), ("scale_y", "<f4"), ("resized_w", "<i4"), ("resized_h", "<i4")]
 )
 
 _LAYOUTS = {"NCHW": NCHW, "NHWC": NHWC, NCHW: NCHW, NHWC: NHWC}
@@ -49,6 +52,14 @@ RGB_PLANAR, RGB_INTERLEAVED = 2, 3
 _FORMATS = {"nv12": NV12, "i420": I420, "yuv420p": I420, "rgb_planar": RGB_PLANAR,
             "rgb24": RGB_INTERLEAVED, "rgb_interleaved": RGB_INTERLEAVED}
 _OUT_ELEM = {U8: ("u", 1), F32: ("f", 4), BF16: ("u", 2)}  # bf16 is exposed as 2-byte words
+_ARITHS = {"reference": ARITH_REFERENCE, "cuda": ARITH_REFERENCE, "swscale": ARITH_SWSCALE,
+           "ffmpeg": ARITH_SWSCALE}
+_STATUS_TEXT = {
+    _lib.STATUS_IMAGE_TOO_WIDE: "an image is wider than max_src_w and was skipped",
+    _lib.STATUS_WAIT_EXPIRED: "a wait for staged source rows ran out and output rows were skipped",
+    _lib.STATUS_BAD_GEOMETRY: "a descriptor has an empty source or a non-positive scale and was "
+                              "skipped",
+}
 
 
 def _cai(obj: Any) -> tuple[int, tuple[int, ...], str]:
@@ -60,14 +71,14 @@ def _cai(obj: Any) -> tuple[int, tuple[int, ...], str]:
             f"found {type(obj).__name__}.")
     shape = tuple(int(s) for s in iface["shape"])
     strides = iface.get("strides")
-    if strides is not None:
-        item = int(iface["typestr"][2:])
-        expect, acc = [], item
-        for s in reversed(shape):
-            expect.append(acc)
-            acc *= s
-        if tuple(strides) != tuple(reversed(expect)) and all(s > 1 for s in shape):
-            raise RuntimeError("The input CUDA array must be C-contiguous.")
+    if strides is not None and 0 not in shape:
+        # The stride of a dimension of size 1 never enters an address, so producers may report
+        # anything for it; every other dimension must have the packed stride.
+        acc = int(iface["typestr"][2:])
+        for size, stride in zip(reversed(shape), reversed(tuple(strides))):
+            if size != 1 and int(stride) != acc:
+                raise RuntimeError("The input CUDA array must be C-contiguous.")
+            acc *= size
     return int(iface["data"][0]), shape, iface["typestr"]
 
 
@@ -164,9 +175,14 @@ def nv12_to_bgr(buffers: Any, *, device_config: CUDAConfig, coeff: int = 1,
 def convert_nv12(buffers: Any, *, device_config: CUDAConfig, coeff: int = 1,
                  full_range: bool = False, src_format: str = "nv12", layout: str = "NCHW",
                  dtype: str = "uint8", order: str = "rgb", mean=None, std=None,
-                 sync: bool = False) -> CUDABuffer:
+                 arith: str = "reference", sync: bool = False) -> CUDABuffer:
     """Convert ``[N, H*1.5, W]`` NV12 or I420 frames in one pass to ``NCHW``/``NHWC``
     ``uint8``/``float32``/``bfloat16`` RGB or BGR, optionally normalised.
+
+    ``arith="reference"`` computes what the reference's CUDA kernel computes;
+    ``arith="swscale"`` computes what its CPU route computes (libswscale's integer yuv420p ->
+    rgb24 conversion, the end of the ``format=pix_fmts=rgb24`` filter graph), with ``coeff`` read
+    as libswscale's colourspace number (1 BT.709; 5, 6 and anything unknown BT.601).
 
     For float outputs the value is ``(v/255 - mean)/std`` per output channel when ``mean``/
     ``std`` are given (0..1 units, in output channel order), else the plain 0..255 value.
@@ -185,8 +201,8 @@ def convert_nv12(buffers: Any, *, device_config: CUDAConfig, coeff: int = 1,
         raise RuntimeError(
             f"The height of NV12 image (h*1.5) must be divisible by 3. Found: {h2}")
     try:
-        fmt, lay, dt, od = (_FORMATS[src_format.lower()], _LAYOUTS[layout], _DTYPES[dtype],
-                            _ORDERS[order.lower()])
+        fmt, lay, dt, od, ar = (_FORMATS[src_format.lower()], _LAYOUTS[layout], _DTYPES[dtype],
+                                _ORDERS[order.lower()], _ARITHS[arith.lower()])
     except KeyError as e:
         raise RuntimeError(f"Unsupported option: {e}") from None
     h = h2 // 3 * 2
@@ -211,7 +227,7 @@ def convert_nv12(buffers: Any, *, device_config: CUDAConfig, coeff: int = 1,
     a.src_format, a.width, a.height, a.num_frames = fmt, w, h, n
     a.matrix_coeff, a.full_range = int(coeff), int(bool(full_range))
     a.dst, a.dst_frame_stride = out.data_ptr, 0
-    a.layout, a.dtype, a.order = lay, dt, od
+    a.layout, a.dtype, a.order, a.arith = lay, dt, od, ar
     a.scale = (ctypes.c_float * 3)(*scale.tolist())
     a.bias = (ctypes.c_float * 3)(*bias.tolist())
     with _tracing.trace_event("b2::convert_dense"):
@@ -230,8 +246,8 @@ def make_image_descs(widths: Sequence[int], heights: Sequence[int], *, src_forma
                      offsets: Sequence[int] | None = None, resize: tuple[int, int] | None = None,
                      resize_shorter: int | None = None, crop: tuple[int, int] | None = None,
                      out_size: tuple[int, int] | None = None,
-                     src_crop: tuple[int, int, int, int] | None = None
-                     ) -> tuple[np.ndarray, tuple[int, int]]:
+                     src_crop: tuple[int, int, int, int] | None = None,
+                     scale_mode: str | None = None) -> tuple[np.ndarray, tuple[int, int]]:
     """Build the descriptor table of a (possibly ragged) packed batch.
 
     Images are packed back to back (``offsets[i]`` = byte offset of image ``i``; computed when
@@ -241,6 +257,16 @@ def make_image_descs(widths: Sequence[int], heights: Sequence[int], *, src_forma
     Geometry: ``resize=(w, h)`` stretches every image to that size; ``resize_shorter=s`` scales
     the shorter side to ``s`` and the longer to ``int(s * long / short)``; then
     ``crop=(w, h)`` takes the centre window with offset ``int(round((dim - crop) / 2))``.
+    ``scale_mode`` (with ``resize``) keeps the aspect ratio the way the reference's filter
+    strings do (``src/spdl/io/_preprocessing.py:214-229``; ``"pad"`` is the reference's default):
+    ``"pad"`` scales the image to fit inside ``w x h``
+    (``scale=...:force_original_aspect_ratio=decrease``: the other side becomes
+    ``min(round(h * iw / ih), w)`` resp. ``min(round(w * ih / iw), h)``) and centres it on a
+    ``w x h`` canvas (``pad=w:h:x=-1:y=-1``: offset ``(w - iw) // 2``, rounded down to an even
+    number for 4:2:0 sources, as the pad filter aligns to the chroma grid); pixels outside the
+    image take ``convert_resize``'s ``pad_color``.  ``"crop"`` scales the image to cover
+    ``w x h`` (``force_original_aspect_ratio=increase``) and cuts the centre ``w x h`` window
+    (``crop=w:h``: offset ``(iw - w) // 2``, even for 4:2:0 sources).
     ``src_crop=(left, top, right, bottom)`` first cuts that many pixels off each side of every
     source image, the order of the reference's decoder options (crop, then scale:
     ``src/libspdl/cuda/nvdec/detail/utils.cpp:133-220``); for NV12/I420 the four values must be
@@ -269,7 +295,34 @@ def make_image_descs(widths: Sequence[int], heights: Sequence[int], *, src_forma
         off = np.asarray(offsets, np.int64)
     if resize is not None and resize_shorter is not None:
         raise RuntimeError("give either resize or resize_shorter")
-    if resize is not None:
+    if scale_mode not in (None, "pad", "crop"):
+        raise ValueError(f"Unexpected `scale_mode` value ({scale_mode}). "
+                         'Expected values are "pad", "crop", or None.')
+    if scale_mode is not None and resize is None:
+        raise RuntimeError("scale_mode needs resize=(w, h)")
+    # (px, py): where the resized image starts on the canvas that crop / the output window refer
+    # to; (canvas_w, canvas_h): that canvas.  Without scale_mode the canvas is the resized image.
+    px = py = np.zeros(n, np.int64)
+    canvas = None
+    if resize is not None and scale_mode is not None:
+        tw_, th_ = int(resize[0]), int(resize[1])
+        if tw_ < 1 or th_ < 1:
+            raise RuntimeError("resize must be positive")
+        fit_w = (th_ * w + h // 2) // h  # round(th * iw / ih), halves away from zero
+        fit_h = (tw_ * h + w // 2) // w
+        pick = np.minimum if scale_mode == "pad" else np.maximum
+        rw = np.maximum(pick(fit_w, tw_), 1)
+        rh = np.maximum(pick(fit_h, th_), 1)
+        # distance between the canvas and the image origins: the canvas is larger in "pad" mode
+        # (vf_pad: x = (w - iw) / 2), the image in "crop" mode (vf_crop: x = (iw - w) / 2)
+        px, py = np.abs(tw_ - rw) // 2, np.abs(th_ - rh) // 2
+        if fmt in (NV12, I420):
+            # both filters place 4:2:0 frames on the chroma grid (round down)
+            px, py = px - (px % 2), py - (py % 2)
+        if scale_mode == "crop":
+            px, py = -px, -py
+        canvas = (np.full(n, tw_, np.int64), np.full(n, th_, np.int64))
+    elif resize is not None:
         rw = np.full(n, int(resize[0]), np.int64)
         rh = np.full(n, int(resize[1]), np.int64)
     elif resize_shorter is not None:
@@ -278,17 +331,19 @@ def make_image_descs(widths: Sequence[int], heights: Sequence[int], *, src_forma
         rh = np.where(w <= h, (s * h) // w, s)
     else:
         rw, rh = w.copy(), h.copy()
+    cvw, cvh = canvas if canvas is not None else (rw, rh)
     if crop is not None:
         ow, oh = int(crop[0]), int(crop[1])
-        if np.any(rw < ow) or np.any(rh < oh):
+        if np.any(cvw < ow) or np.any(cvh < oh):
             raise RuntimeError("crop window larger than the resized image")
-        cx = np.rint((rw - ow) / 2.0).astype(np.int64)
-        cy = np.rint((rh - oh) / 2.0).astype(np.int64)
+        cx = np.rint((cvw - ow) / 2.0).astype(np.int64)
+        cy = np.rint((cvh - oh) / 2.0).astype(np.int64)
     else:
-        if n and (np.any(rw != rw[0]) or np.any(rh != rh[0])):
+        if n and (np.any(cvw != cvw[0]) or np.any(cvh != cvh[0])):
             raise RuntimeError("without crop every image must resize to the same size")
-        ow, oh = (int(rw[0]), int(rh[0])) if n else (0, 0)
+        ow, oh = (int(cvw[0]), int(cvh[0])) if n else (0, 0)
         cx = cy = np.zeros(n, np.int64)
+    cx, cy = cx - px, cy - py  # output (0,0) in the resized image's own grid
     if out_size is not None and tuple(out_size) != (ow, oh):
         raise RuntimeError(f"out_size {out_size} does not match the geometry {(ow, oh)}")
     d = np.zeros(n, DESC_DTYPE)
@@ -336,19 +391,67 @@ def make_image_descs(widths: Sequence[int], heights: Sequence[int], *, src_forma
     d["crop_x"], d["crop_y"] = cx, cy
     d["scale_x"] = w.astype(np.float32) / rw.astype(np.float32)
     d["scale_y"] = h.astype(np.float32) / rh.astype(np.float32)
+    if scale_mode == "pad":
+        d["resized_w"], d["resized_h"] = rw, rh  # beyond this the kernel writes the pad colour
     return d, (ow, oh)
+
+
+_status_lock = threading.Lock()
+_status_words: dict[tuple[int, int], CUDABuffer] = {}
+
+
+def _status_word(cfg: CUDAConfig) -> CUDABuffer:
+    """The device word ``b2_convert_resize`` reports skipped work in: one per (device, stream),
+    zeroed when it is created and again after every non-zero reading."""
+    key = (cfg.device_index, int(cfg.stream))
+    with _status_lock:
+        word = _status_words.get(key)
+        if word is None:
+            word = _status_words[key] = transfer_buffer(np.zeros(1, np.int32), device_config=cfg)
+    return word
+
+
+def check_resize_status(device_config: CUDAConfig) -> None:
+    """Wait for the stream and raise ``RuntimeError`` if any ``convert_resize`` call queued on it
+    since the last check left output unwritten (see ``b2_resize_status_bits``)."""
+    word = _status_word(device_config)
+    synchronize_stream(device_config)
+    host = np.zeros(1, np.int32)
+    _lib.check(_lib.lib().b2_transfer_d2h(host.ctypes.data, word.data_ptr, 4,
+                                          device_config.device_index))
+    bits = int(host[0])
+    if bits:
+        zero = np.zeros(1, np.int32)
+        _lib.check(_lib.lib().b2_transfer_h2d(word.data_ptr, zero.ctypes.data, 4, 0,
+                                              device_config.device_index, device_config.stream))
+        what = "; ".join(t for b, t in _STATUS_TEXT.items() if bits & b)
+        raise RuntimeError(f"convert_resize left output unwritten: {what} (status {bits})")
 
 
 def convert_resize(base: Any, descs: Any, *, out_size: tuple[int, int], max_src_w: int,
                    device_config: CUDAConfig, src_format: str = "nv12", coeff: int = 1,
                    full_range: bool = False, layout: str = "NCHW", dtype: str = "uint8",
-                   order: str = "rgb", mean=None, std=None, sync: bool = False) -> CUDABuffer:
-    """Fused colour conversion, bilinear resize, crop and normalise over a packed batch.
+                   order: str = "rgb", mean=None, std=None, arith: str = "reference",
+                   pad_color: tuple[float, float, float] = (0.0, 0.0, 0.0),
+                   clip_frames: int | None = None, sync: bool = False,
+                   _debug_flags: int = 0) -> CUDABuffer:
+    """Fused colour conversion, bilinear resize, crop / letterbox and normalise over a packed
+    batch.
 
     ``base`` is a device byte buffer holding every image, ``descs`` a device copy of the table
     from :func:`make_image_descs` (``[N]`` of ``DESC_DTYPE``, i.e. ``N*64`` bytes), ``out_size``
     is ``(out_w, out_h)`` and ``max_src_w`` the widest source image in the table.
-    Returns ``[N,3,out_h,out_w]`` (``NCHW``) or ``[N,out_h,out_w,3]``.
+    Returns ``[N,3,out_h,out_w]`` (``NCHW``) or ``[N,out_h,out_w,3]``.  With ``clip_frames=T``
+    (planar layout, ``N`` a multiple of ``T``) consecutive groups of ``T`` images are stacked as
+    clips in the channel-first video layout ``[N/T, 3, T, out_h, out_w]`` that
+    ``examples/video_classification/utils/pipeline.py:137`` reaches with a ``permute``.
+    ``pad_color`` is the R, G, B (0..255) of letterbox pixels (``scale_mode="pad"``).
+    ``arith`` as in :func:`convert_nv12`.
+
+    The table lives in device memory, so what the host cannot check -- an image wider than
+    ``max_src_w``, a nonsensical descriptor -- is reported by the kernel in a device status word:
+    with ``sync=True`` the call raises ``RuntimeError`` when any image or row was skipped; with
+    ``sync=False`` call :func:`check_resize_status` at a point where waiting is acceptable.
     """
     bptr, _, _ = _cai(base)
     dptr, dshape, dtypestr = _cai(descs)
@@ -357,33 +460,47 @@ def convert_resize(base: Any, descs: Any, *, out_size: tuple[int, int], max_src_
         raise RuntimeError("descs must be a whole number of 64-byte descriptors")
     n = nbytes // 64
     try:
-        fmt, lay, dt, od = (_FORMATS[src_format.lower()], _LAYOUTS[layout], _DTYPES[dtype],
-                            _ORDERS[order.lower()])
+        fmt, lay, dt, od, ar = (_FORMATS[src_format.lower()], _LAYOUTS[layout], _DTYPES[dtype],
+                                _ORDERS[order.lower()], _ARITHS[arith.lower()])
     except KeyError as e:
         raise RuntimeError(f"Unsupported option: {e}") from None
     ow, oh = int(out_size[0]), int(out_size[1])
     _device_of(base, device_config)
     ec, depth = _OUT_ELEM[dt]
     oshape = (n, 3, oh, ow) if lay == NCHW else (n, oh, ow, 3)
+    t = int(clip_frames) if clip_frames else 0
+    if t:
+        if lay != NCHW:
+            raise RuntimeError("clip_frames needs the planar (NCHW) layout")
+        if t < 1 or n % t:
+            raise RuntimeError(f"{n} images do not divide into clips of {t} frames")
+        oshape = (n // t, 3, t, oh, ow)
     out = cuda_buffer(oshape, device_config, ec, depth)
     scale, bias = _scale_bias(mean, std)
+    status = _status_word(device_config)
     a = _lib.ResizeArgs()
     a.struct_size = ctypes.sizeof(_lib.ResizeArgs)
     a.device = device_config.device_index
     a.base, a.descs = bptr, dptr
     a.num_images, a.src_format, a.out_w, a.out_h = n, fmt, ow, oh
     a.matrix_coeff, a.full_range = int(coeff), int(bool(full_range))
-    a.layout, a.dtype, a.order = lay, dt, od
+    a.layout, a.dtype, a.order, a.arith = lay, dt, od, ar
     a.max_src_w = int(max_src_w)
     a.dst, a.dst_image_stride = out.data_ptr, 0
+    if t:
+        a.frames_per_group, a.dst_image_stride = t, oh * ow
+        a.dst_plane_stride, a.dst_group_stride = t * oh * ow, 3 * t * oh * ow
     a.scale = (ctypes.c_float * 3)(*scale.tolist())
     a.bias = (ctypes.c_float * 3)(*bias.tolist())
+    a.pad_value = (ctypes.c_float * 3)(*[float(v) for v in pad_color])
+    a.debug_flags = int(_debug_flags)
+    a.status = status.data_ptr
     with _tracing.trace_event("b2::convert_resize"):
         _lib.check(_lib.lib().b2_convert_resize(ctypes.byref(a), device_config.stream))
     _tracing.record("convert_resize", n, 0, out.nbytes)
     out._owner = (base, descs)
     if sync:
-        synchronize_stream(device_config)
+        check_resize_status(device_config)
     return out
 
 
@@ -400,6 +517,8 @@ class _DeviceSpan:
 def resize_image_list(images: Sequence[Any], *, device_config: CUDAConfig,
                       src_format: str = "rgb24", resize: tuple[int, int] | None = None,
                       resize_shorter: int | None = None, crop: tuple[int, int] | None = None,
+                      scale_mode: str | None = None,
+                      pad_color: tuple[float, float, float] = (0.0, 0.0, 0.0),
                       layout: str = "NCHW", dtype: str = "uint8", order: str = "rgb", mean=None,
                       std=None, sync: bool = False) -> CUDABuffer:
     """Resize, crop and normalise a list of decoded images of different sizes in one launch.
@@ -431,12 +550,13 @@ def resize_image_list(images: Sequence[Any], *, device_config: CUDAConfig,
     base = min(ptrs)
     end = max(p + 3 * w * h for p, w, h in zip(ptrs, ws, hs))
     descs, out_size = make_image_descs(ws, hs, src_format=fmt, offsets=[p - base for p in ptrs],
-                                       resize=resize, resize_shorter=resize_shorter, crop=crop)
+                                       resize=resize, resize_shorter=resize_shorter, crop=crop,
+                                       scale_mode=scale_mode)
     table = transfer_buffer(descs.view(np.uint8), device_config=device_config)
     out = convert_resize(_DeviceSpan(base, end - base, device_config.device_index), table,
                          out_size=out_size, max_src_w=max(ws), device_config=device_config,
                          src_format=fmt, layout=layout, dtype=dtype, order=order, mean=mean,
-                         std=std, sync=sync)
+                         std=std, pad_color=pad_color, sync=sync)
     out._owner = (list(images), table)  # inputs must outlive the queued kernel
     return out
 

@@ -21,8 +21,7 @@ from typing import Any
 import numpy as np
 
 from ._convert import to_torch
-from ._core import (convert_nv12, convert_resize, make_image_descs, synchronize_stream,
-                    transfer_buffer)
+from ._core import convert_nv12, convert_resize, make_image_descs, transfer_buffer
 from ._types import CPUBuffer, CUDAConfig, cuda_config
 
 __all__ = ["FrameStage"]
@@ -34,22 +33,32 @@ class FrameStage:
     ``frames`` is a :class:`CPUBuffer` from ``convert_frames`` (a leading batch/plane dimension
     of size 1 is squeezed) or a ``uint8`` NumPy array.  Without ``resize``/``resize_shorter`` the
     frames are converted at full size; otherwise they are resized (and centre-cropped with
-    ``crop``) in the same kernel.  ``dtype="bfloat16"`` returns a ``torch.bfloat16`` tensor.
+    ``crop``, or letterboxed / cover-cropped with ``scale_mode`` as the reference's filter
+    strings do) in the same kernel.  ``clip_frames=T`` stacks every ``T`` frames as a clip in the
+    channel-first video layout ``[N/T, 3, T, h, w]``.  ``arith="swscale"`` reproduces the pixels
+    of the reference's CPU route (libswscale) instead of those of its CUDA kernel.
+    ``dtype="bfloat16"`` returns a ``torch.bfloat16`` tensor.
     """
 
     def __init__(self, *, src_format: str = "i420", layout: str = "NCHW", dtype: str = "float32",
                  order: str = "rgb", coeff: int = 1, full_range: bool = False, mean=None, std=None,
                  resize: tuple[int, int] | None = None, resize_shorter: int | None = None,
-                 crop: tuple[int, int] | None = None, num_caches: int = 4,
+                 crop: tuple[int, int] | None = None, scale_mode: str | None = None,
+                 pad_color: tuple[float, float, float] = (0.0, 0.0, 0.0),
+                 clip_frames: int | None = None, arith: str = "reference", num_caches: int = 4,
                  device_index: int | None = None) -> None:
         if num_caches < 0:
             raise RuntimeError("num_caches must be non-negative")
         if crop is not None and resize is None and resize_shorter is None:
             raise RuntimeError("crop needs resize or resize_shorter")
         self._opts = dict(src_format=src_format, layout=layout, dtype=dtype, order=order,
-                          coeff=coeff, full_range=full_range, mean=mean, std=std)
-        self._geom = dict(resize=resize, resize_shorter=resize_shorter, crop=crop)
+                          coeff=coeff, full_range=full_range, mean=mean, std=std, arith=arith)
+        self._geom = dict(resize=resize, resize_shorter=resize_shorter, crop=crop,
+                          scale_mode=scale_mode)
         self._resizing = resize is not None or resize_shorter is not None
+        if clip_frames and not self._resizing:
+            raise RuntimeError("clip_frames needs resize or resize_shorter")
+        self._resize_opts = dict(pad_color=pad_color, clip_frames=clip_frames)
         self._num_caches = int(num_caches)
         self._device_index = device_index
         self._local = threading.local()
@@ -107,11 +116,11 @@ class FrameStage:
         dev = transfer_buffer(view, device_config=cfg)
         if self._resizing:
             descs, out = self._descs_for(st, n, w, h)
+            # sync=True waits for the stream once and checks the kernel's status word
             result = convert_resize(dev, descs, out_size=out, max_src_w=w, device_config=cfg,
-                                    **self._opts)
+                                    sync=True, **self._opts, **self._resize_opts)
         else:
-            result = convert_nv12(dev, device_config=cfg, **self._opts)
-        synchronize_stream(cfg)
+            result = convert_nv12(dev, device_config=cfg, sync=True, **self._opts)
         tensor = to_torch(result, torch.bfloat16 if self._opts["dtype"] in ("bfloat16", "bf16")
                           else None)
         if self._num_caches:

@@ -18,6 +18,7 @@ pytestmark = pytest.mark.gpu
 MEAN, STD = (0.485, 0.456, 0.406), (0.229, 0.224, 0.225)
 _O_DT = {"uint8": oracle.U8, "float32": oracle.F32, "bfloat16": oracle.BF16}
 _O_FMT = {"nv12": oracle.NV12, "i420": oracle.I420, "rgb_planar": oracle.RGBP, "rgb24": oracle.RGBI}
+_O_ARITH = {"reference": oracle.ARITH_REFERENCE, "swscale": oracle.ARITH_SWSCALE}
 
 
 def _dev(a):
@@ -56,9 +57,11 @@ def test_dense_random_cases(cuda_cfg, seed):
     h = int(r.integers(1, 20)) * 2
     nv = synth.nv12_batch(n, w, h, config=9, index=seed, full_range=True)
     norm = dict(mean=MEAN, std=STD) if dtype != "uint8" and r.integers(0, 2) else {}
+    arith = str(r.choice(["reference", "swscale"]))
     got = io.to_torch(io.convert_nv12(_dev(nv), device_config=cuda_cfg, src_format=fmt,
                                       layout=layout, dtype=dtype, order=order, coeff=coeff,
-                                      full_range=full, sync=True, **norm)).cpu().numpy()
+                                      full_range=full, arith=arith, sync=True,
+                                      **norm)).cpu().numpy()
     flat = nv.reshape(-1)
     h2 = h * 3 // 2
     if fmt == "nv12":
@@ -70,7 +73,7 @@ def test_dense_random_cases(cuda_cfg, seed):
         uv_frame_stride=h2 * w, src_format=_O_FMT[fmt],
         layout=oracle.NCHW if layout == "NCHW" else oracle.NHWC, dtype=_O_DT[dtype],
         order=oracle.RGB if order == "rgb" else oracle.BGR, coeff=coeff, full_range=full,
-        sb=oracle.scale_bias(MEAN, STD) if norm else None)
+        sb=oracle.scale_bias(MEAN, STD) if norm else None, arith=_O_ARITH[arith])
     _check(got, want, dtype)
 
 
@@ -94,8 +97,13 @@ def test_resize_random_cases(cuda_cfg, seed):
     sizes = ws * hs + 2 * ((ws + 1) // 2) * ((hs + 1) // 2) if yuv else 3 * ws * hs
     offs = np.concatenate([[0], np.cumsum(sizes)[:-1]])
     data = r.integers(0, 256, int(sizes.sum()), dtype=np.uint8)
-    mode = int(r.integers(0, 3))
-    if mode == 0:      # stretch to a fixed size (up- or down-scaling)
+    mode = int(r.integers(0, 5))
+    pad = (0.0, 0.0, 0.0)
+    if mode >= 3:      # keep the aspect ratio: letterbox (3) or cover and crop (4)
+        geom = dict(resize=(int(r.integers(2, 140)), int(r.integers(2, 140))),
+                    scale_mode="pad" if mode == 3 else "crop")
+        pad = tuple(float(v) for v in r.integers(0, 256, 3))
+    elif mode == 0:    # stretch to a fixed size (up- or down-scaling)
         geom = dict(resize=(int(r.integers(1, 120)), int(r.integers(1, 120))))
     elif mode == 1:    # shorter side + centre crop
         s = int(r.integers(8, 100))
@@ -106,16 +114,17 @@ def test_resize_random_cases(cuda_cfg, seed):
         geom = dict(resize=(rw, rh), crop=(int(r.integers(1, rw + 1)), int(r.integers(1, rh + 1))))
     descs, out = io.make_image_descs(ws, hs, src_format=fmt, offsets=offs, **geom)
     norm = dict(mean=MEAN, std=STD) if dtype != "uint8" and r.integers(0, 2) else {}
+    arith = str(r.choice(["reference", "swscale"]))
     buf = io.convert_resize(_dev(data), _dev(descs.view(np.uint8)), out_size=out,
                             max_src_w=int(ws.max()), device_config=cuda_cfg, src_format=fmt,
                             coeff=coeff, full_range=full, layout=layout, dtype=dtype, order=order,
-                            sync=True, **norm)
+                            arith=arith, pad_color=pad, sync=True, **norm)
     got = io.to_torch(buf).cpu().numpy()
     want = oracle.convert_resize(
         data, descs, out_w=out[0], out_h=out[1], src_format=_O_FMT[fmt], coeff=coeff,
         full_range=full, layout=oracle.NCHW if layout == "NCHW" else oracle.NHWC,
         dtype=_O_DT[dtype], order=oracle.RGB if order == "rgb" else oracle.BGR,
-        sb=oracle.scale_bias(MEAN, STD) if norm else None)
+        sb=oracle.scale_bias(MEAN, STD) if norm else None, arith=_O_ARITH[arith], pad_value=pad)
     _check(got, want, dtype)
 
 
@@ -182,6 +191,7 @@ def test_dense_random_memory_layouts(cuda_cfg, seed):
     a.y_pitch = a.uv_pitch = pitch
     a.src_format, a.width, a.height, a.num_frames = _lib.NV12, w, h, n
     a.matrix_coeff, a.full_range = 1, int(r.integers(0, 2))
+    a.arith = int(r.integers(0, 2))
     frame = 3 * h * w
     stride = frame + int(r.choice([0, 0, 16, 7, 2]))
     dst_off = int(r.integers(0, 4))
@@ -202,7 +212,7 @@ def test_dense_random_memory_layouts(cuda_cfg, seed):
         nv, nv.reshape(-1)[h * w:], None, width=w, height=h, num_frames=n, y_pitch=w, uv_pitch=w,
         y_frame_stride=h2 * w, uv_frame_stride=h2 * w, src_format=oracle.NV12,
         layout=oracle.NCHW if layout == "NCHW" else oracle.NHWC, dtype=_O_DT[dtype],
-        full_range=bool(a.full_range), sb=sb)
+        full_range=bool(a.full_range), sb=sb, arith=int(a.arith))
     we = w & ~1
     shape = (3, h, w) if layout == "NCHW" else (h, w, 3)
     cols = (slice(None), slice(None), slice(0, we)) if layout == "NCHW" else \

@@ -27,7 +27,7 @@ def test_library_exports_every_declared_symbol():
     handle = ctypes.CDLL(str(_lib.LIB_PATH))
     for name in declared:
         assert hasattr(handle, name), name
-    assert _lib.lib().b2_abi_version() == 1
+    assert _lib.lib().b2_abi_version() == 2
     assert _lib.lib().b2_last_error() == b""
 
 
@@ -36,6 +36,12 @@ def test_struct_layouts_match_header_sizes():
     # field order of the ctypes mirrors follows the header; offsets that matter to the kernels
     assert _lib.DenseArgs.y.offset == 8 and _lib.DenseArgs.y_pitch.offset == 56
     assert _lib.ResizeArgs.base.offset == 8 and _lib.ResizeArgs.dst.offset == 64
+    # version 1 of the structs ended at these offsets; the later fields start there
+    assert _lib.DenseArgs.arith.offset == 168 and ctypes.sizeof(_lib.DenseArgs) == 176
+    assert _lib.ResizeArgs.arith.offset == 104 and ctypes.sizeof(_lib.ResizeArgs) == 152
+    assert _lib.ResizeArgs.status.offset == 144
+    header = (ROOT / "include" / "b2frames.h").read_text()
+    assert "version 1 (168)" in header and "version 1 (104)" in header
 
 
 def test_status_and_message_without_a_gpu():
@@ -330,3 +336,66 @@ def test_source_window_of_make_image_descs():
     # RGB sources take any window
     d3, _ = io.make_image_descs([w], [h], src_format="rgb24", resize=(8, 8), src_crop=(1, 3, 5, 7))
     assert int(d3["y_off"][0]) == 3 * 3 * w + 3 and int(d3["src_w"][0]) == w - 6
+
+
+# ---- contiguity check of device arrays (no GPU needed: a fake __cuda_array_interface__) -----------
+
+
+class _FakeCuda:
+    def __init__(self, shape, strides, typestr="|u1"):
+        self.__cuda_array_interface__ = {"version": 2, "shape": shape, "typestr": typestr,
+                                         "data": (0x7F0000000000, False), "strides": strides}
+
+
+def test_contiguity_check_ignores_only_size_one_dimensions():
+    from spdl_b200.io._core import _cai
+
+    # packed, with and without explicit strides
+    assert _cai(_FakeCuda((2, 1620, 1920), None))[1] == (2, 1620, 1920)
+    assert _cai(_FakeCuda((2, 1620, 1920), (1620 * 1920, 1920, 1)))[1] == (2, 1620, 1920)
+    # a single pitched surface (row pitch 2048 > width): rejected although N == 1
+    with pytest.raises(RuntimeError, match="C-contiguous"):
+        _cai(_FakeCuda((1, 1620, 1920), (1620 * 2048, 2048, 1)))
+    with pytest.raises(RuntimeError, match="C-contiguous"):
+        _cai(_FakeCuda((2, 1620, 1920), (1620 * 2048, 2048, 1)))
+    # a transposed single image
+    with pytest.raises(RuntimeError, match="C-contiguous"):
+        _cai(_FakeCuda((1, 48, 64), (48 * 64, 1, 48)))
+    # the stride of a size-1 dimension is meaningless and may be anything
+    assert _cai(_FakeCuda((1, 1620, 1920), (12345, 1920, 1)))[1] == (1, 1620, 1920)
+    assert _cai(_FakeCuda((4, 1, 1920), (1920, 999, 1)))[1] == (4, 1, 1920)
+    # wider elements, empty arrays
+    assert _cai(_FakeCuda((3, 5), (20, 4), "<f4"))[2] == "<f4"
+    with pytest.raises(RuntimeError, match="C-contiguous"):
+        _cai(_FakeCuda((3, 5), (40, 8), "<f4"))
+    assert _cai(_FakeCuda((0, 10, 10), (1, 1, 1)))[1] == (0, 10, 10)
+
+
+def test_aspect_preserving_geometry_follows_the_reference_filter_strings():
+    """``scale_mode`` mirrors ``force_original_aspect_ratio=decrease`` + ``pad=...:x=-1:y=-1`` and
+    ``increase`` + ``crop`` (src/spdl/io/_preprocessing.py:214-229)."""
+    ws, hs = [1280, 640, 100], [720, 480, 300]
+    d, out = io.make_image_descs(ws, hs, resize=(256, 256), scale_mode="pad")
+    assert out == (256, 256)
+    # the fitted side is min(round(other * aspect), target)
+    assert [int(v) for v in d["resized_w"]] == [256, 256, 85]
+    assert [int(v) for v in d["resized_h"]] == [144, 192, 256]
+    # centred with (canvas - image) // 2, on the chroma grid for 4:2:0 sources
+    assert [int(v) for v in d["crop_y"]] == [-56, -32, 0]
+    assert [int(v) for v in d["crop_x"]] == [0, 0, -84]
+    assert np.float32(d["scale_x"][2]) == np.float32(100) / np.float32(85)
+    d24, _ = io.make_image_descs(ws, hs, src_format="rgb24", resize=(256, 256), scale_mode="pad")
+    assert [int(v) for v in d24["crop_x"]] == [0, 0, -85]  # (256 - 85) // 2, no chroma grid
+    d, out = io.make_image_descs(ws, hs, resize=(256, 256), scale_mode="crop")
+    assert out == (256, 256)
+    assert [int(v) for v in d["resized_w"]] == [0, 0, 0]  # nothing lies outside the image
+    assert [int(v) for v in d["crop_x"]] == [98, 42, 0]   # (455 - 256) // 2 = 99 -> even
+    assert [int(v) for v in d["crop_y"]] == [0, 0, 256]   # (768 - 256) // 2
+    assert np.float32(d["scale_x"][0]) == np.float32(1280) / np.float32(455)
+    # a centre crop after the letterbox refers to the canvas
+    d, out = io.make_image_descs(ws, hs, resize=(256, 256), scale_mode="pad", crop=(224, 224))
+    assert out == (224, 224) and [int(v) for v in d["crop_y"]] == [16 - 56, 16 - 32, 16]
+    with pytest.raises(ValueError):
+        io.make_image_descs(ws, hs, resize=(256, 256), scale_mode="fit")
+    with pytest.raises(RuntimeError):
+        io.make_image_descs(ws, hs, resize_shorter=256, scale_mode="pad")

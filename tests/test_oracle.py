@@ -255,3 +255,47 @@ def test_bilinear_matches_torch_random_geometry(seed):
     got = oracle.convert_resize(nv.reshape(-1), descs, out_w=ow, out_h=oh, dtype=oracle.F32)
     cx, cy = int(descs["crop_x"][0]), int(descs["crop_y"][0])
     np.testing.assert_allclose(got, want[:, :, cy:cy + oh, cx:cx + ow], rtol=0, atol=3e-4)
+
+
+def test_letterbox_pads_outside_the_resized_grid():
+    """Pixels outside the resized image take the pad colour through the same rounding and
+    scale/bias; pixels inside equal the plain resize of the image to its fitted size."""
+    import spdl_b200.io as io
+
+    w, h = 128, 72
+    nv = synth.nv12_batch(1, w, h, config=9, index=5)
+    descs, out = io.make_image_descs([w], [h], resize=(64, 64), scale_mode="pad")
+    assert out == (64, 64) and int(descs["resized_h"][0]) == 36 and int(descs["crop_y"][0]) == -14
+    pad = (12.0, 200.0, 77.0)
+    got = oracle.convert_resize(nv.reshape(-1), descs.view(oracle.DESC_DTYPE), out_w=64, out_h=64,
+                                pad_value=pad)
+    plain_d, plain_out = io.make_image_descs([w], [h], resize=(64, 36))
+    plain = oracle.convert_resize(nv.reshape(-1), plain_d.view(oracle.DESC_DTYPE), out_w=64,
+                                  out_h=36)
+    assert (got[0, :, 14:50] == plain[0]).all()
+    for c in range(3):
+        assert (got[0, c, :14] == int(pad[c])).all() and (got[0, c, 50:] == int(pad[c])).all()
+    sb = oracle.scale_bias((0.485, 0.456, 0.406), (0.229, 0.224, 0.225))
+    f = oracle.convert_resize(nv.reshape(-1), descs.view(oracle.DESC_DTYPE), out_w=64, out_h=64,
+                              pad_value=pad, dtype=oracle.F32, sb=sb, order=oracle.BGR)
+    # BGR: output slot 0 holds blue, normalised with slot 0's scale and bias
+    np.testing.assert_allclose(f[0, 0, 0, 0], np.float32(pad[2]) * sb[0] + sb[3], rtol=1e-6)
+
+
+def test_clip_layout_and_untouched_bad_descriptors():
+    import spdl_b200.io as io
+
+    t, w, h = 4, 64, 36
+    frames = np.concatenate([synth.nv12_clip(t, w, h, config=4, index=i) for i in range(2)])
+    descs, out = io.make_image_descs([w] * 2 * t, [h] * 2 * t, resize=(16, 12))
+    descs = descs.view(oracle.DESC_DTYPE)
+    flat = oracle.convert_resize(frames.reshape(-1), descs, out_w=16, out_h=12)
+    cthw = oracle.convert_resize(frames.reshape(-1), descs, out_w=16, out_h=12, clip_frames=t)
+    assert cthw.shape == (2, 3, t, 12, 16)
+    assert (cthw == flat.reshape(2, t, 3, 12, 16).transpose(0, 2, 1, 3, 4)).all()
+    bad = descs.copy()
+    bad["scale_x"][3] = 0.0
+    bad["src_h"][5] = 0
+    kept = oracle.convert_resize(frames.reshape(-1), bad, out_w=16, out_h=12,
+                                 out=np.full((2 * t, 3, 12, 16), 0xA5, np.uint8))
+    assert (kept[3] == 0xA5).all() and (kept[5] == 0xA5).all() and (kept[4] == flat[4]).all()
