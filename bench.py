@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                     [--scaling weak|strong] [--workload c2|c3|c4|c5|j5|aux] [--scale F]
-                    [--kernel-only] [--no-numa]
+                    [--repeats R] [--arith reference|swscale] [--kernel-only] [--no-numa]
 
 One "step" converts one batch of 64 synthetic 1920x1080 NV12 frames (BT.709 limited range) to
 interleaved RGB u8 with a single kernel launch.  Inputs are seeded synthetic frames with the
@@ -42,10 +42,21 @@ METRIC = "1080p NV12->RGB frames/s"
 WORKLOAD = "64 x 1920x1080 NV12 -> interleaved RGB u8 (NHWC), BT.709 limited range"
 ROTATE = 4  # distinct input batches cycled through, so no step finds its input in L2
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dense kernel on this workload,
-# from an ncu capture of this very workload (summary kept under profiles/)
-# (199,076,864 read + 345,854,976 written; part of the 398 MB output is still in L2 at kernel end).
-NCU_TRAFFIC_BYTES_PER_LAUNCH: int | None = 544_931_840
+#: what both arms print as ``config`` (the driver compares the two dicts)
+CONFIG = {"workload": WORKLOAD, "frames_per_step_per_gpu": N_FRAMES}
+DENSE_PROFILE = ROOT / "profiles" / "dense_nhwc_u8_1080p_x64.md"
+
+
+def ncu_traffic_bytes_per_launch() -> int:
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dense kernel on this
+    workload, read from the committed ncu summary of this very workload (its
+    ``traffic_bytes_per_launch:`` line), so that the figure cannot drift from the evidence."""
+    import re
+
+    m = re.search(r"^traffic_bytes_per_launch:\s*([0-9_,]+)", DENSE_PROFILE.read_text(), re.M)
+    if m is None:
+        raise SystemExit(f"{DENSE_PROFILE} has no traffic_bytes_per_launch line")
+    return int(m.group(1).replace(",", "").replace("_", ""))
 
 
 def measured_peak() -> tuple[float, str]:
@@ -194,12 +205,23 @@ def time_cpu(frames: int, steps: int, warmup: int, limit_s: float = 60.0) -> dic
     run, kind, desc = make_cpu_runner(frames)
     for _ in range(warmup):
         run()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        run()
-    dt = time.perf_counter() - t0
+    # the K steps are timed `repeats` times (at least 10, about `limit_s` / 4 seconds in all) and
+    # the median repeat is reported: one pass of K steps lasts a fraction of a second and moves
+    # by +-15 % with whatever else the host is doing
+    est = steps * frames / rate
+    repeats = int(max(10, min(200, (limit_s / 4) / max(est, 1e-6))))
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            run()
+        times.append(time.perf_counter() - t0)
+    times.sort()
+    dt = times[len(times) // 2]
     res = {"value": frames * steps / dt, "unit": "frames/s", "cores": cpu_cores(), "kind": kind,
-           "sample": desc, "ms_per_step": 1e3 * dt / steps, "frames_per_step": frames}
+           "sample": desc + f"; median of {repeats} repeats of the {steps} steps",
+           "ms_per_step": 1e3 * dt / steps, "frames_per_step": frames, "repeats": repeats,
+           "best": frames * steps / times[0], "worst": frames * steps / times[-1]}
     if kind == "reference":
         # The reference's filter graph runs on one thread
         # (src/libspdl/core/detail/ffmpeg/filter_graph.cpp:52); that figure, on 8 frames.
@@ -227,9 +249,10 @@ def run_reference_arm(args) -> None:
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "frames_per_step": r["frames_per_step"],
-                   "note": "CPU path takes yuv420p (what FFmpeg decoders emit) instead of NV12; "
-                           "a step is a bounded sample of the 64-frame batch"},
+        "config": dict(CONFIG),
+        "notes": {"input": "the CPU path takes yuv420p (what FFmpeg decoders emit) instead of NV12",
+                  "frames_per_step": r["frames_per_step"], "repeats": r["repeats"],
+                  "best": r["best"], "worst": r["worst"]},
         "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample",
                                            "single_thread_frames_per_s") if k in r},
         "e2e": {"value": r["value"], "unit": "frames/s", "h2d_bytes_per_step": 0,
@@ -294,6 +317,7 @@ def run_ours(args) -> None:
         a.matrix_coeff, a.full_range = 1, 0
         a.dst, a.dst_frame_stride = dst.data_ptr(), 0
         a.layout, a.dtype, a.order = _lib.NHWC, _lib.U8, _lib.RGB
+        a.arith = _lib.ARITH_SWSCALE if args.arith == "swscale" else _lib.ARITH_REFERENCE
         a.scale = (ctypes.c_float * 3)(1, 1, 1)
         a.bias = (ctypes.c_float * 3)(0, 0, 0)
         return a
@@ -313,26 +337,33 @@ def run_ours(args) -> None:
             torch.cuda.synchronize(dev)
 
     # -- kernel-resident timing: K steps, CUDA events on the launching stream ---------------------
+    # The K steps are timed R times back to back, each pass between its own pair of events, with
+    # one barrier + synchronize before the first pass and one after the last.  The median pass is
+    # reported (best and worst beside it), and the clock sampler's window spans all passes, so its
+    # samples lie inside timed regions.
+    R = max(1, args.repeats)
     clocks = ClockSampler(info.local_rank).start() if info.rank == 0 else None
     for i in range(Wm):
         step(i)
     if clocks is not None:
         clocks.wait_ready()
     barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+          for _ in range(R)]
     launches = 0
     if clocks is not None:
         clocks.begin()
-    e0.record(stream)
-    for i in range(K):
-        step(i)
-    e1.record(stream)
+    for e0, e1 in ev:
+        e0.record(stream)
+        for i in range(K):
+            step(i)
+        e1.record(stream)
     barrier()
-    ms_total = e0.elapsed_time(e1)
+    pass_ms = [e0.elapsed_time(e1) for e0, e1 in ev]
     timed_launches = launches
     if clocks is not None:
         clocks.end()
-        # a short timed region holds too few 20 ms samples: keep the same load running, untimed
+        # a short timed region holds too few sampling periods: keep the same load running, untimed
         give_up = time.perf_counter() + 1.0
         while len(clocks.in_window()) < 3 and time.perf_counter() < give_up:
             clocks.extended = True
@@ -341,6 +372,7 @@ def run_ours(args) -> None:
             torch.cuda.synchronize(dev)
             clocks.end()
         clocks.stop()
+    ms_total = sorted(pass_ms)[R // 2]  # this rank's median pass of K steps
 
     # -- end to end through the public API: pinned host NV12 -> H2D -> convert -> checksum -> D2H -
     if args.kernel_only:
@@ -369,7 +401,7 @@ def run_ours(args) -> None:
             tls.stream = torch.cuda.Stream(dev)
             tls.cfg = io.cuda_config(info.local_rank, stream=tls.stream.cuda_stream)
         d = io.transfer_buffer(host[i % 2], device_config=tls.cfg)
-        rgb = io.convert_nv12(d, device_config=tls.cfg, layout="NHWC")
+        rgb = io.convert_nv12(d, device_config=tls.cfg, layout="NHWC", arith=args.arith)
         return io.frame_checksum(rgb, device_config=tls.cfg)
 
     with ThreadPoolExecutor(2) as pool:
@@ -396,9 +428,11 @@ def run_ours(args) -> None:
         os.sched_setaffinity(0, numa["previous"])  # the CPU legs below use every core again
 
     # -- max over ranks ----------------------------------------------------------------------------
-    per_rank = gather_stats([ms_total, e2e_s], device=dev)
-    ms_max = max(r[0] for r in per_rank)
-    e2e_max = max(r[1] for r in per_rank)
+    per_rank = gather_stats([e2e_s] + pass_ms, device=dev)
+    e2e_max = max(r[0] for r in per_rank)
+    # every pass takes as long as its slowest rank; the median pass is the reported one
+    worst_rank = sorted(max(r[1 + j] for r in per_rank) for j in range(R))
+    ms_max, ms_best, ms_worst = worst_rank[R // 2], worst_rank[0], worst_rank[-1]
     total_frames = N_FRAMES * K * info.world_size
 
     if info.rank == 0:
@@ -410,11 +444,15 @@ def run_ours(args) -> None:
             "n_gpus": info.world_size, "steps": K, "warmup": Wm, "ms_per_step": ms_max / K,
             "higher_is_better": True, "scaling": SCALING, "vs_baseline": None, "dtype": "u8",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD, "frames_per_step_per_gpu": N_FRAMES,
-                       "l2": f"inputs ({N_FRAMES * FRAME_IN / 1e6:.0f} MB per batch) rotate over "
-                             f"{ROTATE} batches, {ROTATE * N_FRAMES * FRAME_IN / 1e6:.0f} MB in "
-                             f"all, more than L2",
-                       "sharding": "each rank converts its own frames; no data-path collective"},
+            "config": dict(CONFIG, frames_per_step_per_gpu=N_FRAMES) if args.arith == "reference"
+            else dict(CONFIG, frames_per_step_per_gpu=N_FRAMES, arith=args.arith),
+            "notes": {"l2": f"inputs ({N_FRAMES * FRAME_IN / 1e6:.0f} MB per batch) rotate over "
+                            f"{ROTATE} batches, {ROTATE * N_FRAMES * FRAME_IN / 1e6:.0f} MB in "
+                            f"all, more than L2",
+                      "sharding": "each rank converts its own frames; no data-path collective",
+                      "timing": f"median of {R} back-to-back passes of the {K} steps, each between "
+                                f"its own CUDA events; every pass counted at its slowest rank",
+                      "ms_per_step_best": ms_best / K, "ms_per_step_worst": ms_worst / K},
             "e2e": {"value": N_FRAMES * info.world_size / e2e_max, "unit": "frames/s",
                     "steps": min(K, 50),
                     "h2d_bytes_per_step": N_FRAMES * FRAME_IN, "d2h_bytes_per_step": N_FRAMES * 8,
@@ -423,11 +461,13 @@ def run_ours(args) -> None:
                     "host_binding": None if numa is None else
                     {k: numa[k] for k in ("node", "cpus", "bound")},
                     "note": "pinned NV12 -> transfer_buffer -> convert_nv12 -> frame_checksum -> "
-                            "host, per step, two worker threads on private streams, host-timed"},
+                            "host, per step, two worker threads on private streams, host-timed; "
+                            "the converted frames stay on the device by design (the model reads "
+                            "them there), only their 64 checksums are copied back"},
             "gpu_launches": timed_launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "frac_of_nominal_8000": achieved / 8000.0,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH * N_FRAMES // 64,
+                         "traffic": ncu_traffic_bytes_per_launch() * N_FRAMES // 64,
                          "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)"
                          if peak_kind == "measured" else "fallback 6650 GB/s",
                          "algorithmic_bytes_per_launch": N_FRAMES * ALGO_BYTES_PER_FRAME,
@@ -467,109 +507,196 @@ def _tap_bytes(w, h, rw, rh, cx, cy, ow, oh, fmt) -> tuple[int, int]:
     return exact, rows
 
 
+def _clips_on_device(torch, dev, clip_ids, t: int, w: int, h: int):
+    """Clips of the sharded clip workload, generated on the device: frame 0 uniform in the nominal
+    ranges, every later frame the previous one plus rounded Gaussian noise (sigma 4), clipped to
+    [16,235] (Y) / [16,240] (UV).  Seeded per clip, so a rank's shard equals the same clips of
+    the whole batch whichever GPU generates them."""
+    h2 = h * 3 // 2
+    out = torch.empty((len(clip_ids) * t, h2, w), dtype=torch.uint8, device=dev)
+    hi = torch.full((h2, 1), 240, dtype=torch.int16, device=dev)
+    hi[:h] = 235
+    for k, clip in enumerate(clip_ids):
+        g = torch.Generator(device=dev).manual_seed(4000 + int(clip))
+        cur = torch.empty((h2, w), dtype=torch.int16, device=dev)
+        cur[:h] = torch.randint(16, 236, (h, w), dtype=torch.int16, device=dev, generator=g)
+        cur[h:] = torch.randint(16, 241, (h // 2, w), dtype=torch.int16, device=dev, generator=g)
+        out[k * t] = cur.to(torch.uint8)
+        for f in range(1, t):
+            step = torch.randn((h2, w), device=dev, generator=g).mul_(4.0).round_().to(torch.int16)
+            cur = torch.minimum(torch.clamp_min(cur + step, 16), hi)
+            out[k * t + f] = cur.to(torch.uint8)
+    return out
+
+
 def run_resize_workload(args) -> None:
-    """``--workload c3|c4|c5|j5``: one GPU, kernel-resident timing of the fused resize kernel on
-    the other benchmark configurations (j5: the images of c5 as decoded RGB), with tap-exact and
-    row-granular roofline figures."""
+    """``--workload c3|c4|c5|j5``: kernel-resident timing of the fused resize kernel on the other
+    benchmark configurations (j5: the images of c5 as decoded RGB), with tap-exact and
+    row-granular roofline figures.  Under ``torch.distributed.run`` the units of the workload
+    (clips for c4, images otherwise) are split over the ranks in contiguous blocks -- the
+    configurations define c4 and c5 as sharded over 8 GPUs -- each rank holding and converting
+    its own shard; after the timed steps the per-image checksums of all ranks are gathered and
+    compared with the whole batch converted on rank 0's GPU."""
     import torch
+    import torch.distributed as dist
 
     import spdl_b200.io as io
     from spdl_b200 import _lib
+    from spdl_b200.sharding import ShardWorker, gather_stats, rank_info, shard_range
     from tests import synth
 
-    torch.cuda.init()
-    dev = torch.device("cuda", 0)
-    stream = torch.cuda.Stream(dev)
+    info = rank_info()
+    multi = info.world_size > 1
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)  # libraries print to stdout too (NCCL's banner); keep it for the JSON line
+    if multi:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", info.local_rank))
+    worker = ShardWorker(info)
+    dev, stream, cfg = worker.device, worker.stream, worker.config
     L = _lib.lib()
     scale = float(args.scale)
     mean, std = (0.485, 0.456, 0.406), (0.229, 0.224, 0.225)
-    if args.workload == "c3":
-        n, w, h = max(1, int(16 * scale)), 3840, 2160
-        ws, hs = [w] * n, [h] * n
-        descs, out = io.make_image_descs(ws, hs, resize=(224, 224))
-        spec = dict(fmt="nv12", layout=_lib.NCHW, dtype=_lib.BF16, esz=2, coeff=1, full=0, norm=True,
-                    name=f"{n} x 3840x2160 NV12 -> 224x224 bf16 NCHW, BT.709, normalised")
-        copies, nbytes = 8, n * w * h * 3 // 2
-    elif args.workload == "c4":
-        n, w, h = max(1, int(1024 * scale)), 1280, 720
-        ws, hs = [w] * n, [h] * n
-        descs, out = io.make_image_descs(ws, hs, resize=(256, 256))
-        spec = dict(fmt="nv12", layout=_lib.NCHW, dtype=_lib.U8, esz=1, coeff=6, full=0, norm=False,
-                    name=f"{n} frames ({n // 16} clips x 16) 1280x720 NV12 -> 256x256 u8 "
-                         f"N x T x C x H x W, BT.601")
-        copies, nbytes = 2, n * w * h * 3 // 2
-    elif args.workload == "j5":
-        # the sizes of c5, but already decoded to interleaved RGB (what a JPEG decoder emits)
-        n = max(1, int(2048 * scale))
-        r = synth.rng_for(5, 0)
-        ws = (r.integers(128, 513, n) * 2).astype(np.int64)
-        hs = (r.integers(128, 513, n) * 2).astype(np.int64)
-        sizes = 3 * ws * hs
-        offs = np.concatenate([[0], np.cumsum(sizes)[:-1]]).astype(np.int64)
-        descs, out = io.make_image_descs(ws, hs, src_format="rgb24", offsets=offs,
-                                         resize_shorter=256, crop=(224, 224))
-        spec = dict(fmt="rgb24", layout=_lib.NCHW, dtype=_lib.F32, esz=4, coeff=1, full=0, norm=True,
-                    name=f"{n} ragged interleaved RGB images (256..1024) -> shorter side 256, "
-                         f"centre crop 224x224 fp32 NCHW, normalised")
-        copies, nbytes = 2, int(sizes.sum())
+    wl = args.workload
+    per_unit = 1  # images per sharded unit
+    if wl == "c3":
+        units, w, h = max(info.world_size, int(16 * scale)), 3840, 2160
+        geom = dict(resize=(224, 224))
+        spec = dict(fmt="nv12", dtype="bfloat16", esz=2, coeff=1, full=False, norm=True,
+                    name="{n} x 3840x2160 NV12 -> 224x224 bf16 NCHW, BT.709, normalised")
+    elif wl == "c4":
+        per_unit = 16
+        units, w, h = max(info.world_size, int(64 * scale)), 1280, 720
+        geom = dict(resize=(256, 256))
+        spec = dict(fmt="nv12", dtype="uint8", esz=1, coeff=6, full=False, norm=False,
+                    name="{n} frames ({u} clips x 16) 1280x720 NV12 -> 256x256 u8 "
+                         "N x T x C x H x W, BT.601")
     else:
-        n = max(1, int(2048 * scale))
-        data, ws, hs, offs = synth.ragged_i420(n)
-        descs, out = io.make_image_descs(ws, hs, src_format="i420", offsets=offs,
-                                         resize_shorter=256, crop=(224, 224))
-        spec = dict(fmt="i420", layout=_lib.NCHW, dtype=_lib.F32, esz=4, coeff=6, full=1, norm=True,
-                    name=f"{n} ragged I420 images (256..1024) -> shorter side 256, centre crop "
-                         f"224x224 fp32 NCHW, full-range BT.601, normalised")
-        copies, nbytes = 2, int(data.nbytes)
-    with torch.cuda.stream(stream):
-        if args.workload == "c5":
-            first = torch.from_numpy(data).to(dev)
-            bases = [first] + [first.clone() for _ in range(copies - 1)]
+        units = max(info.world_size, int(2048 * scale))
+        geom = dict(resize_shorter=256, crop=(224, 224))
+        if wl == "j5":
+            spec = dict(fmt="rgb24", dtype="float32", esz=4, coeff=1, full=False, norm=True,
+                        name="{n} ragged interleaved RGB images (256..1024) -> shorter side 256, "
+                             "centre crop 224x224 fp32 NCHW, normalised")
         else:
-            g = torch.Generator(device=dev).manual_seed(3000)
-            bases = [torch.randint(16, 236, (nbytes,), dtype=torch.uint8, device=dev, generator=g)
-                     for _ in range(copies)]
+            spec = dict(fmt="i420", dtype="float32", esz=4, coeff=6, full=True, norm=True,
+                        name="{n} ragged I420 images (256..1024) -> shorter side 256, centre crop "
+                             "224x224 fp32 NCHW, full-range BT.601, normalised")
+    lo, hi = shard_range(units, info.rank, info.world_size)
+
+    # -- inputs: the rank's shard resident in its own HBM (rank 0 also builds the whole batch, after
+    #    the timed steps, for the shard-equals-whole check) -------------------------------------------
+    host_cache: dict = {}
+
+    def build(first: int, last: int):
+        """(device bytes, descriptor table, (out_w, out_h), widths, heights) of units [first, last)."""
+        if wl in ("c3", "c4"):
+            n_img = (last - first) * per_unit
+            if wl == "c4":
+                data = _clips_on_device(torch, dev, range(first, last), 16, w, h).reshape(-1)
+            else:
+                g = torch.Generator(device=dev)
+                parts = []
+                for i in range(first, last):
+                    g.manual_seed(3000 + i)
+                    f = torch.empty((h * 3 // 2, w), dtype=torch.uint8, device=dev)
+                    f[:h] = torch.randint(16, 236, (h, w), dtype=torch.uint8, device=dev, generator=g)
+                    f[h:] = torch.randint(16, 241, (h // 2, w), dtype=torch.uint8, device=dev,
+                                          generator=g)
+                    parts.append(f.reshape(-1))
+                data = torch.cat(parts)
+            ws_, hs_ = [w] * n_img, [h] * n_img
+            descs, out = io.make_image_descs(ws_, hs_, **geom)
+            return data, descs, out, np.asarray(ws_), np.asarray(hs_)
+        # ragged images: sizes and bytes from the seeded host generator, the shard's bytes uploaded
+        if wl == "c5":
+            if "c5" not in host_cache:
+                host_cache["c5"] = synth.ragged_i420(units)
+            host, ws_, hs_, offs = host_cache["c5"]
+            sizes = ws_ * hs_ * 3 // 2
+        else:
+            r = synth.rng_for(5, 0)
+            ws_ = (r.integers(128, 513, units) * 2).astype(np.int64)
+            hs_ = (r.integers(128, 513, units) * 2).astype(np.int64)
+            sizes = 3 * ws_ * hs_
+            offs = np.concatenate([[0], np.cumsum(sizes)[:-1]]).astype(np.int64)
+            host = None
+        b0 = int(offs[first])
+        b1 = int(offs[last - 1] + sizes[last - 1])
+        if host is not None:
+            data = torch.from_numpy(host[b0:b1]).to(dev)
+        else:
+            g = torch.Generator(device=dev).manual_seed(5000)
+            whole = torch.randint(0, 256, (int(sizes.sum()),), dtype=torch.uint8, device=dev,
+                                  generator=g)
+            data = whole[b0:b1].clone()
+            del whole
+        descs, out = io.make_image_descs(ws_[first:last], hs_[first:last], src_format=spec["fmt"],
+                                         offsets=offs[first:last] - b0, **geom)
+        return data, descs, out, ws_[first:last], hs_[first:last]
+
+    with torch.cuda.stream(stream):
+        data, descs, out, ws, hs = build(lo, hi)
+        n = len(descs)
+        # rotate copies of the shard so that a step does not find its source rows in L2
+        copies = max(2, min(8, int(2 * 126e6 // max(int(data.numel()), 1)) + 1))
+        bases = [data] + [data.clone() for _ in range(copies - 1)]
         dd = torch.from_numpy(descs.view(np.uint8)).to(dev)
         dst = torch.empty(n * 3 * out[0] * out[1] * spec["esz"], dtype=torch.uint8, device=dev)
     sc, bi = io._core._scale_bias(mean if spec["norm"] else None, std if spec["norm"] else None)
-    calls = []
-    for b in bases:
+
+    def make_call(base, table, count, target, max_w):
         a = _lib.ResizeArgs()
         a.struct_size = ctypes.sizeof(_lib.ResizeArgs)
-        a.device, a.base, a.descs = 0, b.data_ptr(), dd.data_ptr()
-        a.num_images, a.src_format = n, io._core._FORMATS[spec["fmt"]]
+        a.device, a.base, a.descs = info.local_rank, base.data_ptr(), table.data_ptr()
+        a.num_images, a.src_format = count, io._core._FORMATS[spec["fmt"]]
         a.out_w, a.out_h = out
-        a.matrix_coeff, a.full_range = spec["coeff"], spec["full"]
-        a.layout, a.dtype, a.order = spec["layout"], spec["dtype"], _lib.RGB
-        a.max_src_w, a.dst = int(max(ws)), dst.data_ptr()
+        a.matrix_coeff, a.full_range = spec["coeff"], int(spec["full"])
+        a.layout, a.dtype, a.order = _lib.NCHW, io._core._DTYPES[spec["dtype"]], _lib.RGB
+        a.max_src_w, a.dst = int(max_w), target.data_ptr()
         a.scale = (ctypes.c_float * 3)(*sc.tolist())
         a.bias = (ctypes.c_float * 3)(*bi.tolist())
-        calls.append(a)
+        return a
+
+    calls = [make_call(b, dd, n, dst, max(ws)) for b in bases]
     K, Wm = args.steps, max(args.warmup, 3)
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if multi:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
     stream.synchronize()
     for i in range(Wm):
         _lib.check(L.b2_convert_resize(ctypes.byref(calls[i % copies]), stream.cuda_stream))
-    torch.cuda.synchronize(dev)
+    clocks = ClockSampler(info.local_rank).start() if info.rank == 0 else None
+    if clocks is not None:
+        clocks.wait_ready()
+    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    clocks = ClockSampler(0).start()
-    clocks.wait_ready()
-    clocks.begin()
+    if clocks is not None:
+        clocks.begin()
     e0.record(stream)
     for i in range(K):
         _lib.check(L.b2_convert_resize(ctypes.byref(calls[i % copies]), stream.cuda_stream))
     e1.record(stream)
-    torch.cuda.synchronize(dev)
-    clocks.end()
+    barrier()
     ms = e0.elapsed_time(e1) / K
-    give_up = time.perf_counter() + 1.0
-    # keep the same load running, untimed, until three samples are in
-    while len(clocks.in_window()) < 3 and time.perf_counter() < give_up:
-        clocks.extended = True
-        for i in range(K):
-            _lib.check(L.b2_convert_resize(ctypes.byref(calls[i % copies]), stream.cuda_stream))
-        torch.cuda.synchronize(dev)
+    if clocks is not None:
         clocks.end()
-    clocks.stop()
+        give_up = time.perf_counter() + 1.0
+        # keep the same load running, untimed, until three samples are in
+        while len(clocks.in_window()) < 3 and time.perf_counter() < give_up:
+            clocks.extended = True
+            for i in range(K):
+                _lib.check(L.b2_convert_resize(ctypes.byref(calls[i % copies]), stream.cuda_stream))
+            torch.cuda.synchronize(dev)
+            clocks.end()
+        clocks.stop()
+
+    # -- the shard's bytes (tap-exact and row-granular), summed over ranks ----------------------------
     rw = np.rint(np.asarray(ws) / descs["scale_x"].astype(np.float64)).astype(np.int64)
     rh = np.rint(np.asarray(hs) / descs["scale_y"].astype(np.float64)).astype(np.int64)
     cache: dict = {}
@@ -582,24 +709,81 @@ def run_resize_workload(args) -> None:
         exact += cache[key][0]
         rows += cache[key][1]
     out_bytes = n * 3 * out[0] * out[1] * spec["esz"]
-    peak, peak_kind = measured_peak()
-    line = {
-        "metric": "fused convert+resize images/s", "value": n / (ms * 1e-3), "unit": "images/s",
-        "n_gpus": 1, "steps": K, "warmup": Wm, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": {1: "u8", 2: "bf16", 4: "f32"}[spec["esz"]],
-        "data": "synthetic", "config": {"workload": spec["name"], "images_per_step": n,
-                                        "l2": f"{copies} input copies rotated"},
-        "gpu_launches": K,
-        "roofline": {"bound": "hbm", "unit": "GB/s", "peak": peak, "peak_source": peak_kind,
-                     "achieved": (exact + out_bytes) / (ms * 1e-3) / 1e9,
-                     "frac": (exact + out_bytes) / (ms * 1e-3) / 1e9 / peak,
-                     "algorithmic_bytes_per_launch": exact + out_bytes,
-                     "row_granular_bytes_per_launch": rows + out_bytes,
-                     "row_granular_gb_per_s": (rows + out_bytes) / (ms * 1e-3) / 1e9,
-                     "traffic": None, "kernel": "resize_kernel", "ms_per_launch": ms},
-        "clocks": clocks.summary(),
-    }
-    print(json.dumps(line), flush=True)
+
+    # -- correctness in the same run: checksums of every rank's output against the whole batch ------
+    frame_bytes = 3 * out[0] * out[1] * spec["esz"]
+    sums = torch.empty(n, dtype=torch.int64, device=dev)
+    _lib.check(L.b2_convert_resize(ctypes.byref(calls[0]), stream.cuda_stream))
+    _lib.check(L.b2_frame_checksum(dst.data_ptr(), frame_bytes, n, sums.data_ptr(),
+                                   info.local_rank, stream.cuda_stream))
+    stream.synchronize()
+    equal = None
+    if multi:
+        counts = [(shard_range(units, r, info.world_size)[1] -
+                   shard_range(units, r, info.world_size)[0]) * per_unit
+                  for r in range(info.world_size)]
+        padded = torch.zeros(max(counts), dtype=torch.int64, device=dev)
+        padded[:n] = sums
+        gathered = [torch.zeros_like(padded) for _ in range(info.world_size)]
+        dist.all_gather(gathered, padded)
+        if info.rank == 0:
+            all_sums = torch.cat([g[:c] for g, c in zip(gathered, counts)]).cpu().numpy()
+    else:
+        all_sums = sums.cpu().numpy()
+    if info.rank == 0:
+        del bases[1:], calls[1:]
+        with torch.cuda.stream(stream):
+            wdata, wdescs, _, wws, _ = build(0, units)
+            wdd = torch.from_numpy(wdescs.view(np.uint8)).to(dev)
+            wn = len(wdescs)
+            wdst = torch.empty(wn * frame_bytes, dtype=torch.uint8, device=dev)
+            wsums = torch.empty(wn, dtype=torch.int64, device=dev)
+        whole_call = make_call(wdata, wdd, wn, wdst, max(wws))
+        _lib.check(L.b2_convert_resize(ctypes.byref(whole_call), stream.cuda_stream))
+        _lib.check(L.b2_frame_checksum(wdst.data_ptr(), frame_bytes, wn, wsums.data_ptr(),
+                                       info.local_rank, stream.cuda_stream))
+        stream.synchronize()
+        equal = bool((wsums.cpu().numpy() == all_sums).all())
+        if not equal:
+            raise SystemExit("the ranks' outputs differ from the whole batch converted on one GPU")
+
+    per_rank = gather_stats([ms, float(exact), float(rows), float(out_bytes), float(n)], device=dev)
+    if info.rank == 0:
+        ms_max = max(r[0] for r in per_rank)
+        t_exact, t_rows, t_out = (sum(r[i] for r in per_rank) for i in (1, 2, 3))
+        total_n = int(sum(r[4] for r in per_rank))
+        peak, peak_kind = measured_peak()
+        g = info.world_size
+        per_gpu = lambda b: b / g / (ms_max * 1e-3) / 1e9  # noqa: E731
+        line = {
+            "metric": "fused convert+resize images/s", "value": total_n / (ms_max * 1e-3),
+            "unit": "images/s", "n_gpus": g, "steps": K, "warmup": Wm, "ms_per_step": ms_max,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": {1: "u8", 2: "bf16", 4: "f32"}[spec["esz"]], "data": "synthetic",
+            "config": {"workload": spec["name"].format(n=total_n, u=units),
+                       "images_per_step": total_n, "images_per_gpu": total_n // g,
+                       "l2": f"{copies} copies of each rank's shard rotated",
+                       "sharding": "contiguous blocks of clips/images per rank, each resident in "
+                                   "its own GPU's memory; no data-path collective"},
+            "ms_per_rank": [r[0] for r in per_rank],
+            "shards_equal_whole": equal,
+            "gpu_launches": K,
+            "roofline": {"bound": "hbm", "unit": "GB/s", "peak": peak, "peak_source": peak_kind,
+                         "achieved": per_gpu(t_exact + t_out),
+                         "frac": per_gpu(t_exact + t_out) / peak,
+                         "algorithmic_bytes_per_launch": (t_exact + t_out) / g,
+                         "row_granular_bytes_per_launch": (t_rows + t_out) / g,
+                         "row_granular_gb_per_s": per_gpu(t_rows + t_out),
+                         "row_granular_frac": per_gpu(t_rows + t_out) / peak,
+                         "traffic": None, "kernel": "resize_kernel", "ms_per_launch": ms_max,
+                         "note": "per GPU: the ranks' bytes divided by the number of GPUs and by "
+                                 "the slowest rank's time"},
+            "clocks": clocks.summary() if clocks is not None else None,
+        }
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
+    if multi:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def run_aux_workload(args) -> None:
@@ -784,6 +968,11 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--repeats", type=int, default=25,
+                    help="c2: how many times the K timed steps are run (median reported)")
+    ap.add_argument("--arith", choices=["reference", "swscale"], default="reference",
+                    help="c2: which colour arithmetic the kernel computes (the reference's CUDA "
+                         "kernel, or libswscale's integers as on the reference's CPU route)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU legs (for profiler captures)")
     ap.add_argument("--workload", choices=["c2", "c3", "c4", "c5", "j5", "aux"], default="c2",

@@ -114,24 +114,6 @@ __device__ __forceinline__ float2 x2_fma_rm(float2 a, float2 b, float2 c) {
   return unpack2(d);
 }
 
-struct Chroma2 {
-  float2 vr, ug, vg, ub;  // lane x: first quad, lane y: second quad
-};
-// bu, bv: {2^23 + U, 2^23 + V} of the two quads
-template <int ARITH = B2_ARITH_REFERENCE>
-__device__ __forceinline__ Chroma2 chroma2_of(const ColorMat& m, float2 bu, float2 bv);
-template <>
-__device__ __forceinline__ Chroma2 chroma2_of<B2_ARITH_REFERENCE>(const ColorMat& m, float2 bu,
-                                                                  float2 bv) {
-  const float2 nz = dup2(m.neg_zero), off = dup2(-(kTwo23 + 128.0f));
-  const float2 fu = x2_add(bu, off), fv = x2_add(bv, off);
-  Chroma2 c;
-  c.vr = x2_fma(dup2(m.vr), fv, nz);
-  c.ug = x2_fma(dup2(m.ug), fu, nz);
-  c.vg = x2_fma(dup2(m.vg), fv, nz);
-  c.ub = x2_fma(dup2(m.ub), fu, nz);
-  return c;
-}
 // ---- libswscale's arithmetic -----------------------------------------------------------------
 // The x86 SIMD converter libswscale uses for unscaled yuv420p -> rgb24 works on 16-bit lanes:
 //     y' = (Y << 3) - yOffset          u' = (U << 3) - 1024          v' = (V << 3) - 1024
@@ -143,45 +125,100 @@ __device__ __forceinline__ Chroma2 chroma2_of<B2_ARITH_REFERENCE>(const ColorMat
 // toward minus infinity leaves 1.5 * 2^23 + floor(product): no integer instruction is needed.
 // ColorMat carries coeff / 2^13 for this arithmetic (exact: a 16-bit integer times 2^-13).
 // Chroma2.ug holds ug'' + vg''; Chroma2.vg is unused.
-template <>
-__device__ __forceinline__ Chroma2 chroma2_of<B2_ARITH_SWSCALE>(const ColorMat& m, float2 bu,
-                                                                float2 bv) {
-  const float2 off = dup2(-(kTwo23 + 128.0f)), magic = dup2(kQuantMagic);
-  const float2 fu = x2_add(bu, off), fv = x2_add(bv, off);
+//
+// The arithmetic below reads the matrix through a small interface -- g2(), vr2(), ... return a
+// coefficient in both lanes -- so that a kernel can either duplicate the scalars where they are
+// used (MatDup: fine when a thread converts many pixels in straight-line code) or hold the pairs
+// in registers across a loop (MatPairs; pin2 keeps the compiler from rebuilding a pair from the
+// kernel parameters at every use, which costs two moves each time).
+struct MatDup {
+  const ColorMat& m;
+  __device__ __forceinline__ float2 g2() const { return dup2(m.g); }
+  __device__ __forceinline__ float2 vr2() const { return dup2(m.vr); }
+  __device__ __forceinline__ float2 ug2() const { return dup2(m.ug); }
+  __device__ __forceinline__ float2 vg2() const { return dup2(m.vg); }
+  __device__ __forceinline__ float2 ub2() const { return dup2(m.ub); }
+  __device__ __forceinline__ float2 neg_ybias2() const { return dup2(-m.y_bias); }
+  __device__ __forceinline__ float2 nz2() const { return dup2(m.neg_zero); }
+  __device__ __forceinline__ float2 coff2() const { return dup2(-(kTwo23 + 128.0f)); }
+  __device__ __forceinline__ float2 magic2() const { return dup2(kQuantMagic); }
+  __device__ __forceinline__ float2 neg_magic2() const { return dup2(-kQuantMagic); }
+};
+__device__ __forceinline__ float2 pin2(float2 v) {
+  unsigned long long r = pack2(v);
+  asm volatile("" : "+l"(r));
+  return unpack2(r);
+}
+template <int ARITH>
+struct MatPairs {  // only the pairs the arithmetic reads are built (and held)
+  float2 g, vr, ug, vg, ub, neg_ybias, coff, magic, extra;  // extra: -0.0 or -1.5 * 2^23
+  __device__ __forceinline__ explicit MatPairs(const ColorMat& m)
+      : g(pin2(dup2(m.g))), vr(pin2(dup2(m.vr))), ug(pin2(dup2(m.ug))), vg(pin2(dup2(m.vg))),
+        ub(pin2(dup2(m.ub))), neg_ybias(pin2(dup2(-m.y_bias))),
+        coff(pin2(dup2(-(kTwo23 + 128.0f)))), magic(pin2(dup2(kQuantMagic))),
+        extra(pin2(dup2(ARITH == B2_ARITH_REFERENCE ? m.neg_zero : -kQuantMagic))) {}
+  __device__ __forceinline__ float2 g2() const { return g; }
+  __device__ __forceinline__ float2 vr2() const { return vr; }
+  __device__ __forceinline__ float2 ug2() const { return ug; }
+  __device__ __forceinline__ float2 vg2() const { return vg; }
+  __device__ __forceinline__ float2 ub2() const { return ub; }
+  __device__ __forceinline__ float2 neg_ybias2() const { return neg_ybias; }
+  __device__ __forceinline__ float2 nz2() const { return extra; }
+  __device__ __forceinline__ float2 coff2() const { return coff; }
+  __device__ __forceinline__ float2 magic2() const { return magic; }
+  __device__ __forceinline__ float2 neg_magic2() const { return extra; }
+};
+
+struct Chroma2 {
+  float2 vr, ug, vg, ub;  // lane x: first quad, lane y: second quad
+};
+// bu, bv: {2^23 + U, 2^23 + V} of the two quads
+template <int ARITH, class M>
+__device__ __forceinline__ Chroma2 chroma2_of(const M& m, float2 bu, float2 bv) {
+  const float2 fu = x2_add(bu, m.coff2()), fv = x2_add(bv, m.coff2());
   Chroma2 c;
-  c.vr = x2_add(x2_fma_rm(dup2(m.vr), fv, magic), dup2(-kQuantMagic));
-  c.ub = x2_add(x2_fma_rm(dup2(m.ub), fu, magic), dup2(-kQuantMagic));
-  c.ug = x2_add(x2_fma_rm(dup2(m.ug), fu, magic),
-                x2_add(x2_fma_rm(dup2(m.vg), fv, magic), dup2(-2.0f * kQuantMagic)));
-  c.vg = dup2(0.0f);
+  if constexpr (ARITH == B2_ARITH_REFERENCE) {
+    c.vr = x2_fma(m.vr2(), fv, m.nz2());
+    c.ug = x2_fma(m.ug2(), fu, m.nz2());
+    c.vg = x2_fma(m.vg2(), fv, m.nz2());
+    c.ub = x2_fma(m.ub2(), fu, m.nz2());
+  } else {
+    // libswscale (see below): floors of the four products; ug carries ug'' + vg''
+    c.vr = x2_add(x2_fma_rm(m.vr2(), fv, m.magic2()), m.neg_magic2());
+    c.ub = x2_add(x2_fma_rm(m.ub2(), fu, m.magic2()), m.neg_magic2());
+    c.ug = x2_add(x2_add(x2_fma_rm(m.ug2(), fu, m.magic2()), m.neg_magic2()),
+                  x2_add(x2_fma_rm(m.vg2(), fv, m.magic2()), m.neg_magic2()));
+    c.vg = dup2(0.0f);
+  }
   return c;
+}
+template <int ARITH = B2_ARITH_REFERENCE>
+__device__ __forceinline__ Chroma2 chroma2_of(const ColorMat& m, float2 bu, float2 bv) {
+  return chroma2_of<ARITH>(MatDup{m}, bu, bv);
 }
 
 // Two pixels (one per quad): by = {2^23 + Y, 2^23 + Y'}.  Results are the channel values plus
 // 1.5*2^23 rounded toward zero, i.e. floor(x) sits in the low 16 mantissa bits as a signed halfword (see clamp2_bits).
+template <int ARITH, class M>
+__device__ __forceinline__ void pixel2_bits(const M& m, float2 by, const Chroma2& c, float2& r,
+                                            float2& g, float2& b) {
+  const float2 fy = x2_add(by, m.neg_ybias2());
+  if constexpr (ARITH == B2_ARITH_REFERENCE) {
+    const float2 ly = x2_fma(m.g2(), fy, m.nz2());
+    r = x2_add_rz(x2_add(ly, c.vr), m.magic2());
+    g = x2_add_rz(x2_add(x2_fma(m.g2(), fy, c.ug), c.vg), m.magic2());
+    b = x2_add_rz(x2_fma(m.g2(), fy, c.ub), m.magic2());
+  } else {
+    const float2 lm = x2_fma_rm(m.g2(), fy, m.magic2());  // 1.5*2^23 + y''
+    r = x2_add(lm, c.vr);  // sums of small integers and the magic constant: exact
+    g = x2_add(lm, c.ug);
+    b = x2_add(lm, c.ub);
+  }
+}
 template <int ARITH = B2_ARITH_REFERENCE>
 __device__ __forceinline__ void pixel2_bits(const ColorMat& m, float2 by, const Chroma2& c,
-                                            float2& r, float2& g, float2& b);
-template <>
-__device__ __forceinline__ void pixel2_bits<B2_ARITH_SWSCALE>(const ColorMat& m, float2 by,
-                                                              const Chroma2& c, float2& r,
-                                                              float2& g, float2& b) {
-  const float2 fy = x2_add(by, dup2(-m.y_bias));
-  const float2 lm = x2_fma_rm(dup2(m.g), fy, dup2(kQuantMagic));  // 1.5*2^23 + y''
-  r = x2_add(lm, c.vr);  // sums of small integers and the magic constant: exact
-  g = x2_add(lm, c.ug);
-  b = x2_add(lm, c.ub);
-}
-template <>
-__device__ __forceinline__ void pixel2_bits<B2_ARITH_REFERENCE>(const ColorMat& m, float2 by,
-                                                                const Chroma2& c, float2& r,
-                                                                float2& g, float2& b) {
-  const float2 g2 = dup2(m.g), magic = dup2(kQuantMagic);
-  const float2 fy = x2_add(by, dup2(-m.y_bias));
-  const float2 ly = x2_fma(g2, fy, dup2(m.neg_zero));
-  r = x2_add_rz(x2_add(ly, c.vr), magic);
-  g = x2_add_rz(x2_add(x2_fma(g2, fy, c.ug), c.vg), magic);
-  b = x2_add_rz(x2_fma(g2, fy, c.ub), magic);
+                                            float2& r, float2& g, float2& b) {
+  pixel2_bits<ARITH>(MatDup{m}, by, c, r, g, b);
 }
 // The same two pixels for 8-bit output.  The last step of each channel is a multiply by 2^-149
 // with round-toward-zero: the result is the subnormal whose mantissa is trunc(|x|), so its BIT

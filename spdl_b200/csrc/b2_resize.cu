@@ -50,7 +50,9 @@ struct ResizeParams {
   float ch_scale[3], ch_bias[3];         // per colour channel; scale carries the 2^24 of kTapScale
   float ch_pad[3];                       // pad colour per channel, scaled by 2^-24 like the taps
   int span_cap;                          // bytes reserved per staged row span (multiple of 16)
-  int rows;                              // output rows per CTA: 4, or 2 for wide sources
+  int vec_store;                         // 1: whole groups of four pixels may use vector stores
+  int rows;                              // output rows per tile: 4, or 2 for wide sources
+  int tiles;                             // tiles a CTA converts, one after the other
   int* status;                           // optional device word for B2_STATUS_* bits
   unsigned wait_limit;                   // polls of about a microsecond each
   int debug_flags;
@@ -111,32 +113,207 @@ __device__ __forceinline__ float2 x2_mul(float2 a, float2 b) {
   return unpack2(d);
 }
 
-// Waits for phase 0 of an mbarrier, at most `limit` polls of about a microsecond each.
-__device__ __forceinline__ bool bounded_wait(uint32_t bar_addr, unsigned limit) {
+// Waits for the phase of an mbarrier with the given parity, at most `limit` polls of about a
+// microsecond each.
+__device__ __forceinline__ bool bounded_wait(uint32_t bar_addr, uint32_t parity, unsigned limit) {
   uint32_t done = 0;
   for (unsigned spin = 0; spin < limit && !done; ++spin)
     asm volatile(
-        "{ .reg .pred P; mbarrier.try_wait.parity.shared::cta.b64 P, [%1], 0, %2; "
+        "{ .reg .pred P; mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3; "
         "selp.u32 %0, 1, 0, P; }"
         : "=r"(done)
-        : "r"(bar_addr), "r"(1000u)
+        : "r"(bar_addr), "r"(parity), "r"(1000u)
         : "memory");
   return done != 0;
 }
 
-template <int FMT, int DTYPE, int ARITH>
+// ---- shared-memory loads by 32-bit shared address (no generic-pointer arithmetic) ---------------
+__device__ __forceinline__ uint32_t lds_u8(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint4 lds_v4(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(a));
+  return v;
+}
+
+// What warp 0 works out for each output row of a tile while it stages the rows: shared addresses
+// of the staged source rows (first plane's rows y0/y1, then the second and third planes'), the
+// vertical weights, and whether the row lies inside the image at all.
+struct __align__(16) RowInfo {
+  uint32_t row[6];
+  float wy0, wy1;
+};
+
+// One tap column of one output pixel: two source rows in the two lanes -> clamped 8-bit R, G, B
+// (scaled by 2^-24, see kTapScale).
+template <int FMT, int ARITH, bool UV16, class M>
+__device__ __forceinline__ void convert_taps(const M& m, const RowInfo& in, uint32_t sx,
+                                             uint32_t ci, float2 (&t)[3]) {
+  constexpr bool kYuv = FMT == B2_SRC_NV12 || FMT == B2_SRC_I420;
+  if constexpr (!kYuv) {
+    // already RGB: the taps are the bytes themselves (two rows into 16-bit lanes)
+    if constexpr (FMT == B2_SRC_RGB_PLANAR) {
+      t[0] = halves_to_float2(__byte_perm(lds_u8(in.row[0] + sx), lds_u8(in.row[1] + sx), 0x5410u));
+      t[1] = halves_to_float2(__byte_perm(lds_u8(in.row[2] + ci), lds_u8(in.row[3] + ci), 0x5410u));
+      t[2] = halves_to_float2(__byte_perm(lds_u8(in.row[4] + ci), lds_u8(in.row[5] + ci), 0x5410u));
+    } else {
+#pragma unroll
+      for (int ch = 0; ch < 3; ++ch)
+        t[ch] = halves_to_float2(
+            __byte_perm(lds_u8(in.row[0] + sx + ch), lds_u8(in.row[1] + sx + ch), 0x5410u));
+    }
+  } else {
+    float2 bu, bv;
+    if constexpr (FMT == B2_SRC_NV12) {
+      uint32_t p0, p1;  // {U, V} of row 0 / row 1
+      if constexpr (UV16) {
+        p0 = lds_u16(in.row[2] + ci);
+        p1 = lds_u16(in.row[3] + ci);
+      } else {
+        p0 = lds_u8(in.row[2] + ci) | (lds_u8(in.row[2] + ci + 1) << 8);
+        p1 = lds_u8(in.row[3] + ci) | (lds_u8(in.row[3] + ci + 1) << 8);
+      }
+      bu = make_float2(biased_byte(p0, 0), biased_byte(p1, 0));
+      bv = make_float2(biased_byte(p0, 1), biased_byte(p1, 1));
+    } else {
+      bu = make_float2(biased(lds_u8(in.row[2] + ci)), biased(lds_u8(in.row[3] + ci)));
+      bv = make_float2(biased(lds_u8(in.row[4] + ci)), biased(lds_u8(in.row[5] + ci)));
+    }
+    const Chroma2 ch = chroma2_of<ARITH>(m, bu, bv);
+    float2 cr, cg, cb;
+    pixel2_bits<ARITH>(m, make_float2(biased(lds_u8(in.row[0] + sx)), biased(lds_u8(in.row[1] + sx))),
+                       ch, cr, cg, cb);
+    t[0] = clamp_to_float2(cr);
+    t[1] = clamp_to_float2(cg);
+    t[2] = clamp_to_float2(cb);
+  }
+}
+
+// Rounding / scale+bias of one blended value (scaled by 2^-24), channel c.
+// u8: floor(val + 0.5) as a subnormal bit pattern (val >= 0), ready for pack4_sat.
+template <int DTYPE>
+__device__ __forceinline__ float finish(const ResizeParams& p, float v, int c) {
+  if constexpr (DTYPE == B2_U8) return __fmul_rz(__fmaf_rn(v, kTapScale, 0.5f), __uint_as_float(1u));
+  else return __fmaf_rn(v, p.ch_scale[c], p.ch_bias[c]);
+}
+template <int DTYPE, typename T>
+__device__ __forceinline__ void store_elem(T* q, float f) {
+  if constexpr (DTYPE == B2_U8) *q = (uint8_t)pack4_sat(f, 0.0f, 0.0f, 0.0f);
+  else if constexpr (DTYPE == B2_F32) *q = f;
+  else *q = __float2bfloat16_rn(f);
+}
+__device__ __forceinline__ uint32_t bf16x2_bits(float a, float b) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+
+// The four-pixel groups g, g + gstep, ... below `gend` of one output row.  drow: the row in the
+// destination; val[k][c]: pixel k, colour channel c.
+template <int FMT, int LAYOUT, int DTYPE, int ARITH, bool UV16, typename T>
+__device__ __forceinline__ void convert_row(const ResizeParams& p, const MatPairs<ARITH>& m,
+                                            const RowInfo& in, uint32_t xoffs, uint32_t xw,
+                                            T* drow, int g, int gend, int gstep, int groups,
+                                            int cin0, int cin1) {
+  for (; g < gend; g += gstep) {
+    const int ox0 = 4 * g;
+    const uint4 w4 = lds_v4(xw + 16u * (uint32_t)g);
+    const float w1s[4] = {__uint_as_float(w4.x), __uint_as_float(w4.y), __uint_as_float(w4.z),
+                          __uint_as_float(w4.w)};
+    float val[4][3];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      // entries are stored so that neighbouring lanes read neighbouring entries
+      const uint4 e = lds_v4(xoffs + 16u * (uint32_t)(k * groups + g));
+      const float2 wx1 = dup2(w1s[k]), wx0 = dup2(__fsub_rn(1.0f, w1s[k]));
+      float2 t0[3], t1[3];  // [channel] of tap column x0 / x1, lanes = {row y0, row y1}
+      convert_taps<FMT, ARITH, UV16>(m, in, e.x, e.z, t0);
+      convert_taps<FMT, ARITH, UV16>(m, in, e.y, e.w, t1);
+#pragma unroll
+      for (int c = 0; c < 3; ++c) {
+        // {top, bot} = fma(wx1, t?1, wx0 * t?0) for both rows at once
+        const float2 tb = x2_fma(wx1, t1[c], x2_mul(wx0, t0[c]));
+        val[k][c] = finish<DTYPE>(p, __fmaf_rn(in.wy1, tb.y, __fmul_rn(in.wy0, tb.x)), c);
+      }
+    }
+    if (p.vec_store && ox0 >= cin0 && ox0 + 4 <= cin1) {
+      // four whole pixels inside the image, 16-byte aligned destination: vector stores
+      if constexpr (LAYOUT == B2_NCHW) {
+#pragma unroll
+        for (int c = 0; c < 3; ++c) {
+          T* q = drow + p.chan_off[c] + ox0;
+          if constexpr (DTYPE == B2_U8)
+            *reinterpret_cast<uint32_t*>(q) = pack4_sat(val[0][c], val[1][c], val[2][c], val[3][c]);
+          else if constexpr (DTYPE == B2_F32)
+            *reinterpret_cast<float4*>(q) = make_float4(val[0][c], val[1][c], val[2][c], val[3][c]);
+          else
+            *reinterpret_cast<uint2*>(q) = make_uint2(bf16x2_bits(val[0][c], val[1][c]),
+                                                      bf16x2_bits(val[2][c], val[3][c]));
+        }
+      } else {
+        if (p.chan_off[0] != 0) {  // BGR: blue goes first
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float tmp = val[k][0];
+            val[k][0] = val[k][2];
+            val[k][2] = tmp;
+          }
+        }
+        T* q = drow + 3 * ox0;
+        if constexpr (DTYPE == B2_U8) {
+          uint32_t* o = reinterpret_cast<uint32_t*>(q);
+          o[0] = pack4_sat(val[0][0], val[0][1], val[0][2], val[1][0]);
+          o[1] = pack4_sat(val[1][1], val[1][2], val[2][0], val[2][1]);
+          o[2] = pack4_sat(val[2][2], val[3][0], val[3][1], val[3][2]);
+        } else if constexpr (DTYPE == B2_F32) {
+          float4* o = reinterpret_cast<float4*>(q);
+          o[0] = make_float4(val[0][0], val[0][1], val[0][2], val[1][0]);
+          o[1] = make_float4(val[1][1], val[1][2], val[2][0], val[2][1]);
+          o[2] = make_float4(val[2][2], val[3][0], val[3][1], val[3][2]);
+        } else {
+          uint2* o = reinterpret_cast<uint2*>(q);
+          o[0] = make_uint2(bf16x2_bits(val[0][0], val[0][1]), bf16x2_bits(val[0][2], val[1][0]));
+          o[1] = make_uint2(bf16x2_bits(val[1][1], val[1][2]), bf16x2_bits(val[2][0], val[2][1]));
+          o[2] = make_uint2(bf16x2_bits(val[2][2], val[3][0]), bf16x2_bits(val[3][1], val[3][2]));
+        }
+      }
+      continue;
+    }
+    // the ragged end of a row, padding columns, or a destination that is not 16-byte aligned
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int ox = ox0 + k;
+      if (ox >= p.out_w) break;
+      const bool inside = ox >= cin0 && ox < cin1;
+#pragma unroll
+      for (int c = 0; c < 3; ++c)
+        store_elem<DTYPE>(drow + p.chan_off[c] + (long long)ox * p.px_stride,
+                          inside ? val[k][c] : finish<DTYPE>(p, p.ch_pad[c], c));
+    }
+  }
+}
+
+template <int FMT, int LAYOUT, int DTYPE, int ARITH>
 __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kernel(const ResizeParams p) {
   using T = typename OutT<DTYPE>::type;
   constexpr bool kYuv = FMT == B2_SRC_NV12 || FMT == B2_SRC_I420;
   constexpr int kPlanes = FMT == B2_SRC_NV12 ? 4 : (FMT == B2_SRC_RGB_INTERLEAVED ? 2 : 6);
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ b2_image_desc sd;
-  __shared__ int s_off[kMaxSpans];
+  __shared__ RowInfo s_rows[kRows];
   // bar[0]: the staged rows.  bar[1]: nothing ever arrives on it (B2_DEBUG_EXPIRE_WAIT).
   __shared__ __align__(8) unsigned long long bar[2];
 
   const int n = blockIdx.y;
-  const int oy0 = blockIdx.x * p.rows;
   const int tid = threadIdx.x;
   if (tid < 16)
     reinterpret_cast<uint32_t*>(&sd)[tid] =
@@ -166,11 +343,11 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
     rin0 = max(0, -d.crop_y);
     rin1 = min(p.out_h, d.resized_h - d.crop_y);
   }
-  const bool any_cols = cin0 < cin1;
+  if (cin0 >= cin1) cin0 = cin1 = rin0 = rin1 = 0;  // nothing maps into the image: all padding
 
   // Horizontal extent of source pixels touched by this image's output columns.
   int xlo = 0, xhi = 1;
-  if (any_cols) {
+  if (cin0 < cin1) {
     const Axis ax_first = axis_of(d.scale_x, (float)(d.crop_x + cin0), d.src_w);
     const Axis ax_last = axis_of(d.scale_x, (float)(d.crop_x + cin1 - 1), d.src_w);
     xlo = ax_first.i0;
@@ -194,222 +371,158 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
     return;
   }
 
-  const int rows_here = min(p.rows, p.out_h - oy0);
-  if (tid < 32) {
-    const int lane = tid;
-    const int nspans = rows_here * kPlanes;
-    const int r = lane / kPlanes, pl = lane - r * kPlanes;
-    const int oy = oy0 + r;
-    const bool active = lane < nspans && any_cols && oy >= rin0 && oy < rin1;
-    long long key = -1 - lane;  // unique for idle lanes
-    const uint8_t* src = nullptr;
-    int lo = 0, bytes = 0, head = 0;
-    if (active) {
-      const Axis ay = axis_of(d.scale_y, (float)(d.crop_y + oy), d.src_h);
-      const int yrow = (pl & 1) ? ay.i1 : ay.i0;
-      if (pl < 2) {
-        key = yrow;
-        src = p.base + d.y_off + (size_t)yrow * d.y_pitch;
-        lo = blo;
-        bytes = bhi - blo;
-      } else {
-        const int plane = pl < 4 ? 1 : 2;          // second / third plane
-        const int prow = kYuv ? yrow >> 1 : yrow;  // chroma planes are half height
-        key = ((long long)plane << 32) | (uint32_t)prow;
-        src = p.base + (plane == 1 ? d.u_off : d.v_off) + (size_t)prow * d.uv_pitch;
-        lo = cxlo;
-        bytes = cxhi - cxlo;
-      }
-      head = (int)((uintptr_t)(src + lo) & 15);
-      bytes = (bytes + head + 15) & ~15;
-    }
-    // the first lane holding a given (plane, source row) fetches it; the others alias its slot
-    const unsigned same = __match_any_sync(0xffffffffu, key);
-    const int owner = __ffs(same) - 1;
-    const bool fetch = active && owner == lane;
-    if (lane < kMaxSpans) s_off[lane] = active ? owner * p.span_cap + head : 0;
-    const unsigned total = __reduce_add_sync(0xffffffffu, fetch ? (unsigned)bytes : 0u);
-    if (lane == 0)
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&bar[0])),
-                   "r"(total)
-                   : "memory");
-    __syncwarp();
-    if (fetch)
-      // The source must allow reads of every aligned 16-byte segment that holds at least one
-      // byte of a touched row (true of any allocation that starts and ends on such boundaries).
-      asm volatile(
-          "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-              smem_u32(smem + (size_t)lane * p.span_cap)),
-          "l"(src + lo - head), "r"(bytes), "r"(smem_u32(&bar[0]))
-          : "memory");
-  }
-  // While the copies are in flight: one table entry per output column (the horizontal taps are
-  // the same for every row of the image): byte offsets of the two tap columns in a staged
-  // first-plane row (x, y) and in a staged second/third-plane row (z, w), and the weight of the
-  // second tap (negative: a padding column).
-  uint4* const xoffs = reinterpret_cast<uint4*>(smem + (size_t)p.rows * kPlanes * p.span_cap);
-  float* const xw = reinterpret_cast<float*>(xoffs + p.out_w);
-  for (int ox = tid; ox < p.out_w; ox += kResizeThreads) {
-    if (ox < cin0 || ox >= cin1) {
-      xoffs[ox] = make_uint4(0u, 0u, 0u, 0u);
-      xw[ox] = -1.0f;
-      continue;
-    }
-    const Axis ax = axis_of(d.scale_x, (float)(d.crop_x + ox), d.src_w);
-    // inside [xlo, xhi) by construction; the clamp keeps a nonsensical descriptor in the rows
-    const int i0 = min(max(ax.i0, xlo), xhi - 1), i1 = min(max(ax.i1, xlo), xhi - 1);
-    const int m3 = FMT == B2_SRC_RGB_INTERLEAVED ? 3 : 1;
-    const uint32_t x0 = (uint32_t)(m3 * (i0 - xlo)), x1 = (uint32_t)(m3 * (i1 - xlo));
-    uint32_t c0, c1;
-    if constexpr (FMT == B2_SRC_NV12) {
-      c0 = (uint32_t)((i0 & ~1) - cxlo);
-      c1 = (uint32_t)((i1 & ~1) - cxlo);
-    } else if constexpr (FMT == B2_SRC_I420) {
-      c0 = (uint32_t)((i0 >> 1) - cxlo);
-      c1 = (uint32_t)((i1 >> 1) - cxlo);
-    } else {
-      c0 = x0;
-      c1 = x1;
-    }
-    xoffs[ox] = make_uint4(x0, x1, c0, c1);
-    xw[ox] = fmaxf(ax.w1, 0.0f);
-  }
-  __syncthreads();  // s_off and the column table are visible
-  if (!bounded_wait(smem_u32(&bar[0]), p.wait_limit)) {
-    // The rows did not arrive in time: report, give the copies that may still be in flight one
-    // more bounded wait (shared memory must not be released under them), and leave the tile.
-    report(B2_STATUS_WAIT_EXPIRED);
-    bounded_wait(smem_u32(&bar[0]), p.wait_limit);
-    return;
-  }
-  if (p.debug_flags & B2_DEBUG_EXPIRE_WAIT) {
-    if (!bounded_wait(smem_u32(&bar[1]), 4u)) {
-      report(B2_STATUS_WAIT_EXPIRED);
-      return;
-    }
-  }
-
-  // ---- compute: a warp per output row ------------------------------------------------------------
+  // Column table, one entry per output column (the horizontal taps are the same for every row of
+  // the image): byte offsets of the two tap columns in a staged first-plane row (x, y) and in a
+  // staged second/third-plane row (z, w), and the weight of the second tap.  Columns are handled
+  // in groups of four by one lane; entry k of group g sits at [k * groups + g] so that the lanes
+  // of a warp read neighbouring entries, and the four weights of a group form one vector.
+  const int groups = (p.out_w + 3) >> 2;
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t xoffs = sbase + (uint32_t)(p.rows * kPlanes * p.span_cap);
+  const uint32_t xw = xoffs + 64u * (uint32_t)groups;
   const int warp = tid >> 5, lane = tid & 31;
-  const int r = warp % p.rows;             // p.rows is 2 or 4
-  const int col0 = lane + 32 * (warp / p.rows);
-  const int cstep = 32 * (kResizeWarps / p.rows);
-  if (r >= rows_here) return;
-  const int oy = oy0 + r;
-  const ColorMat m = p.mat;
+  const int r = warp % p.rows;  // p.rows is 2 or 4: the output row of a tile this warp converts
+  const int g0 = lane + 32 * (warp / p.rows);
+  const int gstep = 32 * (kResizeWarps / p.rows);
   long long img = (long long)p.first_image + n;
   if (p.frames_per_group > 1) {
-    const long long g = img / p.frames_per_group;
-    img = g * p.group_stride + (img - g * p.frames_per_group) * p.image_stride;
+    const long long grp = img / p.frames_per_group;
+    img = grp * p.group_stride + (img - grp * p.frames_per_group) * p.image_stride;
   } else {
     img *= p.image_stride;
   }
-  T* const drow = static_cast<T*>(p.dst) + img + (long long)oy * p.row_stride;
-  T* const d0 = drow + p.chan_off[0];
-  T* const d1 = drow + p.chan_off[1];
-  T* const d2 = drow + p.chan_off[2];
-  auto store = [&](int ox, float v0, float v1, float v2) {  // blended values (scaled by 2^-24)
-    const long long o = (long long)ox * p.px_stride;
-    if constexpr (DTYPE == B2_U8) {
-      // floor(val + 0.5) as a subnormal bit pattern (val >= 0), then a saturating pack
-      const float unit = __uint_as_float(1u);
-      const uint32_t w = pack4_sat(__fmul_rz(__fmaf_rn(v0, kTapScale, 0.5f), unit),
-                                   __fmul_rz(__fmaf_rn(v1, kTapScale, 0.5f), unit),
-                                   __fmul_rz(__fmaf_rn(v2, kTapScale, 0.5f), unit), 0.0f);
-      d0[o] = (uint8_t)w;
-      d1[o] = (uint8_t)(w >> 8);
-      d2[o] = (uint8_t)(w >> 16);
-    } else {
-      const float f0 = __fmaf_rn(v0, p.ch_scale[0], p.ch_bias[0]);
-      const float f1 = __fmaf_rn(v1, p.ch_scale[1], p.ch_bias[1]);
-      const float f2 = __fmaf_rn(v2, p.ch_scale[2], p.ch_bias[2]);
-      if constexpr (DTYPE == B2_F32) {
-        d0[o] = f0;
-        d1[o] = f1;
-        d2[o] = f2;
-      } else {
-        d0[o] = __float2bfloat16_rn(f0);
-        d1[o] = __float2bfloat16_rn(f1);
-        d2[o] = __float2bfloat16_rn(f2);
+  T* const dimg = static_cast<T*>(p.dst) + img;
+  const MatPairs<ARITH> m(p.mat);  // the coefficients as register pairs, built once
+
+  // A CTA converts p.tiles consecutive tiles of p.rows output rows, one after the other through
+  // the same staging buffer: what depends on the image only (descriptor, geometry, the column
+  // table) is then worked out once for all of them.
+  for (int tile = 0; tile < p.tiles; ++tile) {
+    const int oy0 = (blockIdx.x * p.tiles + tile) * p.rows;
+    if (oy0 >= p.out_h) break;
+    const int rows_here = min(p.rows, p.out_h - oy0);
+    if (tile > 0) __syncthreads();  // every warp is done with the rows of the previous tile
+    bool arrived = true;
+    if (tid < 32) {
+      const int nspans = rows_here * kPlanes;
+      const int sr = lane / kPlanes, pl = lane - sr * kPlanes;
+      const int oy = oy0 + sr;
+      const bool active = lane < nspans && oy >= rin0 && oy < rin1;
+      long long key = -1 - lane;  // unique for idle lanes
+      const uint8_t* src = nullptr;
+      int lo = 0, bytes = 0, head = 0;
+      if (active) {
+        const Axis ay = axis_of(d.scale_y, (float)(d.crop_y + oy), d.src_h);
+        const int yrow = (pl & 1) ? ay.i1 : ay.i0;
+        if (pl == 0) {
+          s_rows[sr].wy0 = __fsub_rn(1.0f, ay.w1);
+          s_rows[sr].wy1 = ay.w1;
+        }
+        if (pl < 2) {
+          key = yrow;
+          src = p.base + d.y_off + (size_t)yrow * d.y_pitch;
+          lo = blo;
+          bytes = bhi - blo;
+        } else {
+          const int plane = pl < 4 ? 1 : 2;          // second / third plane
+          const int prow = kYuv ? yrow >> 1 : yrow;  // chroma planes are half height
+          key = ((long long)plane << 32) | (uint32_t)prow;
+          src = p.base + (plane == 1 ? d.u_off : d.v_off) + (size_t)prow * d.uv_pitch;
+          lo = cxlo;
+          bytes = cxhi - cxlo;
+        }
+        head = (int)((uintptr_t)(src + lo) & 15);
+        bytes = (bytes + head + 15) & ~15;
+      }
+      // the first lane holding a given (plane, source row) fetches it; the others alias its slot
+      const unsigned same = __match_any_sync(0xffffffffu, key);
+      const int owner = __ffs(same) - 1;
+      const bool fetch = active && owner == lane;
+      if (active) s_rows[sr].row[pl] = sbase + (uint32_t)(owner * p.span_cap + head);
+      const unsigned total = __reduce_add_sync(0xffffffffu, fetch ? (unsigned)bytes : 0u);
+      if (tile > 0)  // order the other warps' reads of the buffer before the engine's writes
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      if (lane == 0)
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
+                         smem_u32(&bar[0])),
+                     "r"(total)
+                     : "memory");
+      __syncwarp();
+      if (fetch)
+        // The source must allow reads of every aligned 16-byte segment that holds at least one
+        // byte of a touched row (true of any allocation that starts and ends on such boundaries).
+        asm volatile(
+            "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+                "r"(sbase + (uint32_t)(lane * p.span_cap)),
+            "l"(src + lo - head), "r"(bytes), "r"(smem_u32(&bar[0]))
+            : "memory");
+    }
+    if (tile == 0) {
+      // the column table, while the first copies are in flight
+      for (int ox = tid; ox < 4 * groups; ox += kResizeThreads) {
+        const int oxc = min(max(ox, cin0), max(cin1 - 1, cin0));  // padding repeats an edge column
+        const Axis ax = axis_of(d.scale_x, (float)(d.crop_x + oxc), d.src_w);
+        // inside [xlo, xhi) by construction; the clamp keeps a nonsensical descriptor in the rows
+        const int i0 = min(max(ax.i0, xlo), xhi - 1), i1 = min(max(ax.i1, xlo), xhi - 1);
+        const int m3 = FMT == B2_SRC_RGB_INTERLEAVED ? 3 : 1;
+        const uint32_t x0 = (uint32_t)(m3 * (i0 - xlo)), x1 = (uint32_t)(m3 * (i1 - xlo));
+        uint32_t c0, c1;
+        if constexpr (FMT == B2_SRC_NV12) {
+          c0 = (uint32_t)((i0 & ~1) - cxlo);
+          c1 = (uint32_t)((i1 & ~1) - cxlo);
+        } else if constexpr (FMT == B2_SRC_I420) {
+          c0 = (uint32_t)((i0 >> 1) - cxlo);
+          c1 = (uint32_t)((i1 >> 1) - cxlo);
+        } else {
+          c0 = x0;
+          c1 = x1;
+        }
+        const int grp = ox >> 2, k = ox & 3;
+        reinterpret_cast<uint4*>(smem + (xoffs - sbase))[k * groups + grp] =
+            make_uint4(x0, x1, c0, c1);
+        reinterpret_cast<float*>(smem + (xw - sbase))[ox] = ax.w1;
       }
     }
-  };
-  if (!any_cols || oy < rin0 || oy >= rin1) {  // a row of padding
-    for (int ox = col0; ox < p.out_w; ox += cstep) store(ox, p.ch_pad[0], p.ch_pad[1], p.ch_pad[2]);
-    return;
-  }
+    // Warp 0 waits for the rows (the other warps wait at the barrier, which costs no issue
+    // slots); the barrier publishes the rows, s_rows and the column table to everybody and makes
+    // the outcome one decision for the whole CTA.
+    if (tid < 32) arrived = bounded_wait(smem_u32(&bar[0]), (uint32_t)(tile & 1), p.wait_limit);
+    if (!__syncthreads_and(arrived)) {
+      // The rows did not arrive in time: report, give the copies that may still be in flight one
+      // more bounded wait (shared memory must not be released under them), and leave.
+      report(B2_STATUS_WAIT_EXPIRED);
+      bounded_wait(smem_u32(&bar[0]), (uint32_t)(tile & 1), p.wait_limit);
+      return;
+    }
+    if (p.debug_flags & B2_DEBUG_EXPIRE_WAIT) {
+      if (!__syncthreads_and(bounded_wait(smem_u32(&bar[1]), 0u, 4u))) {
+        report(B2_STATUS_WAIT_EXPIRED);
+        return;
+      }
+    }
 
-  const Axis ay = axis_of(d.scale_y, (float)(d.crop_y + oy), d.src_h);
-  const float2 wy = make_float2(__fsub_rn(1.0f, ay.w1), ay.w1);  // {wy0, wy1}
-  const int* so = s_off + r * kPlanes;
-  const unsigned char* y0p = smem + so[0];
-  const unsigned char* y1p = smem + so[1];
-  const unsigned char* u0p = kPlanes > 2 ? smem + so[2] : nullptr;
-  const unsigned char* u1p = kPlanes > 2 ? smem + so[3] : nullptr;
-  const unsigned char* v0p = kPlanes > 4 ? smem + so[4] : nullptr;
-  const unsigned char* v1p = kPlanes > 4 ? smem + so[5] : nullptr;
-  // interleaved chroma pairs can be fetched with one 16-bit load when the staged rows kept an
-  // even address (they do whenever the source plane and pitch are even)
-  const bool uv16 = FMT == B2_SRC_NV12 && ((so[2] | so[3]) & 1) == 0;
-  (void)u0p; (void)u1p; (void)v0p; (void)v1p; (void)uv16;
-
-  for (int ox = col0; ox < p.out_w; ox += cstep) {
-    const float w1 = xw[ox];
-    if (w1 < 0.0f) {  // a padding column
-      store(ox, p.ch_pad[0], p.ch_pad[1], p.ch_pad[2]);
+    // ---- compute: a warp per output row ----------------------------------------------------------
+    if (r >= rows_here) continue;
+    const int oy = oy0 + r;
+    T* const drow = dimg + (long long)oy * p.row_stride;
+    if (oy < rin0 || oy >= rin1) {  // a row of padding
+      for (int ox = lane + 32 * (warp / p.rows); ox < p.out_w; ox += gstep)
+#pragma unroll
+        for (int c = 0; c < 3; ++c)
+          store_elem<DTYPE>(drow + p.chan_off[c] + (long long)ox * p.px_stride,
+                            finish<DTYPE>(p, p.ch_pad[c], c));
       continue;
     }
-    const uint4 e = xoffs[ox];
-    const float2 wx1 = dup2(w1), wx0 = dup2(__fsub_rn(1.0f, w1));
-    float2 t[2][3];  // [column x0/x1][channel], lanes = {row y0, row y1}, clamped 0..255
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      const uint32_t sx = c ? e.y : e.x;
-      const uint32_t ci = c ? e.w : e.z;
-      if constexpr (!kYuv) {
-        // already RGB: the taps are the bytes themselves (two rows into 16-bit lanes)
-        if constexpr (FMT == B2_SRC_RGB_PLANAR) {
-          t[c][0] = halves_to_float2(__byte_perm(y0p[sx], y1p[sx], 0x5410u));
-          t[c][1] = halves_to_float2(__byte_perm(u0p[ci], u1p[ci], 0x5410u));
-          t[c][2] = halves_to_float2(__byte_perm(v0p[ci], v1p[ci], 0x5410u));
-        } else {
-#pragma unroll
-          for (int ch = 0; ch < 3; ++ch)
-            t[c][ch] = halves_to_float2(__byte_perm(y0p[sx + ch], y1p[sx + ch], 0x5410u));
-        }
-      } else {
-        float2 bu, bv;
-        if constexpr (FMT == B2_SRC_NV12) {
-          uint32_t p0, p1;  // {U, V} of row 0 / row 1
-          if (uv16) {
-            p0 = *reinterpret_cast<const uint16_t*>(u0p + ci);
-            p1 = *reinterpret_cast<const uint16_t*>(u1p + ci);
-          } else {
-            p0 = u0p[ci] | ((uint32_t)u0p[ci + 1] << 8);
-            p1 = u1p[ci] | ((uint32_t)u1p[ci + 1] << 8);
-          }
-          bu = make_float2(biased_byte(p0, 0), biased_byte(p1, 0));
-          bv = make_float2(biased_byte(p0, 1), biased_byte(p1, 1));
-        } else {
-          bu = make_float2(biased(u0p[ci]), biased(u1p[ci]));
-          bv = make_float2(biased(v0p[ci]), biased(v1p[ci]));
-        }
-        const Chroma2 ch = chroma2_of<ARITH>(m, bu, bv);
-        float2 cr, cg, cb;
-        pixel2_bits<ARITH>(m, make_float2(biased(y0p[sx]), biased(y1p[sx])), ch, cr, cg, cb);
-        t[c][0] = clamp_to_float2(cr);
-        t[c][1] = clamp_to_float2(cg);
-        t[c][2] = clamp_to_float2(cb);
-      }
-    }
-    float val[3];
-#pragma unroll
-    for (int c = 0; c < 3; ++c) {
-      // {top, bot} = fma(wx1, t?1, wx0 * t?0) for both rows at once
-      const float2 tb = x2_fma(wx1, t[1][c], x2_mul(wx0, t[0][c]));
-      val[c] = __fmaf_rn(wy.y, tb.y, __fmul_rn(wy.x, tb.x));
-    }
-    store(ox, val[0], val[1], val[2]);
+    const RowInfo in = s_rows[r];
+    // interleaved chroma pairs can be fetched with one 16-bit load when the staged rows kept an
+    // even address (they do whenever the source plane and pitch are even)
+    const bool uv16 = FMT == B2_SRC_NV12 && ((in.row[2] | in.row[3]) & 1) == 0;
+    if (uv16)
+      convert_row<FMT, LAYOUT, DTYPE, ARITH, true>(p, m, in, xoffs, xw, drow, g0, groups, gstep,
+                                                   groups, cin0, cin1);
+    else
+      convert_row<FMT, LAYOUT, DTYPE, ARITH, false>(p, m, in, xoffs, xw, drow, g0, groups, gstep,
+                                                    groups, cin0, cin1);
   }
 }
 
@@ -425,15 +538,15 @@ int allow_big_smem(K kern, int device, std::atomic<unsigned long long>& done) {
   return B2_OK;
 }
 
-template <int FMT, int DTYPE, int ARITH>
+template <int FMT, int LAYOUT, int DTYPE, int ARITH>
 int launch_t(const b2_resize_args& a, const ResizeParams& p, size_t smem, cudaStream_t stream) {
-  auto kern = resize_kernel<FMT, DTYPE, ARITH>;
+  auto kern = resize_kernel<FMT, LAYOUT, DTYPE, ARITH>;
   static std::atomic<unsigned long long> big_smem_done{0};
   if (smem > 48 * 1024) {
     const int rc = allow_big_smem(kern, a.device, big_smem_done);
     if (rc != B2_OK) return rc;
   }
-  const int row_blocks = (a.out_h + p.rows - 1) / p.rows;
+  const int row_blocks = (a.out_h + p.rows * p.tiles - 1) / (p.rows * p.tiles);
   for (int n0 = 0; n0 < a.num_images; n0 += 65535) {
     const int nn = a.num_images - n0 < 65535 ? a.num_images - n0 : 65535;
     ResizeParams q = p;
@@ -445,13 +558,18 @@ int launch_t(const b2_resize_args& a, const ResizeParams& p, size_t smem, cudaSt
   return B2_OK;
 }
 
+template <int FMT, int LAYOUT, int ARITH>
+int launch_fla(const b2_resize_args& a, const ResizeParams& p, size_t smem, cudaStream_t s) {
+  switch (a.dtype) {
+    case B2_U8: return launch_t<FMT, LAYOUT, B2_U8, ARITH>(a, p, smem, s);
+    case B2_F32: return launch_t<FMT, LAYOUT, B2_F32, ARITH>(a, p, smem, s);
+    default: return launch_t<FMT, LAYOUT, B2_BF16, ARITH>(a, p, smem, s);
+  }
+}
 template <int FMT, int ARITH>
 int launch_fa(const b2_resize_args& a, const ResizeParams& p, size_t smem, cudaStream_t s) {
-  switch (a.dtype) {
-    case B2_U8: return launch_t<FMT, B2_U8, ARITH>(a, p, smem, s);
-    case B2_F32: return launch_t<FMT, B2_F32, ARITH>(a, p, smem, s);
-    default: return launch_t<FMT, B2_BF16, ARITH>(a, p, smem, s);
-  }
+  return a.layout == B2_NCHW ? launch_fla<FMT, B2_NCHW, ARITH>(a, p, smem, s)
+                             : launch_fla<FMT, B2_NHWC, ARITH>(a, p, smem, s);
 }
 
 }  // namespace
@@ -478,6 +596,12 @@ int launch_resize(const b2_resize_args& a, cudaStream_t stream) {
     p.ch_bias[c] = a.bias[slot];
     p.ch_pad[c] = a.pad_value[c] * (1.0f / 16777216.0f);
   }
+  // Vector stores need every group of four pixels 16-byte aligned in the destination.
+  const int esz = a.dtype == B2_U8 ? 1 : (a.dtype == B2_F32 ? 4 : 2);
+  auto aligned16 = [&](long long elements) { return (elements * esz) % 16 == 0; };
+  p.vec_store = a.out_w % 4 == 0 && (uintptr_t)a.dst % 16 == 0 && aligned16(p.image_stride) &&
+                aligned16(p.group_stride) && aligned16(p.row_stride) &&
+                (a.layout != B2_NCHW || aligned16(plane));
   p.status = a.status;
   p.wait_limit = 1u << 20;
   p.debug_flags = a.debug_flags;
@@ -487,7 +611,8 @@ int launch_resize(const b2_resize_args& a, cudaStream_t stream) {
       a.src_format == B2_SRC_RGB_INTERLEAVED ? 3LL * a.max_src_w : (long long)a.max_src_w;
   const long long span = ((row_bytes + 2 + 15 + 15) / 16) * 16;
   const int planes = a.src_format == B2_SRC_NV12 ? 4 : (a.src_format == B2_SRC_RGB_INTERLEAVED ? 2 : 6);
-  const size_t table = (size_t)a.out_w * 20;  // 16 bytes of offsets + 4 bytes of weight per column
+  // per column 16 bytes of offsets + 4 bytes of weight, for whole groups of four columns
+  const size_t table = (size_t)((a.out_w + 3) / 4) * 80;
   // Four output rows per CTA amortise the per-CTA work best; wide sources (4K rows) take two,
   // which halves the staging buffer and lets more CTAs share an SM.
   p.rows = (size_t)kRows * planes * span + table > 40 * 1024 ? 2 : kRows;
@@ -497,6 +622,12 @@ int launch_resize(const b2_resize_args& a, cudaStream_t stream) {
                 "max_src_w %d and out_w %d need %zu bytes of staging; the limit is %d bytes",
                 a.max_src_w, a.out_w, smem, 200 * 1024);
   p.span_cap = (int)span;
+  // Tiles per CTA: enough to spread the per-image work of a CTA over many rows, few enough to
+  // leave every SM several CTAs' worth of an image batch (148 SMs x 8 resident CTAs).
+  p.tiles = 4;
+  while (p.tiles > 1 && (long long)a.num_images * ((a.out_h + p.rows * p.tiles - 1) /
+                                                    (p.rows * p.tiles)) < 4 * 148 * 8)
+    p.tiles >>= 1;
   const bool sws = a.arith == B2_ARITH_SWSCALE;
   switch (a.src_format) {
     case B2_SRC_NV12:
