@@ -32,7 +32,7 @@ class CUDAArrayInterface(Protocol):
 def to_numpy(buffer: Any) -> np.ndarray:
     """View a host buffer (``__array_interface__``) as a NumPy array without copying."""
     if not hasattr(buffer, "__array_interface__"):
-        raise RuntimeError("The given object does not have `__array_interface__` attribute.")
+        raise RuntimeError(f"{type(buffer).__name__} does not expose `__array_interface__`.")
     return np.array(buffer, copy=False)
 
 
@@ -48,17 +48,14 @@ def to_torch(buffer: Any, dtype: Any = None):
     iface = getattr(buffer, "__cuda_array_interface__", None)
     if iface is not None:
         if any(s == 0 for s in iface.get("shape", [])):
-            raise ValueError("0-element array is not supported.")
+            raise ValueError("An array without elements cannot be wrapped.")
         data_ptr = iface["data"][0]
         tensor = torch.as_tensor(buffer, device=f"cuda:{buffer.device_index}")
-        if tensor.data_ptr() == 0:
-            raise RuntimeError(
-                "Failed to convert to PyTorch Tensor. "
-                f"src: {data_ptr}, dst: {tensor.data_ptr()}, device: {buffer.device_index}")
         if tensor.data_ptr() != data_ptr:
+            # torch made a copy (or produced nothing): the result would not alias the buffer
             raise RuntimeError(
-                "[INTERNAL ERROR] Failed to perform zero-copy conversion to PyTorch Tensor. "
-                f"src: {data_ptr}, dst: {tensor.data_ptr()}, device: {buffer.device_index}")
+                f"PyTorch did not wrap the buffer in place: buffer at {data_ptr:#x}, tensor at "
+                f"{tensor.data_ptr():#x} (device {buffer.device_index}).")
     else:
         tensor = torch.as_tensor(to_numpy(buffer))
     if dtype is not None and tensor.dtype != dtype:

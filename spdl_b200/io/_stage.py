@@ -73,7 +73,8 @@ class FrameStage:
             if index is None:
                 index = int(os.environ.get("LOCAL_RANK", "0"))
             if index >= torch.cuda.device_count():
-                raise RuntimeError("The local rank is larger than the number of available GPUs.")
+                raise RuntimeError(f"Local rank {index} was asked for, but this process sees only "
+                                   f"{torch.cuda.device_count()} CUDA device(s).")
             stream = torch.cuda.Stream(torch.device("cuda", index))
             st = {"stream": stream, "cfg": cuda_config(index, stream=stream.cuda_stream),
                   "cache": [None] * self._num_caches, "descs": {}}

@@ -1,26 +1,40 @@
-"""``transfer_tensor``: move CPU tensors to the GPU on a dedicated per-thread stream.
+"""``transfer_tensor``: move the CPU tensors of a batch to the GPU from a pipeline worker thread.
 
-Mirrors ``spdl.io.transfer_tensor`` (``src/spdl/io/_transfer.py:33-177``): containers are
-walked recursively; each CPU tensor is pinned and copied with ``non_blocking=True`` on a stream
-owned by the calling thread on ``cuda:{LOCAL_RANK}``; the stream is synchronised before
-returning; the last ``num_caches`` batches are kept alive so the caching allocator cannot hand
+Behaviour follows ``spdl.io.transfer_tensor`` (``src/spdl/io/_transfer.py:33-177``): the batch may
+be a tensor, a list, tuple, dict, named tuple or dataclass of them, nested; every CPU tensor in it
+is replaced by a copy on ``cuda:{LOCAL_RANK}``, everything else is passed through; the copies run
+on a stream that belongs to the calling thread, the call returns after that stream is idle, and
+the last ``num_caches`` results are kept referenced so that the caching allocator cannot hand
 their memory to another stream while a consumer still reads it.
+
+The transport is this package's own.  Each thread owns one page-locked staging arena
+(``b2_alloc_pinned``), grown geometrically and reused by every call: a batch is packed into it
+with plain memory copies (the reference pins every tensor anew with ``Tensor.pin_memory()``, one
+``cudaHostAlloc`` per tensor per call), each tensor goes to the device with
+``b2_transfer_h2d_async`` on the thread's stream, and the stream is synchronised once per batch.
+Tensors that are already page-locked are copied from where they are.
 """
 
 from __future__ import annotations
 
+import ctypes
 import dataclasses
 import os
 import threading
-from functools import partial
+from collections import deque
 from typing import Any, Callable, TypeVar
+
+from .. import _lib
 
 T = TypeVar("T")
 
 __all__ = ["transfer_tensor"]
 
+_ALIGN = 256  # staging offsets; keeps every tensor on its own cache lines
+
 
 def _recursive_apply(fn: Callable[[Any], Any], obj: Any) -> Any:
+    """``obj`` with ``fn`` applied to every leaf; containers keep their type."""
     if isinstance(obj, tuple) and hasattr(obj, "_fields"):  # namedtuple
         return type(obj)(*(_recursive_apply(fn, v) for v in obj))
     if isinstance(obj, (list, tuple)):
@@ -38,52 +52,143 @@ def _recursive_apply(fn: Callable[[Any], Any], obj: Any) -> Any:
     return fn(obj)
 
 
-def _transfer(obj: Any, device: Any, pinned_cache: set) -> Any:
-    import torch
+def _leaves(obj: Any):
+    """The leaves of ``obj`` in the order ``_recursive_apply`` visits them."""
+    if isinstance(obj, (list, tuple)):
+        for v in obj:
+            yield from _leaves(v)
+    elif isinstance(obj, dict):
+        for v in obj.values():
+            yield from _leaves(v)
+    elif dataclasses.is_dataclass(obj) and not isinstance(obj, type):
+        fields = dataclasses.fields(obj)
+        for f in [f for f in fields if f.init] + [f for f in fields if not f.init]:
+            yield from _leaves(getattr(obj, f.name))
+    else:
+        yield obj
 
-    if isinstance(obj, torch.Tensor) and obj.is_cpu:
-        pinned = obj.pin_memory()
-        pinned_cache.add(pinned)
-        obj = pinned.to(device, non_blocking=True)
-    return obj
+
+class _StagingArena:
+    """One page-locked block per thread, at least as large as the largest batch seen so far."""
+
+    def __init__(self) -> None:
+        self.ptr, self.capacity = 0, 0
+
+    def reserve(self, nbytes: int) -> int:
+        if nbytes > self.capacity:
+            self.release()
+            size = 1 << max(20, (nbytes - 1).bit_length())  # next power of two, 1 MiB at least
+            p = ctypes.c_void_p()
+            _lib.check(_lib.lib().b2_alloc_pinned(ctypes.byref(p), size))
+            self.ptr, self.capacity = int(p.value), size
+        return self.ptr
+
+    def release(self) -> None:
+        if self.ptr:
+            _lib.check(_lib.lib().b2_free_pinned(self.ptr))
+            self.ptr, self.capacity = 0, 0
+
+    def __del__(self) -> None:
+        try:
+            self.release()
+        except Exception:  # interpreter shutdown: the driver reclaims the block
+            pass
 
 
-class _DataTransfer:
-    def __init__(self, device: Any, num_caches: int) -> None:
+class _ThreadTransfer:
+    """The per-thread state: device, private stream, staging arena and the keep-alive window."""
+
+    def __init__(self, device_index: int, num_caches: int) -> None:
         import torch
 
-        self._device = device
-        self._stream = torch.cuda.Stream(device)
-        self._batch_cache: list[Any] = [None for _ in range(num_caches)]
+        self.index = device_index
+        self.device = torch.device("cuda", device_index)
+        self.stream = torch.cuda.Stream(self.device)
+        self.arena = _StagingArena()
+        self.recent: deque = deque([None] * num_caches, maxlen=num_caches) if num_caches else None
 
+    # -- the three device-side steps, separate so that the order of calls can be tested on CPU ----
+    def _empty_like_on_device(self, tensor):
+        import torch
+
+        with torch.cuda.stream(self.stream):  # the allocation belongs to this thread's stream
+            return torch.empty(tensor.shape, dtype=tensor.dtype, device=self.device)
+
+    def _copy_async(self, dst_ptr: int, host_ptr: int, nbytes: int) -> None:
+        _lib.check(_lib.lib().b2_transfer_h2d_async(dst_ptr, host_ptr, nbytes, self.index,
+                                                    self.stream.cuda_stream))
+
+    def _synchronize(self) -> None:
+        _lib.check(_lib.lib().b2_stream_synchronize(self.index, self.stream.cuda_stream))
+
+    # -- one batch -----------------------------------------------------------------------------------
     def __call__(self, batch: T) -> T:
         import torch
 
-        pinned_cache: set = set()
-        fn = partial(_transfer, device=self._device, pinned_cache=pinned_cache)
-        with torch.cuda.stream(self._stream):
-            batch = _recursive_apply(fn, batch)
-        self._stream.synchronize()
-        self._batch_cache.append(batch)
-        self._batch_cache.pop(0)
-        return batch
+        def is_cpu_tensor(obj: Any) -> bool:
+            return isinstance(obj, torch.Tensor) and obj.device.type == "cpu"
+
+        # pass 1: what has to be staged (pageable tensors), and how much room that takes
+        pending: list = []  # (contiguous source, staging offset or None)
+        total = 0
+
+        for obj in _leaves(batch):
+            if is_cpu_tensor(obj):
+                src = obj.contiguous()
+                nbytes = src.numel() * src.element_size()
+                if nbytes and not src.is_pinned():
+                    pending.append((src, total))
+                    total += -(-nbytes // _ALIGN) * _ALIGN
+                else:
+                    pending.append((src, None))
+        base = self.arena.reserve(total) if total else 0
+        queue = iter(pending)
+
+        # pass 2: same walk, same order: stage, allocate on the device, queue the copy
+        def move(obj: Any) -> Any:
+            if not is_cpu_tensor(obj):
+                return obj
+            src, offset = next(queue)
+            nbytes = src.numel() * src.element_size()
+            out = self._empty_like_on_device(src)
+            if nbytes:
+                host = src.data_ptr()
+                if offset is not None:
+                    host = base + offset
+                    ctypes.memmove(host, src.data_ptr(), nbytes)  # drops the GIL while it copies
+                self._copy_async(out.data_ptr(), host, nbytes)
+            return out
+
+        result = _recursive_apply(move, batch)
+        self._synchronize()  # once per batch; the arena and the pinned sources are free again
+        if self.recent is not None:
+            self.recent.append(result)
+        return result
 
 
 _THREAD_LOCAL = threading.local()
 
 
-def _get_transfer_func(num_caches: int) -> _DataTransfer:
-    import torch
+def _thread_transfer(num_caches: int) -> _ThreadTransfer:
+    state = getattr(_THREAD_LOCAL, "transfer", None)
+    if state is None:
+        import torch
 
-    if not hasattr(_THREAD_LOCAL, "transfer"):
         local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-        if local_rank >= torch.cuda.device_count():
-            raise RuntimeError("The local rank is larger than the number of available GPUs.")
-        _THREAD_LOCAL.transfer = _DataTransfer(torch.device(f"cuda:{local_rank}"), num_caches)
-    return _THREAD_LOCAL.transfer
+        available = torch.cuda.device_count()
+        if local_rank >= available:
+            raise RuntimeError(
+                f"LOCAL_RANK is {local_rank}, but this process sees only {available} CUDA "
+                f"device(s).")
+        state = _THREAD_LOCAL.transfer = _ThreadTransfer(local_rank, num_caches)
+    return state
 
 
 def transfer_tensor(batch: T, /, *, num_caches: int = 4) -> T:
     """Transfer the CPU tensors inside ``batch`` (tensor, list, tuple, dict or dataclass) to the
-    GPU chosen by ``LOCAL_RANK`` on a stream private to the calling thread."""
-    return _get_transfer_func(num_caches)(batch)
+    GPU chosen by ``LOCAL_RANK`` on a stream private to the calling thread.
+
+    ``num_caches`` (read when a thread makes its first call) is how many of the thread's latest
+    results stay referenced after they have been returned.
+    """
+    return _thread_transfer(num_caches)(batch)

@@ -139,7 +139,8 @@ class ShardWorker:
 
         self.info = info or rank_info()
         if self.info.local_rank >= torch.cuda.device_count():
-            raise RuntimeError("The local rank is larger than the number of available GPUs.")
+            raise RuntimeError(f"Local rank {self.info.local_rank} was asked for, but this process "
+                               f"sees only {torch.cuda.device_count()} CUDA device(s).")
         self.device = torch.device(f"cuda:{self.info.local_rank}")
         torch.cuda.set_device(self.device)
         _lib.check(_lib.lib().b2_init(self.info.local_rank))

@@ -219,38 +219,67 @@ def test_recursive_apply_over_containers():
     assert out["d"].x == 6 and out["d"].tag == "t" and out["d"].derived == 10
 
 
-def test_transfer_tensor_call_order_mocked():
+def test_leaves_follow_the_order_of_the_container_walk():
+    from spdl_b200.io._transfer import _leaves, _recursive_apply
+
+    s = Sample(3, "t")
+    s.derived = 5
+    batch = {"l": [1, (2, "s")], "p": Pair(4, [5]), "d": s, "n": None}
+    seen = []
+    _recursive_apply(lambda v: seen.append(v) or v, batch)
+    assert list(_leaves(batch)) == seen == [1, 2, "s", 4, 5, 3, "t", 5, None]
+
+
+def test_transfer_tensor_stages_copies_and_synchronises_once(monkeypatch):
+    """The host side of ``transfer_tensor`` without a GPU: pageable tensors are packed into one
+    staging block at aligned offsets, pinned ones are copied from where they are, every copy is
+    queued before the single synchronise, and the last ``num_caches`` results stay referenced."""
     import torch
 
     from spdl_b200.io import _transfer
 
     events = []
-    stream = mock.MagicMock()
-    stream.synchronize.side_effect = lambda: events.append("sync")
 
-    class FakeCtx:
-        def __enter__(self):
-            events.append("enter")
+    class Fake(_transfer._ThreadTransfer):
+        def __init__(self, num_caches):  # no CUDA stream, no device
+            from collections import deque
 
-        def __exit__(self, *a):
-            events.append("exit")
+            self.index, self.arena = 0, _transfer._StagingArena()
+            self.recent = deque([None] * num_caches, maxlen=num_caches) if num_caches else None
 
-    cpu = torch.arange(6)
-    pinned, moved = mock.MagicMock(), object()
-    pinned.to.side_effect = lambda dev, non_blocking: (events.append(("to", non_blocking)), moved)[1]
-    with mock.patch.object(torch.cuda, "Stream", return_value=stream), \
-            mock.patch.object(torch.cuda, "stream", return_value=FakeCtx()), \
-            mock.patch.object(torch.cuda, "device_count", return_value=1), \
-            mock.patch.object(torch.Tensor, "pin_memory", return_value=pinned):
-        _transfer._THREAD_LOCAL.__dict__.pop("transfer", None)
-        out = _transfer.transfer_tensor([cpu, "keep"], num_caches=2)
-        assert out == [moved, "keep"]
-        assert events == ["enter", ("to", True), "exit", "sync"]
-        tr = _transfer._THREAD_LOCAL.transfer
-        assert tr._batch_cache == [None, out]
-        _transfer.transfer_tensor(cpu)
-        assert tr._batch_cache[0] is out
-    _transfer._THREAD_LOCAL.__dict__.pop("transfer", None)
+        def _empty_like_on_device(self, t):
+            return torch.empty_like(t)  # stands in for device memory
+
+        def _copy_async(self, dst, host, nbytes):
+            events.append(("copy", host, nbytes))
+            ctypes.memmove(dst, host, nbytes)
+
+        def _synchronize(self):
+            events.append(("sync",))
+
+    block = (ctypes.c_char * (1 << 20))()
+    base = ctypes.addressof(block)
+    monkeypatch.setattr(_transfer._StagingArena, "reserve",
+                        lambda self, n: events.append(("reserve", n)) or base)
+    a = torch.arange(100, dtype=torch.int32)           # 400 bytes -> 512 in the arena
+    b = torch.arange(24, dtype=torch.float32).reshape(4, 6).t()  # not contiguous, 96 bytes
+    empty = torch.zeros(0)
+    tr = Fake(num_caches=2)
+    out = tr({"a": a, "rest": [b, "label", empty]})
+    assert torch.equal(out["a"], a) and torch.equal(out["rest"][0], b)
+    assert out["rest"][1] == "label" and out["rest"][2].numel() == 0
+    assert out["a"].data_ptr() != a.data_ptr()
+    assert events == [("reserve", 512 + 256), ("copy", base, 400), ("copy", base + 512, 96),
+                      ("sync",)]
+    assert list(tr.recent) == [None, out]
+    second = tr(a)
+    third = tr(a)
+    assert list(tr.recent) == [second, third]          # `out` has left the window
+    # a tensor that reports itself page-locked is copied from its own memory
+    events.clear()
+    monkeypatch.setattr(torch.Tensor, "is_pinned", lambda self, *a: True)
+    tr(a)
+    assert events == [("copy", a.data_ptr(), 400), ("sync",)]
 
 
 def test_transfer_tensor_rejects_bad_local_rank(monkeypatch):
@@ -261,7 +290,7 @@ def test_transfer_tensor_rejects_bad_local_rank(monkeypatch):
     monkeypatch.setenv("LOCAL_RANK", "3")
     _transfer._THREAD_LOCAL.__dict__.pop("transfer", None)
     with mock.patch.object(torch.cuda, "device_count", return_value=1):
-        with pytest.raises(RuntimeError):
+        with pytest.raises(RuntimeError, match="LOCAL_RANK is 3"):
             _transfer.transfer_tensor(torch.zeros(1))
 
 
