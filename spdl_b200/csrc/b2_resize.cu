@@ -54,7 +54,7 @@ struct ResizeParams {
   int rows;                              // output rows per tile: 4, or 2 for wide sources
   int tiles;                             // tiles a CTA converts, one after the other
   int* status;                           // optional device word for B2_STATUS_* bits
-  unsigned wait_limit;                   // polls of about a microsecond each
+  unsigned wait_limit;                   // polls of a bounded wait
   int debug_flags;
 };
 
@@ -113,18 +113,21 @@ __device__ __forceinline__ float2 x2_mul(float2 a, float2 b) {
   return unpack2(d);
 }
 
-// Waits for the phase of an mbarrier with the given parity, at most `limit` polls of about a
-// microsecond each.
+// Waits for the phase of an mbarrier with the given parity: at most `limit` polls, sleeping a few
+// hundred nanoseconds between them (a sleeping warp takes no issue slots from its neighbours).
 __device__ __forceinline__ bool bounded_wait(uint32_t bar_addr, uint32_t parity, unsigned limit) {
-  uint32_t done = 0;
-  for (unsigned spin = 0; spin < limit && !done; ++spin)
+  for (unsigned spin = 0; spin < limit; ++spin) {
+    uint32_t done;
     asm volatile(
-        "{ .reg .pred P; mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3; "
+        "{ .reg .pred P; mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2; "
         "selp.u32 %0, 1, 0, P; }"
         : "=r"(done)
-        : "r"(bar_addr), "r"(parity), "r"(1000u)
+        : "r"(bar_addr), "r"(parity)
         : "memory");
-  return done != 0;
+    if (done) return true;
+    __nanosleep(spin < 64 ? 100 : 2000);
+  }
+  return false;
 }
 
 // ---- shared-memory loads by 32-bit shared address (no generic-pointer arithmetic) ---------------
@@ -344,6 +347,17 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
     rin1 = min(p.out_h, d.resized_h - d.crop_y);
   }
   if (cin0 >= cin1) cin0 = cin1 = rin0 = rin1 = 0;  // nothing maps into the image: all padding
+  // Source coordinates must stay where floor() by mantissa is exact (below 2^22), which also
+  // makes the taps grow with the output coordinate; anything else (a scale of 1e9, an infinity)
+  // is a nonsensical descriptor.
+  {
+    const float sx_max = __fmaf_rn(d.scale_x, (float)(d.crop_x + max(cin1, 1)) + 0.5f, -0.5f);
+    const float sy_max = __fmaf_rn(d.scale_y, (float)(d.crop_y + max(rin1, 1)) + 0.5f, -0.5f);
+    if (!(sx_max < 4194304.0f) || !(sy_max < 4194304.0f)) {
+      report(B2_STATUS_BAD_GEOMETRY);
+      return;
+    }
+  }
 
   // Horizontal extent of source pixels touched by this image's output columns.
   int xlo = 0, xhi = 1;
@@ -603,7 +617,7 @@ int launch_resize(const b2_resize_args& a, cudaStream_t stream) {
                 aligned16(p.group_stride) && aligned16(p.row_stride) &&
                 (a.layout != B2_NCHW || aligned16(plane));
   p.status = a.status;
-  p.wait_limit = 1u << 20;
+  p.wait_limit = 1u << 19;  // about a second of sleeping polls
   p.debug_flags = a.debug_flags;
   // A staged span holds at most max_src_w + 1 bytes (interleaved chroma rows of an odd width)
   // plus up to 15 bytes of alignment head, rounded up to whole 16-byte segments.
