@@ -16,8 +16,17 @@
  *   - Work is enqueued on `stream` and the call returns without waiting unless
  *     the function says otherwise.  Inputs must stay alive until the stream has
  *     run past the call.
- *   - Re-entrant: no global mutable state; a call that takes `device` makes that
- *     device current for its duration and restores the caller's device.
+ *   - Re-entrant: no global mutable state a caller can observe; a call that takes
+ *     `device` makes that device current for its duration and restores the caller's
+ *     device.
+ *   - No source or destination pointer, pitch, stride or width needs any alignment.
+ *     The kernels read whole aligned segments, though: a source buffer must allow
+ *     reads of every aligned 16-byte segment that holds at least one byte of it
+ *     (b2_convert_resize) resp. every aligned 4-byte word (b2_convert_dense on rows
+ *     that are not 16-byte aligned).  Any allocation that starts and ends on such
+ *     boundaries -- cudaMalloc, every framework allocator -- satisfies this; a
+ *     sub-allocation whose last bytes share a 16-byte segment with an unmapped page
+ *     would not.  Nothing is ever written outside the destination elements.
  */
 #ifndef B2FRAMES_H_
 #define B2FRAMES_H_

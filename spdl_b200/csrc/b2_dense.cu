@@ -1,6 +1,6 @@
 // Dense colour conversion: every pixel of every frame, no resampling.
 //
-// Three kernel families.
+// Two kernel families.
 //   dense_vec_kernel   the fast path.  One thread owns a 2-row x PX-pixel block (PX = 16 bytes
 //                      of output per channel: 16 px for u8, 8 for bf16, 4 for fp32), so the two
 //                      rows share one chroma load, every global load is one 4/8/16-byte vector
@@ -9,12 +9,11 @@
 //                      instruction).  Interleaved output (48 bytes per thread per row) is staged
 //                      in shared memory by the warp and leaves as one bulk asynchronous copy
 //                      (cp.async.bulk shared->global) per row segment.
-//   dense_window_kernel rows that start on arbitrary (even) byte boundaries, e.g. packed frames
-//                      whose width is not a multiple of 16: one row per thread, the chunk grid of
-//                      each row slid so that the OUTPUT accesses stay 16-byte aligned, the input
-//                      realigned with 4-byte loads and funnel shifts.
-//   dense_shift_kernel the general case (odd addresses and pitches, any width): 4-byte accesses
-//                      on both sides, output realigned through shared memory.
+//   dense_any_kernel   rows, planes or destinations that are not 16-byte aligned (packed frames
+//                      of width 854 or 1366, crops, odd addresses): the same thread layout, the
+//                      source realigned with 4-byte loads and funnel shifts, the output laid out
+//                      in shared memory at the destination's offset modulo 16 so that its aligned
+//                      interior still leaves as one bulk copy per row segment.
 //
 // The kernels are HBM-bound: 1.5 bytes read and 3*sizeof(T) written per pixel.
 #include "b2_common.cuh"
@@ -357,46 +356,95 @@ __device__ __forceinline__ void convert_chunk(const ColorMat& m, const ScaleBias
   }
 }
 
-// ---- window path: rows on even byte boundaries -----------------------------------------------------
-// Packed batches whose width is not a multiple of 16 (854x480 video, crops) have rows that start
-// anywhere, which rules out the vector kernel's direct 16-byte accesses.  Here a thread owns PX
-// pixels of ONE row, and the chunk grid of every row is slid left by d pixels, d chosen per row
-// so that chunk boundaries fall on 16-byte boundaries of the DESTINATION row.  The output side is
-// then that of the vector kernel (16-byte stores, bulk copies for interleaved output; only the
-// first and last chunk of a row are ragged), and the alignment work moves to the source side,
-// where it is cheap: the 4-byte words that cover the chunk, funnel-shifted.  d must be even so
-// that a chunk starts on a chroma pair, which holds when the destination rows start on even
-// element pairs; rows 2r and 2r+1 get different d, so each thread loads its own chroma.
+// ---- any-alignment path ------------------------------------------------------------------------
+// Rows on arbitrary byte boundaries (packed frames whose width is not a multiple of 16: 854x480,
+// 1366x768; crops; surfaces at odd addresses), any width >= 2.  The thread layout is the vector
+// kernel's -- a warp owns 2 rows x 32*PX pixels, a lane 2 rows x PX pixels under one chroma row,
+// chunks counted from the start of the row so that a chunk starts on a chroma pair -- and the
+// alignment work sits at the two ends of it:
+//   in:   a lane reads the aligned 4-byte words that cover its bytes and funnel-shifts them into
+//         place (load_window);
+//   out:  the bytes a warp produces for one row (or one row of one plane) are contiguous in the
+//         destination.  The warp lays them out in shared memory at the destination's offset
+//         modulo 16 -- a lane shifts its words by the offset modulo 4, taking the spilled bytes
+//         of its left neighbour with one shuffle -- so that shared and global addresses are
+//         congruent; the 16-byte-aligned interior then leaves as ONE bulk asynchronous copy and
+//         the ragged ends (< 16 bytes each) as byte stores.
+constexpr int kAnyThreads = 128;
+constexpr int kAnyMinBlocks = 10;  // 40 warps per SM: the loads of a warp are all issued up front
+constexpr int kAnySegPad = 32;  // the 0..15-byte offset in front, one spilled word behind
 
-constexpr int kWindowThreads = 128;
+// One segment: lane l contributes SEGW words w (stream bytes [4*SEGW*l, 4*SEGW*(l+1))); the first
+// `nbytes` stream bytes go to global address g.  seg: this segment's staging area (16-byte
+// aligned, 4*SEGW*32 + kAnySegPad bytes).  Issues at most one bulk copy (not yet committed).
+template <int SEGW>
+__device__ __forceinline__ void stage_and_copy(unsigned char* seg, const uint32_t* w, uint8_t* g,
+                                               int nbytes, int lane) {
+  const uint32_t a = (uint32_t)((uintptr_t)g & 15), sh = a & 3;
+  unsigned char* base = seg + (a - sh) + lane * (4 * SEGW);  // 4-byte aligned
+  if (sh == 0) {
+    if (((a - sh) & 15) == 0 && SEGW % 4 == 0) {
+#pragma unroll
+      for (int i = 0; i < SEGW; i += 4)
+        *reinterpret_cast<uint4*>(base + 4 * i) = make_uint4(w[i], w[i + 1], w[i + 2], w[i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < SEGW; ++i) *reinterpret_cast<uint32_t*>(base + 4 * i) = w[i];
+    }
+  } else {
+    // shifted stream: word k holds the top `sh` bytes of stream word k-1 and the low bytes of k
+    uint32_t prev = __shfl_up_sync(0xffffffffu, w[SEGW - 1], 1);
+#pragma unroll
+    for (int i = 0; i < SEGW; ++i) {
+      *reinterpret_cast<uint32_t*>(base + 4 * i) = __funnelshift_l(prev, w[i], 8 * sh);
+      prev = w[i];
+    }
+    if (lane == 31) *reinterpret_cast<uint32_t*>(base + 4 * SEGW) = prev >> (32 - 8 * sh);
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncwarp();
+  const unsigned char* data = seg + a;  // stream byte j sits at data[j]; data + head is 16-aligned
+  int head = (int)((16 - a) & 15);
+  if (head > nbytes) head = nbytes;
+  const int body = (nbytes - head) & ~15;
+  const int tail0 = head + body;
+  if (lane < head) g[lane] = data[lane];
+  if (tail0 + lane < nbytes) g[tail0 + lane] = data[tail0 + lane];
+  if (lane == 0 && body > 0)
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(g + head),
+                 "r"(smem_addr(data + head)), "r"((uint32_t)body)
+                 : "memory");
+}
 
 template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE, int ARITH>
-__global__ void __launch_bounds__(kWindowThreads) dense_window_kernel(const DenseParams p) {
+__global__ void __launch_bounds__(kAnyThreads, kAnyMinBlocks) dense_any_kernel(const DenseParams p) {
   using T = typename OutT<DTYPE>::type;
   constexpr int ESZ = (int)sizeof(T);
   constexpr int PX = 16 / ESZ;
   constexpr int NW = PX / 4;
   constexpr int UVB = FMT == B2_SRC_NV12 ? PX : PX / 2;
   constexpr int UVW = (UVB + 3) / 4;
-  extern __shared__ __align__(128) unsigned char window_smem[];  // interleaved: 1536 B per warp
-  const int lane = threadIdx.x & 31;
+  constexpr int SEGW = LAYOUT == B2_NHWC ? 12 : 4;  // words a lane adds to a segment
+  constexpr int NSEG = LAYOUT == B2_NHWC ? 2 : 6;   // rows, or rows x planes
+  constexpr int SEGS = 4 * SEGW * 32 + kAnySegPad;  // bytes reserved per segment
+  extern __shared__ __align__(128) unsigned char any_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned char* wsm = any_smem + warp * (NSEG * SEGS);
 
-  const int row = blockIdx.y, n = blockIdx.z;
+  // warps are numbered through the frame: warp -> (row pair, block of 32*PX pixels in the row),
+  // so that rows narrower than a CTA leave no warp without work
+  const int n = blockIdx.z;
   const int we = p.width & ~1;  // a trailing odd column is left untouched
-  uint8_t* grow = reinterpret_cast<uint8_t*>(static_cast<T*>(p.dst) + (long long)n * p.dst_frame_stride +
-                                             (long long)row * p.dst_row_pitch);
-  // pixels to slide the chunk grid left so that chunks start on 16-byte boundaries of this row
-  const int a = (int)((uintptr_t)grow & 15);
-  int d;
-  if constexpr (LAYOUT == B2_NCHW) d = (a / ESZ) & (PX - 1);                // ESZ*d = a (mod 16)
-  else if constexpr (DTYPE == B2_U8) d = (11 * a) & 15;                      // 3d = a (mod 16)
-  else if constexpr (DTYPE == B2_BF16) d = (3 * (a >> 1)) & 7;               // 6d = a (mod 16)
-  else d = (3 * (a >> 2)) & 3;                                               // 12d = a (mod 16)
-  const int cx = blockIdx.x * blockDim.x + threadIdx.x;
-  const int x0 = cx * PX - d, wx0 = (cx - lane) * PX - d;
-  if (wx0 >= we) return;  // the whole warp lies past the row end
+  const int segs = (we + 32 * PX - 1) / (32 * PX);
+  const int wid = blockIdx.x * (kAnyThreads / 32) + warp;
+  const int rp = wid / segs;
+  if (2 * rp >= p.height) return;
+  const int wx0 = (wid - rp * segs) * 32 * PX;
+  const int x0 = wx0 + lane * PX;
 
-  uint32_t out[1][12];
+  uint32_t out[2][12];
+#pragma unroll
+  for (int i = 0; i < 12; ++i) out[0][i] = out[1][i] = 0u;
   if (x0 < we) {
     const uint8_t *yb, *ub, *vb = nullptr;
     if constexpr (TABLE) {
@@ -408,9 +456,11 @@ __global__ void __launch_bounds__(kWindowThreads) dense_window_kernel(const Dens
       ub = p.u + (long long)n * p.uv_frame_stride;
       if constexpr (FMT == B2_SRC_I420) vb = p.v + (long long)n * p.uv_frame_stride;
     }
-    uint32_t yw[1][NW], uw[UVW], vw[UVW];
-    load_window<PX>(yb + (size_t)row * (unsigned)p.y_pitch, x0, we, yw[0]);
-    const size_t uv_off = (size_t)(row >> 1) * (unsigned)p.uv_pitch;
+    uint32_t yw[2][NW], uw[UVW], vw[UVW];
+    const uint8_t* y0 = yb + (size_t)(2 * rp) * (unsigned)p.y_pitch;
+    load_window<PX>(y0, x0, we, yw[0]);
+    load_window<PX>(y0 + p.y_pitch, x0, we, yw[1]);
+    const size_t uv_off = (size_t)rp * (unsigned)p.uv_pitch;
     if constexpr (FMT == B2_SRC_NV12) {
       load_window<UVB>(ub + uv_off, x0, we, uw);
     } else {
@@ -421,213 +471,27 @@ __global__ void __launch_bounds__(kWindowThreads) dense_window_kernel(const Dens
     convert_chunk<FMT, LAYOUT, DTYPE, BGR, ARITH>(p.mat, p.sb, yw, uw, vw, out);
   }
 
-  if constexpr (LAYOUT == B2_NCHW) {
-    if (x0 >= we) return;
-    if (x0 >= 0 && x0 + PX <= we) {
-#pragma unroll
-      for (int s = 0; s < 3; ++s)
-        __stcs(reinterpret_cast<uint4*>(grow + (s * p.dst_plane_stride + x0) * (long long)ESZ),
-               make_uint4(out[0][4 * s], out[0][4 * s + 1], out[0][4 * s + 2], out[0][4 * s + 3]));
-    } else {  // first or last chunk of the row: element by element
-#pragma unroll
-      for (int s = 0; s < 3; ++s) {
-        T* q = reinterpret_cast<T*>(grow) + s * p.dst_plane_stride + x0;
-#pragma unroll
-        for (int k = 0; k < PX; ++k) {
-          if (x0 + k < 0 || x0 + k >= we) continue;
-          const uint32_t word = out[0][4 * s + k * ESZ / 4];
-          if constexpr (ESZ == 1) reinterpret_cast<uint8_t*>(q)[k] = (uint8_t)(word >> (8 * (k & 3)));
-          else if constexpr (ESZ == 2)
-            reinterpret_cast<uint16_t*>(q)[k] = (uint16_t)(word >> (16 * (k & 1)));
-          else reinterpret_cast<uint32_t*>(q)[k] = word;
-        }
-      }
-    }
-  } else {
-    unsigned char* seg = window_smem + (threadIdx.x >> 5) * 1536;
-    if (x0 < we) {
-#pragma unroll
-      for (int i = 0; i < 3; ++i)
-        *reinterpret_cast<uint4*>(seg + lane * 48 + i * 16) =
-            make_uint4(out[0][4 * i], out[0][4 * i + 1], out[0][4 * i + 2], out[0][4 * i + 3]);
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncwarp();
-    // The warp's 1536-byte segment starts 16-byte aligned at gseg; bytes [s0, s1) of it lie in
-    // the row.  Whole 16-byte pieces leave as one bulk copy, the ragged ends byte by byte.
-    const int seg_off = wx0 * (3 * ESZ);  // rows are shorter than 2^31 bytes
-    uint8_t* gseg = grow + seg_off;
-    const int left = we * (3 * ESZ) - seg_off;
-    int b0 = 0, b1 = 1536;
-    if (seg_off < 0 || left < 1536) {  // first or last segment of the row
-      const int s0 = seg_off < 0 ? -seg_off : 0;
-      const int s1 = left < 1536 ? left : 1536;
-      b0 = (s0 + 15) & ~15;
-      b1 = s1 & ~15;
-      const int head_end = b1 > b0 ? b0 : s1;
-      if (s0 + lane < head_end) gseg[s0 + lane] = seg[s0 + lane];
-      if (b1 > b0 && b1 + lane < s1) gseg[b1 + lane] = seg[b1 + lane];
-    }
-    if (lane == 0 && b1 > b0) {
-      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gseg + b0),
-                   "r"(smem_addr(seg + b0)), "r"((uint32_t)(b1 - b0))
-                   : "memory");
-      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-      // the staging buffer must outlive the engine's reads of it
-      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-    }
-  }
-}
-
-// ---- shift path: any alignment, no block-wide staging --------------------------------------------
-// For rows on arbitrary byte boundaries.  A warp owns the same 2-row x 32*PX-pixel block as in the
-// vector kernel, but its lanes take the luma words of a row in turn (lane l owns words l, l+32,
-// ...), so every access is a coalesced 4-byte access and a row that starts between two words
-// costs one funnel shift per word, with no dependence on where the row starts.  The output
-// segments of the warp are assembled in shared memory and leave as 4-byte stores shifted the
-// other way, with byte stores at the ragged ends.  Needs only __syncwarp.
-
-// The 32-bit word at any address p (its first byte is valid; bytes at or past `end` are not
-// needed).  Reads only aligned words that hold at least one valid byte.
-__device__ __forceinline__ uint32_t ldg_word_any(const uint8_t* p, const uint8_t* end) {
-  const int a = (int)((uintptr_t)p & 3);
-  const uint8_t* base = p - a;
-  const uint32_t lo = __ldg(reinterpret_cast<const uint32_t*>(base));
-  uint32_t hi = 0u;
-  if (a != 0 && base + 4 < end) hi = __ldg(reinterpret_cast<const uint32_t*>(base + 4));
-  return __funnelshift_r(lo, hi, a * 8);
-}
-
-template <int N>
-__device__ __forceinline__ void sts_words(unsigned char* q, const uint32_t* w) {
-  if constexpr (N % 4 == 0) {
-#pragma unroll
-    for (int i = 0; i < N; i += 4)
-      *reinterpret_cast<uint4*>(q + 4 * i) = make_uint4(w[i], w[i + 1], w[i + 2], w[i + 3]);
-  } else if constexpr (N % 2 == 0) {
-#pragma unroll
-    for (int i = 0; i < N; i += 2) *reinterpret_cast<uint2*>(q + 4 * i) = make_uint2(w[i], w[i + 1]);
-  } else {
-#pragma unroll
-    for (int i = 0; i < N; ++i) *reinterpret_cast<uint32_t*>(q + 4 * i) = w[i];
-  }
-}
-
-// g[0..n) = s[0..n) by one warp for any alignment of g; s is 4-byte aligned shared memory,
-// readable up to n + 4 bytes; n <= MAXB.
-template <int MAXB>
-__device__ __forceinline__ void warp_store(uint8_t* g, const unsigned char* s, int n, int lane) {
-  int head = (int)((4 - ((uintptr_t)g & 3)) & 3);
-  if (head > n) head = n;
-  const int nw = (n - head) >> 2;
-  const int tail0 = head + (nw << 2);
-  if (lane < head) g[lane] = s[lane];
-  if (tail0 + lane < n) g[tail0 + lane] = s[tail0 + lane];
-  const uint32_t* sw = reinterpret_cast<const uint32_t*>(s);
-  uint32_t* gw = reinterpret_cast<uint32_t*>(g + head);
-  const int bs = head * 8;
-  if (bs == 0) {
-#pragma unroll
-    for (int i = 0; i < MAXB / 128; ++i) {
-      const int m = lane + 32 * i;
-      if (m < nw) __stcs(gw + m, sw[m]);
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < MAXB / 128; ++i) {
-      const int m = lane + 32 * i;
-      if (m < nw) __stcs(gw + m, __funnelshift_r(sw[m], sw[m + 1], bs));
-    }
-  }
-}
-
-constexpr int kShiftThreads = 128;
-constexpr int kShiftWarpSmem = 2 * 1536 + 16;  // two interleaved or six planar row segments
-
-template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE, int ARITH>
-__global__ void __launch_bounds__(kShiftThreads) dense_shift_kernel(const DenseParams p) {
-  using T = typename OutT<DTYPE>::type;
-  constexpr int ESZ = (int)sizeof(T);
-  constexpr int PX = 16 / ESZ;
-  constexpr int NW = PX / 4;
-  constexpr int UVB = FMT == B2_SRC_NV12 ? PX : PX / 2;
-  constexpr int UVW = (UVB + 3) / 4;
-  constexpr int KW = 3 * ESZ;  // interleaved output words per luma word
-  constexpr int CW = ESZ;      // planar output words per channel and luma word
-  extern __shared__ __align__(128) unsigned char shift_smem[];
-  const int lane = threadIdx.x & 31;
-  unsigned char* wsm = shift_smem + (threadIdx.x >> 5) * kShiftWarpSmem;
-
-  const int rp = blockIdx.y, n = blockIdx.z;
-  const int we = p.width & ~1;  // a trailing odd column is left untouched
-  const int wx0 = (blockIdx.x * (kShiftThreads / 32) + (threadIdx.x >> 5)) * 32 * PX;
-  if (wx0 >= we) return;  // the whole warp lies past the row end
-
-  const uint8_t *yb, *ub, *vb = nullptr;
-  if constexpr (TABLE) {
-    yb = static_cast<const uint8_t*>(p.y_table[n]);
-    ub = static_cast<const uint8_t*>(p.u_table[n]);
-    if constexpr (FMT == B2_SRC_I420) vb = static_cast<const uint8_t*>(p.v_table[n]);
-  } else {
-    yb = p.y + (long long)n * p.y_frame_stride;
-    ub = p.u + (long long)n * p.uv_frame_stride;
-    if constexpr (FMT == B2_SRC_I420) vb = p.v + (long long)n * p.uv_frame_stride;
-  }
-  const uint8_t* y0 = yb + (size_t)(2 * rp) * (unsigned)p.y_pitch;
-  const uint8_t* y1 = y0 + p.y_pitch;
-  const uint8_t* u0 = ub + (size_t)rp * (unsigned)p.uv_pitch;
-  const uint8_t* v0 = FMT == B2_SRC_I420 ? vb + (size_t)rp * (unsigned)p.uv_pitch : nullptr;
-
-  uint32_t yw[2][NW], uw[UVW], vw[UVW];
-#pragma unroll
-  for (int i = 0; i < UVW; ++i) uw[i] = vw[i] = 0u;
-#pragma unroll
-  for (int j = 0; j < NW; ++j) {
-    const int x = wx0 + 4 * (lane + 32 * j);  // first pixel of this lane's luma word j
-    yw[0][j] = yw[1][j] = 0u;
-    if (x < we) {
-      yw[0][j] = ldg_word_any(y0 + x, y0 + we);
-      yw[1][j] = ldg_word_any(y1 + x, y1 + we);
-      if constexpr (FMT == B2_SRC_NV12) {
-        uw[j] = ldg_word_any(u0 + x, u0 + we);
-      } else {  // two bytes per plane under four pixels
-        uw[j >> 1] |= (ldg_word_any(u0 + x / 2, u0 + we / 2) & 0xffffu) << (16 * (j & 1));
-        vw[j >> 1] |= (ldg_word_any(v0 + x / 2, v0 + we / 2) & 0xffffu) << (16 * (j & 1));
-      }
-    }
-  }
-  (void)vw;
-  uint32_t out[2][12];
-  convert_chunk<FMT, LAYOUT, DTYPE, BGR, ARITH>(p.mat, p.sb, yw, uw, vw, out);
-#pragma unroll
-  for (int r = 0; r < 2; ++r)
-#pragma unroll
-    for (int j = 0; j < NW; ++j) {
-      const int word = lane + 32 * j;
-      if constexpr (LAYOUT == B2_NHWC) {
-        sts_words<KW>(wsm + r * 1536 + word * (KW * 4), &out[r][KW * j]);
-      } else {
-#pragma unroll
-        for (int s = 0; s < 3; ++s)
-          sts_words<CW>(wsm + (r * 3 + s) * 512 + word * (CW * 4), &out[r][4 * s + CW * j]);
-      }
-    }
-  __syncwarp();
-
-  const int px = we - wx0 < 32 * PX ? we - wx0 : 32 * PX;
+  const int px = we - wx0 < 32 * PX ? we - wx0 : 32 * PX;  // pixels of the warp's block in the row
   uint8_t* dst = reinterpret_cast<uint8_t*>(static_cast<T*>(p.dst) + (long long)n * p.dst_frame_stride);
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const long long row = 2 * rp + r;
+  for (int sidx = 0; sidx < NSEG; ++sidx) {
     if constexpr (LAYOUT == B2_NHWC) {
-      warp_store<1536>(dst + (row * p.dst_row_pitch + (long long)wx0 * 3) * ESZ, wsm + r * 1536,
-                       px * 3 * ESZ, lane);
+      const long long row = 2 * rp + sidx;
+      stage_and_copy<SEGW>(wsm + sidx * SEGS, &out[sidx][0],
+                           dst + (row * p.dst_row_pitch + (long long)wx0 * 3) * ESZ, px * 3 * ESZ,
+                           lane);
     } else {
-#pragma unroll
-      for (int s = 0; s < 3; ++s)
-        warp_store<512>(dst + (s * p.dst_plane_stride + row * p.dst_row_pitch + wx0) * ESZ,
-                        wsm + (r * 3 + s) * 512, px * ESZ, lane);
+      const int r = sidx / 3, slot = sidx % 3;
+      const long long row = 2 * rp + r;
+      stage_and_copy<SEGW>(wsm + sidx * SEGS, &out[r][4 * slot],
+                           dst + (slot * p.dst_plane_stride + row * p.dst_row_pitch + wx0) * ESZ,
+                           px * ESZ, lane);
     }
+  }
+  if (lane == 0) {
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    // the staging buffer must outlive the engine's reads of it
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
   }
 }
 
@@ -638,13 +502,6 @@ int launch_t(const DenseLaunch& L, const DenseParams& p, bool vec, cudaStream_t 
   using T = typename OutT<DTYPE>::type;
   constexpr int PX = 16 / (int)sizeof(T);
   const int He = L.height & ~1;
-  // The window kernel needs destination rows that start on even element pairs (so that its chunk
-  // grid starts on a chroma pair) and, for planar output, planes that are equally aligned.
-  constexpr int kPair = 2 * (int)sizeof(T);
-  bool window = mult((long long)(uintptr_t)p.dst, kPair) &&
-                mult((long long)p.dst_row_pitch * (long long)sizeof(T), kPair) &&
-                mult(p.dst_frame_stride * (long long)sizeof(T), kPair);
-  if (LAYOUT == B2_NCHW) window = window && mult(p.dst_plane_stride * (long long)sizeof(T), 16);
   // gridDim.z is limited to 65535 frames per launch
   for (int n0 = 0; n0 < L.num_frames; n0 += 65535) {
     const int nn = L.num_frames - n0 < 65535 ? L.num_frames - n0 : 65535;
@@ -667,18 +524,14 @@ int launch_t(const DenseLaunch& L, const DenseParams& p, bool vec, cudaStream_t 
       dim3 block(bx, by), grid((chunks + bx - 1) / bx, (He / 2 + by - 1) / by, nn);
       const size_t smem = LAYOUT == B2_NHWC ? (size_t)(kDenseThreads / 32) * 2 * 32 * 48 : 0;
       dense_vec_kernel<FMT, LAYOUT, DTYPE, BGR, TABLE, ARITH><<<grid, block, smem, stream>>>(q);
-    } else if (window) {
-      if (He < 2) continue;
-      const int chunks = ((L.width & ~1) + 2 * PX - 2) / PX;  // the grid slides by up to PX-1 pixels
-      dim3 grid((chunks + kWindowThreads - 1) / kWindowThreads, He, nn);
-      const size_t smem = LAYOUT == B2_NHWC ? (size_t)(kWindowThreads / 32) * 1536 : 0;
-      dense_window_kernel<FMT, LAYOUT, DTYPE, BGR, TABLE, ARITH><<<grid, kWindowThreads, smem, stream>>>(q);
     } else {
       if (He < 2) continue;
-      const int per_cta = kShiftThreads * PX;  // pixels of a row per CTA
-      dim3 grid(((L.width & ~1) + per_cta - 1) / per_cta, He / 2, nn);
-      dense_shift_kernel<FMT, LAYOUT, DTYPE, BGR, TABLE, ARITH>
-          <<<grid, kShiftThreads, (kShiftThreads / 32) * kShiftWarpSmem, stream>>>(q);
+      constexpr int kSegW = LAYOUT == B2_NHWC ? 12 : 4, kSegN = LAYOUT == B2_NHWC ? 2 : 6;
+      const size_t smem = (size_t)(kAnyThreads / 32) * kSegN * (4 * kSegW * 32 + kAnySegPad);
+      const long long segs = ((L.width & ~1) + 32 * PX - 1) / (32 * PX);  // warps per row pair
+      const long long warps = segs * (He / 2);
+      dim3 grid((unsigned)((warps + kAnyThreads / 32 - 1) / (kAnyThreads / 32)), 1, nn);
+      dense_any_kernel<FMT, LAYOUT, DTYPE, BGR, TABLE, ARITH><<<grid, kAnyThreads, smem, stream>>>(q);
     }
     B2_CUDA(cudaPeekAtLastError(), "launch of the dense conversion kernel failed");
   }

@@ -651,6 +651,8 @@ class FrameBatcher:
             device_config
         self._pending: list[tuple[int, int]] = []
         self._queue: list[CUDABuffer] = []
+        self._tables = None  # pinned ring for the pointer/pitch tables, made on first use
+        self._slot = 0
 
     def empty(self) -> bool:
         return not self._queue
@@ -671,12 +673,36 @@ class FrameBatcher:
             raise RuntimeError("There is no buffer available.")
         return self._queue.pop(0)
 
+    _TABLE_SLOTS = 8  # pinned copies of the pointer/pitch table in flight at most
+
+    def _table_slot(self) -> tuple[int, np.ndarray]:
+        """Host address and int64 view of the next pinned table slot.  The slots form a ring; the
+        stream is synchronised once per lap, so a slot is never rewritten while its upload may
+        still be reading it, and a steady stream of batches costs one wait per eight."""
+        from ._types import CPUStorage
+
+        if self._tables is None:
+            self._tables = CPUStorage(self._TABLE_SLOTS * 16 * self._n, pin_memory=True)
+            self._slot = 0
+        if self._slot == self._TABLE_SLOTS:
+            synchronize_stream(self._cfg)
+            self._slot = 0
+        off = self._slot * 16 * self._n
+        self._slot += 1
+        view = self._tables.as_array()[off:off + 16 * self._n].view(np.int64)
+        return self._tables.data_ptr + off, view
+
     def _emit(self) -> None:
         k = len(self._pending)
         h2 = self._h + self._h // 2
         out = cuda_buffer((k, h2, self._w), self._cfg)
-        table = np.array([p for p, _ in self._pending] + [q for _, q in self._pending], np.int64)
-        dtab = transfer_buffer(table, device_config=self._cfg)
+        host_ptr, table = self._table_slot()
+        table[:k] = [p for p, _ in self._pending]
+        table[k:2 * k] = [q for _, q in self._pending]
+        dtab = cuda_buffer((2 * k,), self._cfg, "i", 8)
+        # asynchronous upload from pinned memory, then the gather on the same stream: no host wait
+        _lib.check(_lib.lib().b2_transfer_h2d_async(dtab.data_ptr, host_ptr, 16 * k,
+                                                    self._cfg.device_index, self._cfg.stream))
         _lib.check(_lib.lib().b2_gather_surfaces(
             dtab.data_ptr, dtab.data_ptr + 8 * k, k, self._w, self._h, out.data_ptr,
             self._cfg.device_index, self._cfg.stream))

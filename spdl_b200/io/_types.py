@@ -193,21 +193,30 @@ class CUDABuffer:
                 pass
 
 
-def _default_allocator(device: int) -> Allocator:
+_PSEUDO_STREAMS = (0, 1, 2)  # default, legacy and per-thread stream handles
+
+
+def _default_allocator(device: int, stream: int) -> Allocator:
     """Allocator used when the config carries none.
 
     The reference calls ``cudaMalloc``/``cudaFree`` per buffer
-    (``src/libspdl/cuda/storage.cpp:44-58``).  When torch has initialised CUDA this uses its
-    caching allocator instead, so a steady-state call allocates without touching the driver;
-    otherwise it is the library's ``cudaMalloc`` wrapper.
+    (``src/libspdl/cuda/storage.cpp:44-58``); ``cudaFree`` waits for the device, which is what
+    makes it safe to free a buffer whose kernel is still queued.  That pair is kept for the
+    pseudo stream handles ``0``, ``1`` and ``2``: they name a different real stream in every
+    thread, so a caching allocator keyed by the handle could hand a block freed in one thread to
+    another thread's stream while the first thread's kernel still runs
+    (``docs/source/io/pytorch_cuda_race_condition.rst`` of the reference describes that race).
+    For a real stream handle, and when torch has initialised CUDA, torch's caching allocator is
+    used instead, so a steady-state call allocates without touching the driver.
     """
-    try:
-        import torch
+    if stream not in _PSEUDO_STREAMS:
+        try:
+            import torch
 
-        if torch.cuda.is_available():
-            return (torch.cuda.caching_allocator_alloc, torch.cuda.caching_allocator_delete)
-    except Exception:
-        pass
+            if torch.cuda.is_available():
+                return (torch.cuda.caching_allocator_alloc, torch.cuda.caching_allocator_delete)
+        except Exception:
+            pass
 
     def alloc(size: int, dev: int, stream: int) -> int:
         p = ctypes.c_void_p()
@@ -232,7 +241,7 @@ def cuda_buffer(shape: Sequence[int], cfg: CUDAConfig, elem_class: str = "u",
     if nbytes == 0:
         raise RuntimeError("`size` must be greater than 0.")
     alloc, free = cfg.allocator if cfg.allocator is not None else _default_allocator(
-        cfg.device_index)
+        cfg.device_index, cfg.stream)
     ptr = int(alloc(nbytes, cfg.device_index, cfg.stream))
     if ptr == 0:
         raise RuntimeError("Failed to allocate CUDA memory")
