@@ -638,7 +638,7 @@ int launch_resize(const b2_resize_args& a, cudaStream_t stream) {
   p.span_cap = (int)span;
   // Tiles per CTA: enough to spread the per-image work of a CTA over many rows, few enough to
   // leave every SM several CTAs' worth of an image batch (148 SMs x 8 resident CTAs).
-  p.tiles = 4;
+  p.tiles = 8;
   while (p.tiles > 1 && (long long)a.num_images * ((a.out_h + p.rows * p.tiles - 1) /
                                                     (p.rows * p.tiles)) < 4 * 148 * 8)
     p.tiles >>= 1;
