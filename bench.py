@@ -770,6 +770,50 @@ def run_resize_workload(args) -> None:
         if not equal:
             raise SystemExit("the ranks' outputs differ from the whole batch converted on one GPU")
 
+    # -- end to end for the uniform-size workloads: decoded frames in pageable host memory (as a
+    #    decoder leaves them) -> FrameStage (stage into pinned memory, upload, fused kernel) ->
+    #    checksum of the result on the host.  Whole frames against row-sparse uploads: only the
+    #    source rows the geometry reads are staged and sent.
+    e2e = None
+    if wl in ("c3", "c4"):
+        from concurrent.futures import ThreadPoolExecutor
+
+        n_e2e = min(n, 16 if wl == "c3" else 128)  # frames per end-to-end step
+        h2 = h * 3 // 2
+        host_frames = [data[:n_e2e * h2 * w].reshape(n_e2e, h2, w).cpu().numpy() for _ in range(2)]
+        stage_kw = dict(src_format="nv12", dtype=spec["dtype"], coeff=spec["coeff"],
+                        mean=mean if spec["norm"] else None, std=std if spec["norm"] else None,
+                        device_index=info.local_rank, **geom)
+        e2e = {"frames_per_step": n_e2e, "unit": "frames/s",
+               "note": "pageable host frames -> FrameStage (pinned staging, H2D, fused kernel) -> "
+                       "frame_checksum -> host; two worker threads on private streams, host-timed"}
+        frame_in = h2 * w
+        for label, sparse in (("whole_frames", False), ("sparse_rows", True)):
+            stg = io.FrameStage(sparse_upload=sparse, **stage_kw)
+
+            def e2e_step(i, stg=stg):
+                t = stg(host_frames[i % 2])
+                cfg_t = stg._state()["cfg"]
+                return io.frame_checksum(t.view(torch.uint8).reshape(n_e2e, -1),
+                                         device_config=cfg_t)
+
+            with ThreadPoolExecutor(2) as pool:
+                list(pool.map(e2e_step, range(4)))
+                barrier()
+                reps = 12
+                t0 = time.perf_counter()
+                last = list(pool.map(e2e_step, range(reps)))[-1]
+                dt = (time.perf_counter() - t0) / reps
+            if sparse:
+                lm, cm = io.touched_rows(descs[0], src_format="nv12", out_h=out[1])
+                sent = int(((lm >= 0).sum() + (cm >= 0).sum()) * w)
+            else:
+                sent = frame_in
+            e2e[label] = {"value": n_e2e / dt, "h2d_bytes_per_step": sent * n_e2e,
+                          "d2h_bytes_per_step": 8 * n_e2e, "ms_per_step": 1e3 * dt,
+                          "checksum_of_frame_0": int(last[0])}
+        assert e2e["whole_frames"]["checksum_of_frame_0"] == e2e["sparse_rows"]["checksum_of_frame_0"]
+
     per_rank = gather_stats([ms, float(exact), float(rows), float(out_bytes), float(n)], device=dev)
     if info.rank == 0:
         ms_max = max(r[0] for r in per_rank)
@@ -790,6 +834,7 @@ def run_resize_workload(args) -> None:
                                    "its own GPU's memory; no data-path collective"},
             "ms_per_rank": [r[0] for r in per_rank],
             "shards_equal_whole": equal,
+            "e2e": e2e,
             "gpu_launches": K,
             "roofline": {"bound": "hbm", "unit": "GB/s", "peak": peak, "peak_source": peak_kind,
                          "achieved": per_gpu(t_exact + t_out),

@@ -217,13 +217,26 @@ typedef struct b2_resize_args {
    * it after the stream has run.  The call itself still returns B2_OK: the host cannot see the
    * descriptor table, which lives in device memory. */
   int32_t* status;
+  /* Row-sparse sources (optional; one pair of maps for the whole call, so for batches whose
+   * images share one geometry, e.g. video frames).  A caller that uploads only the source rows a
+   * geometry touches stores them back to back and says where each row went: with luma_row_map
+   * non-null, row r of the first plane (of every plane for RGB sources) is read from row
+   * luma_row_map[r] of the plane the descriptor points to, and row r of the half-height planes of
+   * a YUV source from row chroma_row_map[r].  Device arrays of int32; entries of rows the geometry
+   * does not touch are never read.  b2_touched_rows computes the maps.  The reference uploads
+   * whole frames (src/libspdl/cuda/transfer.cpp:37-66); a 4K frame resized to 224x224 touches a
+   * quarter of its rows. */
+  const int32_t* luma_row_map;
+  const int32_t* chroma_row_map;
 } b2_resize_args;
 
 enum b2_resize_status_bits {
   B2_STATUS_IMAGE_TOO_WIDE = 1, /* a descriptor needs more staging than max_src_w provides:
                                  * the image was skipped                                     */
   B2_STATUS_WAIT_EXPIRED = 2,   /* a bounded wait for staged rows ran out: the tile was skipped */
-  B2_STATUS_BAD_GEOMETRY = 4    /* src_w/src_h < 1 or a non-positive / non-finite scale: skipped */
+  B2_STATUS_BAD_GEOMETRY = 4    /* src_w/src_h < 1, a non-positive / non-finite scale or source
+                                 * coordinates beyond 2^22: skipped; or a row map that marks a
+                                 * row the geometry reads as absent (row 0 is read instead)   */
 };
 /* B2_DEBUG_EXPIRE_WAIT: after its rows have arrived, every tile also waits (bounded, a few
  * polls) on a barrier that nothing completes, so that the give-up path can be tested without
@@ -231,6 +244,26 @@ enum b2_resize_status_bits {
 enum b2_debug_flags { B2_DEBUG_EXPIRE_WAIT = 1 };
 
 B2_API int b2_convert_resize(const b2_resize_args* args, void* stream);
+
+/* Host helper (no CUDA call): the source rows that the vertical geometry of `desc` touches when
+ * out_h output rows are produced, computed with the arithmetic of the kernel.  luma_map receives
+ * desc->src_h entries, chroma_map (YUV source formats only, may be null otherwise)
+ * (desc->src_h + 1) / 2: the index of the row among the touched rows of its plane, in order, or -1
+ * for a row that is never read.  n_luma / n_chroma receive the numbers of touched rows.  Together
+ * with b2_resize_args.luma_row_map this lets a caller upload a fraction of each frame.  No
+ * counterpart in the reference. */
+B2_API int b2_touched_rows(const b2_image_desc* desc, int src_format, int out_h, int32_t* luma_map,
+                    int32_t* chroma_map, int32_t* n_luma, int32_t* n_chroma);
+
+/* Host helper (no CUDA call): packs selected rows of a batch of equally laid out HOST planes.
+ * For every frame f < num_frames and i < num_rows, row_bytes bytes are copied from
+ * src + f * src_frame_stride + rows[i] * src_pitch to dst + f * dst_frame_stride + i * row_bytes.
+ * It takes the place of the whole-frame copy with which the reference batches decoded frames
+ * (src/libspdl/core/detail/ffmpeg/conversion.cpp:171-216) when only the touched rows are to be
+ * uploaded; dst is typically page-locked. */
+B2_API int b2_copy_rows(void* dst, int64_t dst_frame_stride, const void* src, int64_t src_frame_stride,
+                 int64_t src_pitch, const int32_t* rows, int num_rows, int64_t row_bytes,
+                 int num_frames);
 
 /* ------------------------------------------------------------------------------------------
  * Frame batching.

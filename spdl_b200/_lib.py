@@ -27,7 +27,7 @@ DEBUG_EXPIRE_WAIT = 1
 EXPORTS = (
     "b2_last_error", "b2_abi_version", "b2_init", "b2_device_count", "b2_stream_synchronize",
     "b2_nv12_to_planar_rgb", "b2_nv12_to_planar_bgr", "b2_convert_dense", "b2_convert_resize",
-    "b2_gather_surfaces", "b2_transfer_h2d", "b2_transfer_h2d_async", "b2_transfer_d2h",
+    "b2_touched_rows", "b2_copy_rows", "b2_gather_surfaces", "b2_transfer_h2d", "b2_transfer_h2d_async", "b2_transfer_d2h",
     "b2_alloc_pinned", "b2_free_pinned", "b2_device_alloc", "b2_device_free", "b2_frame_checksum",
 )
 
@@ -72,6 +72,7 @@ class ResizeArgs(Structure):
         ("dst_plane_stride", c_int64), ("dst_group_stride", c_int64),
         ("pad_value", c_float * 3), ("debug_flags", c_int32),
         ("status", c_void_p),
+        ("luma_row_map", c_void_p), ("chroma_row_map", c_void_p),
     ]
 
 
@@ -91,6 +92,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.b2_nv12_to_planar_bgr.argtypes = planar
     lib.b2_convert_dense.argtypes = [POINTER(DenseArgs), c_void_p]
     lib.b2_convert_resize.argtypes = [POINTER(ResizeArgs), c_void_p]
+    lib.b2_touched_rows.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, POINTER(c_int32),
+                                    POINTER(c_int32)]
+    lib.b2_copy_rows.argtypes = [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int,
+                                 c_int64, c_int]
     lib.b2_gather_surfaces.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int,
                                        c_void_p]
     lib.b2_transfer_h2d.argtypes = [c_void_p, c_void_p, c_size_t, c_int, c_int, c_void_p]

@@ -1,4 +1,5 @@
 // extern "C" surface of libb2frames.so: argument validation, device selection, error messages.
+#include <cmath>
 #include <cstdarg>
 #include <cstddef>
 #include <cstdio>
@@ -305,12 +306,75 @@ B2_API int b2_convert_resize(const b2_resize_args* args, void* stream) {
   if (a->frames_per_group < 0 || (a->frames_per_group > 1 && a->dst_group_stride <= 0))
     return fail(B2_ERR_INVALID, "frames_per_group %d needs a positive dst_group_stride (%lld)",
                 a->frames_per_group, (long long)a->dst_group_stride);
+  const bool yuv_src = a->src_format == B2_SRC_NV12 || a->src_format == B2_SRC_I420;
+  if ((a->luma_row_map == nullptr) != (a->chroma_row_map == nullptr) && yuv_src)
+    return fail(B2_ERR_INVALID, "luma_row_map and chroma_row_map go together for YUV sources");
+  if (a->chroma_row_map != nullptr && a->luma_row_map == nullptr)
+    return fail(B2_ERR_INVALID, "chroma_row_map given without luma_row_map");
   for (int i = 0; i < 3; ++i)
     if (!(a->pad_value[i] >= 0.0f && a->pad_value[i] <= 255.0f))
       return fail(B2_ERR_INVALID, "pad_value[%d] = %g is outside 0..255", i, a->pad_value[i]);
   DeviceGuard g(a->device);
   B2_CUDA(g.status(), "selecting the device failed");
   return launch_resize(*a, static_cast<cudaStream_t>(stream));
+}
+
+B2_API int b2_touched_rows(const b2_image_desc* d, int src_format, int out_h, int32_t* luma_map,
+                    int32_t* chroma_map, int32_t* n_luma, int32_t* n_chroma) {
+  clear_error();
+  if (!d || !luma_map || !n_luma) return fail(B2_ERR_INVALID, "null pointer argument");
+  if (!valid_enum(src_format, 3)) return fail(B2_ERR_INVALID, "unknown src_format (%d)", src_format);
+  const bool yuv = src_format == B2_SRC_NV12 || src_format == B2_SRC_I420;
+  if (yuv && (!chroma_map || !n_chroma))
+    return fail(B2_ERR_INVALID, "a YUV source needs chroma_map and n_chroma");
+  if (d->src_w < 1 || d->src_h < 1 || !(d->scale_y > 0.0f) || out_h < 0)
+    return fail(B2_ERR_INVALID, "the descriptor has an empty source or a non-positive scale");
+  const int ch = (d->src_h + 1) / 2;
+  for (int r = 0; r < d->src_h; ++r) luma_map[r] = -1;
+  if (yuv)
+    for (int r = 0; r < ch; ++r) chroma_map[r] = -1;
+  for (int oy = 0; oy < out_h; ++oy) {
+    const int gy = d->crop_y + oy;
+    if (d->resized_h > 0 && (gy < 0 || gy >= d->resized_h)) continue;  // a row of padding
+    // the kernel's axis_of: fma, clamp at zero, truncate, clamp at the last row
+    float s = fmaf(d->scale_y, (float)gy + 0.5f, -0.5f);
+    if (!(s > 0.0f)) s = 0.0f;
+    if (!(s < 4194304.0f)) return fail(B2_ERR_INVALID, "source coordinates beyond 2^22");
+    int y0 = (int)s;
+    if (y0 > d->src_h - 1) y0 = d->src_h - 1;
+    const int y1 = y0 + 1 < d->src_h ? y0 + 1 : d->src_h - 1;
+    luma_map[y0] = luma_map[y1] = 0;
+    if (yuv) chroma_map[y0 >> 1] = chroma_map[y1 >> 1] = 0;
+  }
+  int nl = 0, nc = 0;
+  for (int r = 0; r < d->src_h; ++r)
+    if (luma_map[r] == 0) luma_map[r] = nl++;
+  if (yuv)
+    for (int r = 0; r < ch; ++r)
+      if (chroma_map[r] == 0) chroma_map[r] = nc++;
+  *n_luma = nl;
+  if (n_chroma) *n_chroma = nc;
+  return B2_OK;
+}
+
+B2_API int b2_copy_rows(void* dst, int64_t dst_frame_stride, const void* src, int64_t src_frame_stride,
+                 int64_t src_pitch, const int32_t* rows, int num_rows, int64_t row_bytes,
+                 int num_frames) {
+  clear_error();
+  if (num_rows < 0 || num_frames < 0 || row_bytes < 0)
+    return fail(B2_ERR_INVALID, "negative size: num_rows %d, num_frames %d, row_bytes %lld", num_rows,
+                num_frames, (long long)row_bytes);
+  if (num_rows == 0 || num_frames == 0 || row_bytes == 0) return B2_OK;
+  if (!dst || !src || !rows) return fail(B2_ERR_INVALID, "null pointer argument");
+  for (int i = 0; i < num_rows; ++i)
+    if (rows[i] < 0) return fail(B2_ERR_INVALID, "rows[%d] = %d is negative", i, rows[i]);
+  for (int f = 0; f < num_frames; ++f) {
+    char* d = static_cast<char*>(dst) + (long long)f * dst_frame_stride;
+    const char* s0 = static_cast<const char*>(src) + (long long)f * src_frame_stride;
+    for (int i = 0; i < num_rows; ++i)
+      memcpy(d + (long long)i * row_bytes, s0 + (long long)rows[i] * src_pitch, (size_t)row_bytes);
+  }
+  return B2_OK;
 }
 
 B2_API int b2_gather_surfaces(const void* const* surfaces, const int64_t* pitches, int num_frames,

@@ -53,6 +53,8 @@ struct ResizeParams {
   int vec_store;                         // 1: whole groups of four pixels may use vector stores
   int rows;                              // output rows per tile: 4, or 2 for wide sources
   int tiles;                             // tiles a CTA converts, one after the other
+  const int* luma_map;                   // optional: where source row r of the first plane is
+  const int* chroma_map;                 // ... and of the half-height planes (row-sparse sources)
   int* status;                           // optional device word for B2_STATUS_* bits
   unsigned wait_limit;                   // polls of a bounded wait
   int debug_flags;
@@ -432,16 +434,28 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
           s_rows[sr].wy0 = __fsub_rn(1.0f, ay.w1);
           s_rows[sr].wy1 = ay.w1;
         }
+        // with row maps the caller stored only the touched rows, back to back
         if (pl < 2) {
           key = yrow;
-          src = p.base + d.y_off + (size_t)yrow * d.y_pitch;
+          int at = p.luma_map != nullptr ? __ldg(p.luma_map + yrow) : yrow;
+          if (at < 0) {  // the map does not cover a row the geometry reads: stay in the buffer
+            at = 0;
+            if (p.status != nullptr) atomicOr(p.status, B2_STATUS_BAD_GEOMETRY);
+          }
+          src = p.base + d.y_off + (size_t)at * d.y_pitch;
           lo = blo;
           bytes = bhi - blo;
         } else {
           const int plane = pl < 4 ? 1 : 2;          // second / third plane
           const int prow = kYuv ? yrow >> 1 : yrow;  // chroma planes are half height
           key = ((long long)plane << 32) | (uint32_t)prow;
-          src = p.base + (plane == 1 ? d.u_off : d.v_off) + (size_t)prow * d.uv_pitch;
+          const int* map = kYuv ? p.chroma_map : p.luma_map;
+          int at = map != nullptr ? __ldg(map + prow) : prow;
+          if (at < 0) {
+            at = 0;
+            if (p.status != nullptr) atomicOr(p.status, B2_STATUS_BAD_GEOMETRY);
+          }
+          src = p.base + (plane == 1 ? d.u_off : d.v_off) + (size_t)at * d.uv_pitch;
           lo = cxlo;
           bytes = cxhi - cxlo;
         }
@@ -616,6 +630,8 @@ int launch_resize(const b2_resize_args& a, cudaStream_t stream) {
   p.vec_store = a.out_w % 4 == 0 && (uintptr_t)a.dst % 16 == 0 && aligned16(p.image_stride) &&
                 aligned16(p.group_stride) && aligned16(p.row_stride) &&
                 (a.layout != B2_NCHW || aligned16(plane));
+  p.luma_map = a.luma_row_map;
+  p.chroma_map = a.chroma_row_map;
   p.status = a.status;
   p.wait_limit = 1u << 19;  // about a second of sleeping polls
   p.debug_flags = a.debug_flags;

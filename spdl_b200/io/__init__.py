@@ -5,7 +5,7 @@ from ._convert import (ArrayInterface, CUDAArrayInterface, to_jax, to_numba, to_
                        to_torch)
 from ._core import (DESC_DTYPE, FrameBatcher, check_resize_status, convert_nv12, convert_resize,
                     frame_checksum, make_image_descs, nv12_to_bgr, nv12_to_rgb, resize_image_list, synchronize_stream,
-                    transfer_buffer, transfer_buffer_cpu)
+                    touched_rows, transfer_buffer, transfer_buffer_cpu)
 from ._frames import Frames, convert_array, convert_frames
 from ._stage import FrameStage
 from ._transfer import transfer_tensor
@@ -17,6 +17,6 @@ __all__ = [
     "DESC_DTYPE", "FrameBatcher", "FrameStage", "Frames", "check_resize_status", "convert_array",
     "convert_frames", "convert_nv12", "convert_resize", "cpu_storage", "cuda_buffer",
     "cuda_config", "frame_checksum", "make_image_descs", "nv12_to_bgr", "nv12_to_rgb", "resize_image_list",
-    "synchronize_stream", "to_jax", "to_numba", "to_numpy", "to_torch", "transfer_buffer", "transfer_buffer_cpu",
+    "synchronize_stream", "to_jax", "to_numba", "to_numpy", "to_torch", "touched_rows", "transfer_buffer", "transfer_buffer_cpu",
     "transfer_tensor",
 ]

@@ -32,7 +32,7 @@ from .utils import _tracing
 
 __all__ = [
     "nv12_to_rgb", "nv12_to_bgr", "convert_nv12", "convert_resize", "make_image_descs",
-    "check_resize_status",
+    "check_resize_status", "touched_rows",
     "transfer_buffer", "transfer_buffer_cpu", "synchronize_stream", "FrameBatcher",
     "frame_checksum", "DESC_DTYPE",
 ]
@@ -396,6 +396,29 @@ def make_image_descs(widths: Sequence[int], heights: Sequence[int], *, src_forma
     return d, (ow, oh)
 
 
+def touched_rows(desc: np.ndarray, *, src_format: str = "nv12", out_h: int
+                 ) -> tuple[np.ndarray, np.ndarray]:
+    """Which source rows one descriptor's vertical geometry reads when ``out_h`` output rows are
+    produced: ``(luma_map, chroma_map)``, ``int32`` arrays over the source rows of the first plane
+    and of the half-height planes (empty for RGB sources), holding each touched row's index among
+    the touched rows of its plane and ``-1`` elsewhere.  Computed by the library with the
+    kernel's own arithmetic.  A caller that uploads only those rows, in order, passes the maps to
+    :func:`convert_resize` (``row_maps=``): a 4K frame resized to 224x224 needs a quarter of its
+    rows on the device."""
+    rec = np.ascontiguousarray(np.asarray(desc, DESC_DTYPE).reshape(-1)[:1])
+    fmt = _FORMATS[src_format.lower()]
+    h = int(rec["src_h"][0])
+    if h < 1:
+        raise RuntimeError("the descriptor has an empty source")
+    luma = np.empty(h, np.int32)
+    chroma = np.empty((h + 1) // 2 if fmt in (NV12, I420) else 0, np.int32)
+    nl, nc = ctypes.c_int32(), ctypes.c_int32()
+    _lib.check(_lib.lib().b2_touched_rows(
+        rec.ctypes.data, fmt, int(out_h), luma.ctypes.data,
+        chroma.ctypes.data if chroma.size else None, ctypes.byref(nl), ctypes.byref(nc)))
+    return luma, chroma
+
+
 _status_lock = threading.Lock()
 _status_words: dict[tuple[int, int], CUDABuffer] = {}
 
@@ -433,8 +456,8 @@ def convert_resize(base: Any, descs: Any, *, out_size: tuple[int, int], max_src_
                    full_range: bool = False, layout: str = "NCHW", dtype: str = "uint8",
                    order: str = "rgb", mean=None, std=None, arith: str = "reference",
                    pad_color: tuple[float, float, float] = (0.0, 0.0, 0.0),
-                   clip_frames: int | None = None, sync: bool = False,
-                   _debug_flags: int = 0) -> CUDABuffer:
+                   clip_frames: int | None = None, row_maps: tuple[Any, Any] | None = None,
+                   sync: bool = False, _debug_flags: int = 0) -> CUDABuffer:
     """Fused colour conversion, bilinear resize, crop / letterbox and normalise over a packed
     batch.
 
@@ -446,7 +469,10 @@ def convert_resize(base: Any, descs: Any, *, out_size: tuple[int, int], max_src_
     clips in the channel-first video layout ``[N/T, 3, T, out_h, out_w]`` that
     ``examples/video_classification/utils/pipeline.py:137`` reaches with a ``permute``.
     ``pad_color`` is the R, G, B (0..255) of letterbox pixels (``scale_mode="pad"``).
-    ``arith`` as in :func:`convert_nv12`.
+    ``arith`` as in :func:`convert_nv12`.  ``row_maps=(luma_map, chroma_map)``: device copies of
+    the arrays of :func:`touched_rows`, for a batch of equal geometry whose buffer holds only the
+    touched rows of every image, back to back (the descriptors' plane offsets then point into
+    that compacted buffer; ``chroma_map`` is ``None`` for RGB sources).
 
     The table lives in device memory, so what the host cannot check -- an image wider than
     ``max_src_w``, a nonsensical descriptor -- is reported by the kernel in a device status word:
@@ -494,11 +520,14 @@ def convert_resize(base: Any, descs: Any, *, out_size: tuple[int, int], max_src_
     a.bias = (ctypes.c_float * 3)(*bias.tolist())
     a.pad_value = (ctypes.c_float * 3)(*[float(v) for v in pad_color])
     a.debug_flags = int(_debug_flags)
+    if row_maps is not None:
+        a.luma_row_map = _cai(row_maps[0])[0]
+        a.chroma_row_map = _cai(row_maps[1])[0] if row_maps[1] is not None else None
     a.status = status.data_ptr
     with _tracing.trace_event("b2::convert_resize"):
         _lib.check(_lib.lib().b2_convert_resize(ctypes.byref(a), device_config.stream))
     _tracing.record("convert_resize", n, 0, out.nbytes)
-    out._owner = (base, descs)
+    out._owner = (base, descs, row_maps)
     if sync:
         check_resize_status(device_config)
     return out

@@ -20,9 +20,11 @@ from typing import Any
 
 import numpy as np
 
+from .. import _lib
 from ._convert import to_torch
-from ._core import convert_nv12, convert_resize, make_image_descs, transfer_buffer
-from ._types import CPUBuffer, CUDAConfig, cuda_config
+from ._core import (convert_nv12, convert_resize, make_image_descs, touched_rows,
+                    transfer_buffer)
+from ._types import CPUBuffer, CPUStorage, CUDAConfig, cuda_config
 
 __all__ = ["FrameStage"]
 
@@ -38,6 +40,14 @@ class FrameStage:
     channel-first video layout ``[N/T, 3, T, h, w]``.  ``arith="swscale"`` reproduces the pixels
     of the reference's CPU route (libswscale) instead of those of its CUDA kernel.
     ``dtype="bfloat16"`` returns a ``torch.bfloat16`` tensor.
+
+    ``sparse_upload=True`` (resizing stages only) copies into the page-locked staging buffer, and
+    over PCIe, only the source rows the geometry reads -- a quarter of a 4K frame that becomes
+    224x224, four fifths of a 720p frame that becomes 256x256 -- instead of whole frames; the
+    kernel finds the rows through the maps of :func:`touched_rows`.  The result is identical.
+    ``sparse_upload="auto"`` does so when the geometry reads less than half of a frame's bytes
+    (measured on a B200 host: 3.3 times the frames per second for 4K -> 224x224, but 0.8 times
+    for 720p -> 256x256, where packing 81 % of the rows costs more than sending all of them).
     """
 
     def __init__(self, *, src_format: str = "i420", layout: str = "NCHW", dtype: str = "float32",
@@ -45,7 +55,8 @@ class FrameStage:
                  resize: tuple[int, int] | None = None, resize_shorter: int | None = None,
                  crop: tuple[int, int] | None = None, scale_mode: str | None = None,
                  pad_color: tuple[float, float, float] = (0.0, 0.0, 0.0),
-                 clip_frames: int | None = None, arith: str = "reference", num_caches: int = 4,
+                 clip_frames: int | None = None, arith: str = "reference",
+                 sparse_upload: bool = False, num_caches: int = 4,
                  device_index: int | None = None) -> None:
         if num_caches < 0:
             raise RuntimeError("num_caches must be non-negative")
@@ -59,6 +70,16 @@ class FrameStage:
         if clip_frames and not self._resizing:
             raise RuntimeError("clip_frames needs resize or resize_shorter")
         self._resize_opts = dict(pad_color=pad_color, clip_frames=clip_frames)
+        if sparse_upload not in (False, True, "auto"):
+            raise RuntimeError('sparse_upload is False, True or "auto"')
+        if sparse_upload is True and not self._resizing:
+            raise RuntimeError("sparse_upload needs resize or resize_shorter")
+        if sparse_upload is True and src_format.lower() not in ("nv12", "i420", "yuv420p"):
+            raise RuntimeError("sparse_upload takes NV12 or I420 frames")
+        if sparse_upload == "auto" and not (
+                self._resizing and src_format.lower() in ("nv12", "i420", "yuv420p")):
+            sparse_upload = False
+        self._sparse = sparse_upload
         self._num_caches = int(num_caches)
         self._device_index = device_index
         self._local = threading.local()
@@ -91,6 +112,56 @@ class FrameStage:
             hit = st["descs"][key] = (dev, out)
         return hit
 
+    def _sparse_plan(self, st, n: int, w: int, h: int):
+        """For frames of one size: which rows to copy, the descriptor table of the compacted
+        batch and the row maps on the device (built once per size and thread)."""
+        key = ("sparse", n, w, h)
+        plan = st["descs"].get(key)
+        if plan is None:
+            fmt = self._opts["src_format"].lower()
+            table, out = make_image_descs([w] * n, [h] * n, src_format=fmt, **self._geom)
+            luma, chroma = touched_rows(table[0], src_format=fmt, out_h=out[1])
+            lrows = np.flatnonzero(luma >= 0)
+            crows = np.flatnonzero(chroma >= 0)
+            cw = w if fmt == "nv12" else w // 2            # bytes of a chroma row
+            planes = 1 if fmt == "nv12" else 2             # chroma planes
+            frame_bytes = len(lrows) * w + planes * len(crows) * cw
+            table["y_off"] = np.arange(n, dtype=np.uint64) * frame_bytes
+            table["u_off"] = table["y_off"] + len(lrows) * w
+            if fmt != "nv12":
+                table["v_off"] = table["u_off"] + len(crows) * cw
+            cfg = st["cfg"]
+            plan = st["descs"][key] = dict(
+                out=out, lrows=lrows, crows=crows, cw=cw, frame_bytes=frame_bytes,
+                fraction=frame_bytes / (h * w * 1.5),
+                descs=transfer_buffer(table.view(np.uint8), device_config=cfg),
+                maps=(transfer_buffer(luma, device_config=cfg),
+                      transfer_buffer(chroma, device_config=cfg)))
+        return plan
+
+    def _gather_rows(self, st, frames: np.ndarray, plan, w: int, h: int) -> CPUBuffer:
+        """Copy the touched rows of every frame into the thread's page-locked staging buffer."""
+        n = frames.shape[0]
+        need = n * plan["frame_bytes"]
+        store = st.get("pinned")
+        if store is None or store.size < need:
+            store = st["pinned"] = CPUStorage(max(need, 1 << 20), pin_memory=True)
+        nl, nc, cw = len(plan["lrows"]), len(plan["crows"]), plan["cw"]
+        fb, src_fb = plan["frame_bytes"], frames.strides[0]
+        src, dst = frames.ctypes.data, store.data_ptr
+        copy = _lib.lib().b2_copy_rows  # plain memcpy per row, outside the GIL
+        lrows = np.ascontiguousarray(plan["lrows"], np.int32)
+        crows = np.ascontiguousarray(plan["crows"], np.int32)
+        _lib.check(copy(dst, fb, src, src_fb, w, lrows.ctypes.data, nl, w, n))
+        if cw == w:  # NV12: interleaved chroma rows follow the luma rows
+            _lib.check(copy(dst + nl * w, fb, src + h * w, src_fb, w, crows.ctypes.data, nc, w, n))
+        else:        # I420: a U block and a V block of half-width rows
+            blk = (h // 2) * cw
+            for k in range(2):
+                _lib.check(copy(dst + nl * w + k * nc * cw, fb, src + h * w + k * blk, src_fb, cw,
+                                crows.ctypes.data, nc, cw, n))
+        return CPUBuffer((need,), "u", 1, store)
+
     # -- the call --------------------------------------------------------------------------------
     def __call__(self, frames: Any):
         import torch
@@ -110,6 +181,25 @@ class FrameStage:
             raise RuntimeError(
                 f"The height of NV12 image (h*1.5) must be divisible by 3. Found: {h2}")
         h = h2 // 3 * 2
+        plan = None
+        if self._sparse and not (w % 2 or h % 2):
+            plan = self._sparse_plan(st, n, w, h)
+            if self._sparse == "auto" and plan["fraction"] >= 0.5:
+                plan = None  # packing most of the rows costs more than sending all of them
+        elif self._sparse is True:
+            raise RuntimeError(f"sparse_upload needs even frame sizes. Found: {w}x{h}")
+        if plan is not None:
+            host = np.ascontiguousarray(np.asarray(frames).reshape(shape))
+            dev = transfer_buffer(self._gather_rows(st, host, plan, w, h), device_config=cfg)
+            result = convert_resize(dev, plan["descs"], out_size=plan["out"], max_src_w=w,
+                                    device_config=cfg, row_maps=plan["maps"], sync=True,
+                                    **self._opts, **self._resize_opts)
+            tensor = to_torch(result, torch.bfloat16
+                              if self._opts["dtype"] in ("bfloat16", "bf16") else None)
+            if self._num_caches:
+                st["cache"].append(tensor)
+                st["cache"].pop(0)
+            return tensor
         if isinstance(frames, CPUBuffer):
             view = CPUBuffer(shape, frames.elem_class, frames.depth, frames.storage)
         else:

@@ -38,7 +38,7 @@ def test_struct_layouts_match_header_sizes():
     assert _lib.ResizeArgs.base.offset == 8 and _lib.ResizeArgs.dst.offset == 64
     # version 1 of the structs ended at these offsets; the later fields start there
     assert _lib.DenseArgs.arith.offset == 168 and ctypes.sizeof(_lib.DenseArgs) == 176
-    assert _lib.ResizeArgs.arith.offset == 104 and ctypes.sizeof(_lib.ResizeArgs) == 152
+    assert _lib.ResizeArgs.arith.offset == 104 and ctypes.sizeof(_lib.ResizeArgs) == 168
     assert _lib.ResizeArgs.status.offset == 144
     header = (ROOT / "include" / "b2frames.h").read_text()
     assert "version 1 (168)" in header and "version 1 (104)" in header
@@ -428,3 +428,57 @@ def test_aspect_preserving_geometry_follows_the_reference_filter_strings():
         io.make_image_descs(ws, hs, resize=(256, 256), scale_mode="fit")
     with pytest.raises(RuntimeError):
         io.make_image_descs(ws, hs, resize_shorter=256, scale_mode="pad")
+
+
+def test_touched_rows_of_the_benchmark_geometries():
+    """The host helper that says which source rows a geometry reads (for row-sparse uploads)."""
+    d, out = io.make_image_descs([3840], [2160], resize=(224, 224))
+    luma, chroma = io.touched_rows(d[0], src_format="nv12", out_h=out[1])
+    assert luma.shape == (2160,) and chroma.shape == (1080,)
+    # 224 output rows read two luma rows each; the scale (9.64) keeps all pairs apart
+    assert (luma >= 0).sum() == 448 and (chroma >= 0).sum() == 336
+    kept = luma[luma >= 0]
+    assert (kept == np.arange(448)).all()  # positions in a compacted copy, in row order
+    # 0.24 of the frame's bytes
+    assert abs(((luma >= 0).sum() + (chroma >= 0).sum()) / (2160 * 1.5) - 0.242) < 0.001
+    d, out = io.make_image_descs([1280], [720], resize=(256, 256))
+    luma, chroma = io.touched_rows(d[0], src_format="nv12", out_h=256)
+    assert (luma >= 0).sum() == 512 and (chroma >= 0).sum() == 360
+    # no resize: every row is read; upscaling too
+    d, out = io.make_image_descs([64], [48], resize=(64, 48))
+    luma, chroma = io.touched_rows(d[0], src_format="i420", out_h=48)
+    assert (luma == np.arange(48)).all() and (chroma == np.arange(24)).all()
+    # letterbox: rows of padding read nothing
+    d, out = io.make_image_descs([1280], [720], resize=(64, 64), scale_mode="pad")
+    luma, _ = io.touched_rows(d[0], src_format="nv12", out_h=64)
+    assert (luma >= 0).sum() <= 2 * int(d["resized_h"][0])
+    # RGB sources have no half-height planes
+    d, out = io.make_image_descs([100], [80], src_format="rgb24", resize=(20, 10))
+    luma, chroma = io.touched_rows(d[0], src_format="rgb24", out_h=10)
+    assert chroma.size == 0 and (luma >= 0).sum() == 20
+    bad = d.copy()
+    bad["scale_y"] = 0.0
+    with pytest.raises(RuntimeError):
+        io.touched_rows(bad[0], src_format="rgb24", out_h=10)
+
+
+def test_copy_rows_packs_selected_rows_of_every_frame():
+    """``b2_copy_rows``: the host-side packing step of a row-sparse upload (no CUDA call)."""
+    L = _lib.lib()
+    rng = np.random.default_rng(4)
+    n, rows_total, pitch, row_bytes = 3, 20, 70, 64
+    src = rng.integers(0, 256, (n, rows_total, pitch), dtype=np.uint8)
+    rows = np.array([1, 2, 7, 19], np.int32)
+    dst = np.full((n, len(rows) * row_bytes + 5), 0xA5, np.uint8)
+    assert L.b2_copy_rows(dst.ctypes.data, dst.strides[0], src.ctypes.data, src.strides[0], pitch,
+                          rows.ctypes.data, len(rows), row_bytes, n) == 0
+    for f in range(n):
+        assert (dst[f, :len(rows) * row_bytes].reshape(len(rows), row_bytes) ==
+                src[f, rows, :row_bytes]).all()
+        assert (dst[f, len(rows) * row_bytes:] == 0xA5).all()
+    assert L.b2_copy_rows(None, 0, None, 0, 0, None, 0, 16, 2) == 0  # nothing to do
+    assert L.b2_copy_rows(None, 0, src.ctypes.data, 0, 0, rows.ctypes.data, 4, 16, 2) == 1
+    rows[1] = -3
+    assert L.b2_copy_rows(dst.ctypes.data, dst.strides[0], src.ctypes.data, src.strides[0], pitch,
+                          rows.ctypes.data, len(rows), row_bytes, n) == 1
+    assert b"negative" in L.b2_last_error()

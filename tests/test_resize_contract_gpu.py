@@ -354,3 +354,90 @@ def test_callers_built_against_version_1_of_the_structs(cuda_cfg):
                                            torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
     assert (full.cpu().numpy() == oracle.nv12_to_planar(nv)).all()
+
+
+@pytest.mark.parametrize("fmt", ["nv12", "i420"])
+@pytest.mark.parametrize("src,geom", [((1280, 720), dict(resize=(256, 256))),
+                                      ((640, 360), dict(resize_shorter=96, crop=(80, 80))),
+                                      ((320, 180), dict(resize=(64, 64), scale_mode="pad")),
+                                      ((96, 64), dict(resize=(200, 150)))])
+def test_row_sparse_sources_equal_whole_frames(cuda_cfg, fmt, src, geom):
+    """Only the rows a geometry reads are stored (back to back) and found through the row maps:
+    the result equals the conversion of the whole frames, bit for bit."""
+    import spdl_b200.io as io
+
+    n, (w, h) = 3, src
+    frames = synth.nv12_batch(n, w, h, config=9, index=w + h)
+    table, out = io.make_image_descs([w] * n, [h] * n, src_format=fmt, **geom)
+    dense = io.to_torch(io.convert_resize(_dev(frames.reshape(-1)), _dev(table.view(np.uint8)),
+                                          out_size=out, max_src_w=w, device_config=cuda_cfg,
+                                          src_format=fmt, pad_color=(9, 99, 199),
+                                          sync=True)).cpu().numpy()
+    luma, chroma = io.touched_rows(table[0], src_format=fmt, out_h=out[1])
+    lrows, crows = np.flatnonzero(luma >= 0), np.flatnonzero(chroma >= 0)
+    cw = w if fmt == "nv12" else w // 2
+    packed = []
+    for f in frames:
+        parts = [f[:h][lrows].reshape(-1)]
+        if fmt == "nv12":
+            parts.append(f[h:][crows].reshape(-1))
+        else:
+            flat, blk = f.reshape(-1), (h // 2) * cw
+            for k in range(2):
+                plane = flat[h * w + k * blk:h * w + (k + 1) * blk].reshape(h // 2, cw)
+                parts.append(plane[crows].reshape(-1))
+        packed.append(np.concatenate(parts))
+    fb = packed[0].size
+    assert fb < h * w * 3 // 2 or w == 96  # the upscaling case reads every row
+    sparse_table = table.copy()
+    sparse_table["y_off"] = np.arange(n, dtype=np.uint64) * fb
+    sparse_table["u_off"] = sparse_table["y_off"] + len(lrows) * w
+    if fmt == "i420":
+        sparse_table["v_off"] = sparse_table["u_off"] + len(crows) * cw
+    got = io.to_torch(io.convert_resize(
+        _dev(np.concatenate(packed)), _dev(sparse_table.view(np.uint8)), out_size=out, max_src_w=w,
+        device_config=cuda_cfg, src_format=fmt, pad_color=(9, 99, 199),
+        row_maps=(_dev(luma), _dev(chroma)), sync=True)).cpu().numpy()
+    assert (got == dense).all()
+
+
+def test_a_row_map_with_a_hole_is_reported_not_followed(cuda_cfg):
+    import spdl_b200.io as io
+
+    n, w, h = 2, 128, 72
+    frames = synth.nv12_batch(n, w, h, config=9, index=3)
+    table, out = io.make_image_descs([w] * n, [h] * n, resize=(32, 32))
+    luma, chroma = io.touched_rows(table[0], src_format="nv12", out_h=32)
+    luma = np.arange(h, dtype=np.int32)      # whole frames are on the device ...
+    chroma = np.arange(h // 2, dtype=np.int32)
+    luma[int(np.flatnonzero(io.touched_rows(table[0], src_format="nv12", out_h=32)[0] >= 0)[5])] = -1
+    with pytest.raises(RuntimeError, match="descriptor"):  # ... but the map denies a needed row
+        io.convert_resize(_dev(frames.reshape(-1)), _dev(table.view(np.uint8)), out_size=out,
+                          max_src_w=w, device_config=cuda_cfg, row_maps=(_dev(luma), _dev(chroma)),
+                          sync=True)
+    io.check_resize_status(cuda_cfg)  # the word is clear again
+
+
+def test_frame_stage_sparse_upload_equals_whole_frames():
+    import torch
+
+    import spdl_b200.io as io
+
+    for fmt, (w, h) in (("nv12", (640, 360)), ("i420", (320, 240))):
+        frames = synth.nv12_batch(4, w, h, config=9, index=w)
+        kw = dict(src_format=fmt, dtype="float32", mean=MEAN, std=STD, resize_shorter=96,
+                  crop=(80, 80))
+        whole = io.FrameStage(**kw)(frames)
+        sparse = io.FrameStage(sparse_upload=True, **kw)
+        a = sparse(frames)
+        b = sparse(frames[:2])  # another batch size: a second plan
+        assert torch.equal(a, whole) and torch.equal(b, whole[:2])
+    with pytest.raises(RuntimeError):
+        io.FrameStage(sparse_upload=True)
+    # "auto": sparse for a geometry that reads a small part of the frame, whole frames otherwise
+    frames = synth.nv12_batch(2, 640, 360, config=9, index=5)
+    for geom, expect_sparse in ((dict(resize=(64, 40)), True), (dict(resize=(320, 300)), False)):
+        auto = io.FrameStage(src_format="nv12", dtype="uint8", sparse_upload="auto", **geom)
+        whole = io.FrameStage(src_format="nv12", dtype="uint8", **geom)
+        assert torch.equal(auto(frames), whole(frames))
+        assert ("pinned" in auto._state()) == expect_sparse
