@@ -24,7 +24,7 @@ from .. import _lib
 from ._convert import to_torch
 from ._core import (convert_nv12, convert_resize, make_image_descs, touched_rows,
                     transfer_buffer)
-from ._types import CPUBuffer, CPUStorage, CUDAConfig, cuda_config
+from ._types import CPUBuffer, CPUStorage, CUDAConfig, cuda_buffer, cuda_config
 
 __all__ = ["FrameStage"]
 
@@ -162,6 +162,19 @@ class FrameStage:
                                 crows.ctypes.data, nc, cw, n))
         return CPUBuffer((need,), "u", 1, store)
 
+    @staticmethod
+    def _upload(view, cfg: CUDAConfig):
+        """Host frames to the device on the thread's stream.  Page-locked sources are queued
+        without a wait (the conversion that follows runs on the same stream and the call waits
+        once, at its end); pageable ones go through the blocking copy of ``transfer_buffer``."""
+        if isinstance(view, CPUBuffer) and view.is_pinned():
+            dev = cuda_buffer(view.shape, cfg, view.elem_class, view.depth)
+            _lib.check(_lib.lib().b2_transfer_h2d_async(dev.data_ptr, view.data_ptr, dev.nbytes,
+                                                        cfg.device_index, cfg.stream))
+            dev._owner = view  # the source must outlive the queued copy
+            return dev
+        return transfer_buffer(view, device_config=cfg)
+
     # -- the call --------------------------------------------------------------------------------
     def __call__(self, frames: Any):
         import torch
@@ -190,7 +203,7 @@ class FrameStage:
             raise RuntimeError(f"sparse_upload needs even frame sizes. Found: {w}x{h}")
         if plan is not None:
             host = np.ascontiguousarray(np.asarray(frames).reshape(shape))
-            dev = transfer_buffer(self._gather_rows(st, host, plan, w, h), device_config=cfg)
+            dev = self._upload(self._gather_rows(st, host, plan, w, h), cfg)
             result = convert_resize(dev, plan["descs"], out_size=plan["out"], max_src_w=w,
                                     device_config=cfg, row_maps=plan["maps"], sync=True,
                                     **self._opts, **self._resize_opts)
@@ -204,7 +217,7 @@ class FrameStage:
             view = CPUBuffer(shape, frames.elem_class, frames.depth, frames.storage)
         else:
             view = np.ascontiguousarray(frames).reshape(shape)
-        dev = transfer_buffer(view, device_config=cfg)
+        dev = self._upload(view, cfg)
         if self._resizing:
             descs, out = self._descs_for(st, n, w, h)
             # sync=True waits for the stream once and checks the kernel's status word

@@ -87,3 +87,33 @@ def test_the_two_arithmetics_differ_as_documented():
     b = oracle.exhaustive(1, False, arith=oracle.ARITH_SWSCALE)[16:236, 16:241, 16:241]
     d = np.abs(a - b)
     assert d.max() <= 9 and 0.3 < (d == 0).mean() < 0.7
+
+
+@pytest.mark.skipif(not swscale_ref.available(), reason="libswscale is not on this machine")
+def test_widths_that_are_not_multiples_of_eight():
+    """The library's SIMD loop converts groups of 8 pixels.  Given a destination stride with room
+    it converts up to the next multiple of 8 with the same arithmetic, so every column of a
+    50-wide frame equals the restatement; given a tight stride it leaves the last two columns of
+    that frame unwritten (a property of the library, not a second arithmetic)."""
+    import ctypes
+
+    w, h = 50, 22
+    frame = np.random.default_rng(1).integers(0, 256, (h * 3 // 2, w), dtype=np.uint8)
+    flat = frame.reshape(-1)
+    want = oracle.convert_dense(frame[None], flat[h * w:], flat[h * w + (h // 2) * (w // 2):],
+                                width=w, height=h, num_frames=1, y_pitch=w, uv_pitch=w // 2,
+                                y_frame_stride=h * 3 // 2 * w, uv_frame_stride=h * 3 // 2 * w,
+                                src_format=oracle.I420, layout=oracle.NHWC,
+                                arith=oracle.ARITH_SWSCALE)[0]
+    conv = swscale_ref.I420ToRGB(w, h, 1)
+    tight = np.full((h, w, 3), 77, np.uint8)
+    conv(frame, tight)
+    assert (tight[:, :48] == want[:, :48]).all() and (tight[:, 48:] == 77).all()
+    roomy = np.full((h, 64, 3), 77, np.uint8)
+    base = frame.ctypes.data
+    src = (ctypes.c_void_p * 4)(base, base + w * h, base + w * h + (w // 2) * (h // 2), None)
+    stride = (ctypes.c_int * 4)(w, w // 2, w // 2, 0)
+    dst = (ctypes.c_void_p * 4)(roomy.ctypes.data, None, None, None)
+    dstride = (ctypes.c_int * 4)(64 * 3, 0, 0, 0)
+    assert swscale_ref.load().sws_scale(conv.ctx, src, stride, 0, h, dst, dstride) == h
+    assert (roomy[:, :w] == want).all()
