@@ -3,7 +3,7 @@
 ``.pipe(stage, concurrency=2)`` on a pool of worker threads.
 
 ``spdl.pipeline`` is pure Python and is imported from the reference tree where that tree exists
-(``REFERENCE_ROOT``, default ``/root/reference``); the tests are skipped elsewhere.  The CPU test
+(the ``REFERENCE_ROOT`` environment variable names it); the tests are skipped elsewhere.  The CPU test
 replaces the three device calls of the stage with host stand-ins built on the oracle, so that the
 packaging -- one object shared by all workers, per-thread state, ordered results, the keep-alive
 window -- runs under the reference's executor without a GPU; the GPU test runs the real stage.
