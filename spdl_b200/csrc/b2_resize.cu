@@ -19,14 +19,16 @@
 //            of touched rows and nothing else.
 //   Table:   while the copies are in flight the CTA builds one entry per output column (tap
 //            offsets and weight): the horizontal taps are the same for every row of the image.
-//   Compute: a warp owns one output row (or half of one), a lane walks the row's columns 32
-//            apart.  Everything that depends on the row only -- the staged row addresses, the
-//            vertical weights, the destination row -- is computed once per warp and lives in
-//            registers; per pixel a lane reads its column's table entry, converts the four taps
-//            (the two source rows of a tap column ride in the two lanes of the packed fp32
-//            instructions), blends and stores one element per channel, consecutive lanes to
-//            consecutive addresses.  Stores are element-wise, so no destination pointer, stride
-//            or width has an alignment requirement.
+//   Compute: a lane converts groups of four consecutive output columns.  When a row's groups fill
+//            whole warps, a warp owns one output row (or half of one) and its lanes walk the row's
+//            groups 32 apart, with everything that depends on the row only -- the staged row
+//            addresses, the vertical weights, the destination row -- in registers; otherwise the
+//            CTA's lanes take the (row, group) items of the tile in turn, so that only the tile's
+//            last warp has idle lanes.  Per pixel a lane reads its column's table entry, converts
+//            the four taps (the two source rows of a tap column ride in the two lanes of the packed
+//            fp32 instructions) and blends; a group goes out as vector stores when it lies inside
+//            the image and the destination is 16-byte aligned, element by element otherwise, so
+//            no destination pointer, stride or width has an alignment requirement.
 #include <cuda_fp16.h>
 
 #include <atomic>
@@ -53,6 +55,8 @@ struct ResizeParams {
   int vec_store;                         // 1: whole groups of four pixels may use vector stores
   int rows;                              // output rows per tile: 4, or 2 for wide sources
   int tiles;                             // tiles a CTA converts, one after the other
+  int flat;                              // 1: lanes take the (row, group) items of a tile in turn
+  unsigned groups_recip;                 // 2^32 / groups + 1: item / groups by multiply-high
   const int* luma_map;                   // optional: where source row r of the first plane is
   const int* chroma_map;                 // ... and of the half-height planes (row-sparse sources)
   int* status;                           // optional device word for B2_STATUS_* bits
@@ -222,14 +226,13 @@ __device__ __forceinline__ uint32_t bf16x2_bits(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&t);
 }
 
-// The four-pixel groups g, g + gstep, ... below `gend` of one output row.  drow: the row in the
-// destination; val[k][c]: pixel k, colour channel c.
+// The four-pixel group g of one output row.  drow: the row in the destination; val[k][c]: pixel
+// k, colour channel c.
 template <int FMT, int LAYOUT, int DTYPE, int ARITH, bool UV16, typename T>
-__device__ __forceinline__ void convert_row(const ResizeParams& p, const MatPairs<ARITH>& m,
-                                            const RowInfo& in, uint32_t xoffs, uint32_t xw,
-                                            T* drow, int g, int gend, int gstep, int groups,
-                                            int cin0, int cin1) {
-  for (; g < gend; g += gstep) {
+__device__ __forceinline__ void convert_group(const ResizeParams& p, const MatPairs<ARITH>& m,
+                                              const RowInfo& in, uint32_t xoffs, uint32_t xw,
+                                              T* drow, int g, int groups, int cin0, int cin1) {
+  {
     const int ox0 = 4 * g;
     const uint4 w4 = lds_v4(xw + 16u * (uint32_t)g);
     const float w1s[4] = {__uint_as_float(w4.x), __uint_as_float(w4.y), __uint_as_float(w4.z),
@@ -291,7 +294,7 @@ __device__ __forceinline__ void convert_row(const ResizeParams& p, const MatPair
           o[2] = make_uint2(bf16x2_bits(val[2][2], val[3][0]), bf16x2_bits(val[3][1], val[3][2]));
         }
       }
-      continue;
+      return;
     }
     // the ragged end of a row, padding columns, or a destination that is not 16-byte aligned
 #pragma unroll
@@ -315,6 +318,7 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ b2_image_desc sd;
   __shared__ RowInfo s_rows[kRows];
+  __shared__ int s_odd_chroma;  // a staged interleaved-chroma row of this tile has an odd address
   // bar[0]: the staged rows.  bar[1]: nothing ever arrives on it (B2_DEBUG_EXPIRE_WAIT).
   __shared__ __align__(8) unsigned long long bar[2];
 
@@ -467,6 +471,10 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
       const int owner = __ffs(same) - 1;
       const bool fetch = active && owner == lane;
       if (active) s_rows[sr].row[pl] = sbase + (uint32_t)(owner * p.span_cap + head);
+      if constexpr (FMT == B2_SRC_NV12) {
+        const bool odd = __any_sync(0xffffffffu, active && pl >= 2 && (head & 1));
+        if (lane == 0) s_odd_chroma = odd;
+      }
       const unsigned total = __reduce_add_sync(0xffffffffu, fetch ? (unsigned)bytes : 0u);
       if (tile > 0)  // order the other warps' reads of the buffer before the engine's writes
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -529,12 +537,43 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
       }
     }
 
-    // ---- compute: a warp per output row ----------------------------------------------------------
+    // ---- compute ---------------------------------------------------------------------------------
+    // interleaved chroma pairs can be fetched with one 16-bit load when the staged rows kept an
+    // even address (they do whenever the source plane and pitch are even)
+    const bool uv16 = FMT == B2_SRC_NV12 && !s_odd_chroma;
+    if (p.flat) {
+      // The row's groups do not fill whole warps: the CTA's lanes take the (row, group) items of
+      // the tile in turn instead, so that only the tile's last warp has idle lanes.
+      const int items = rows_here * groups;
+      for (int item = tid; item < items; item += kResizeThreads) {
+        const int ir = (int)__umulhi((unsigned)item, p.groups_recip);
+        const int g = item - ir * groups;
+        const int oy = oy0 + ir;
+        T* const drow = dimg + (long long)oy * p.row_stride;
+        if (oy < rin0 || oy >= rin1) {  // a row of padding
+          for (int ox = 4 * g; ox < min(4 * g + 4, p.out_w); ++ox)
+#pragma unroll
+            for (int c = 0; c < 3; ++c)
+              store_elem<DTYPE>(drow + p.chan_off[c] + (long long)ox * p.px_stride,
+                                finish<DTYPE>(p, p.ch_pad[c], c));
+          continue;
+        }
+        const RowInfo in = s_rows[ir];
+        if (uv16)
+          convert_group<FMT, LAYOUT, DTYPE, ARITH, true>(p, m, in, xoffs, xw, drow, g, groups, cin0,
+                                                         cin1);
+        else
+          convert_group<FMT, LAYOUT, DTYPE, ARITH, false>(p, m, in, xoffs, xw, drow, g, groups,
+                                                          cin0, cin1);
+      }
+      continue;
+    }
+    // a warp per output row (two warps when a tile has two rows)
     if (r >= rows_here) continue;
     const int oy = oy0 + r;
     T* const drow = dimg + (long long)oy * p.row_stride;
     if (oy < rin0 || oy >= rin1) {  // a row of padding
-      for (int ox = lane + 32 * (warp / p.rows); ox < p.out_w; ox += gstep)
+      for (int ox = g0; ox < p.out_w; ox += gstep)
 #pragma unroll
         for (int c = 0; c < 3; ++c)
           store_elem<DTYPE>(drow + p.chan_off[c] + (long long)ox * p.px_stride,
@@ -542,15 +581,15 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
       continue;
     }
     const RowInfo in = s_rows[r];
-    // interleaved chroma pairs can be fetched with one 16-bit load when the staged rows kept an
-    // even address (they do whenever the source plane and pitch are even)
-    const bool uv16 = FMT == B2_SRC_NV12 && ((in.row[2] | in.row[3]) & 1) == 0;
-    if (uv16)
-      convert_row<FMT, LAYOUT, DTYPE, ARITH, true>(p, m, in, xoffs, xw, drow, g0, groups, gstep,
-                                                   groups, cin0, cin1);
-    else
-      convert_row<FMT, LAYOUT, DTYPE, ARITH, false>(p, m, in, xoffs, xw, drow, g0, groups, gstep,
-                                                    groups, cin0, cin1);
+    if (uv16) {
+      for (int g = g0; g < groups; g += gstep)
+        convert_group<FMT, LAYOUT, DTYPE, ARITH, true>(p, m, in, xoffs, xw, drow, g, groups, cin0,
+                                                       cin1);
+    } else {
+      for (int g = g0; g < groups; g += gstep)
+        convert_group<FMT, LAYOUT, DTYPE, ARITH, false>(p, m, in, xoffs, xw, drow, g, groups, cin0,
+                                                        cin1);
+    }
   }
 }
 
@@ -658,6 +697,14 @@ int launch_resize(const b2_resize_args& a, cudaStream_t stream) {
   while (p.tiles > 1 && (long long)a.num_images * ((a.out_h + p.rows * p.tiles - 1) /
                                                     (p.rows * p.tiles)) < 4 * 148 * 8)
     p.tiles >>= 1;
+  // Items in turn when that takes fewer warp passes over a tile than a warp (or two) per row.
+  // The reciprocal is exact for every item of a tile when groups >= 2 (for a single group it does
+  // not fit 32 bits, and a warp per row is as good).
+  const int groups = (a.out_w + 3) / 4, lanes_per_row = 32 * (kResizeWarps / p.rows);
+  const int passes_flat = (p.rows * groups + 31) / 32;
+  const int passes_rows = kResizeWarps * ((groups + lanes_per_row - 1) / lanes_per_row);
+  p.flat = groups >= 2 && passes_flat < passes_rows;
+  p.groups_recip = groups >= 2 ? (unsigned)((1ull << 32) / (unsigned)groups + 1) : 0u;
   const bool sws = a.arith == B2_ARITH_SWSCALE;
   switch (a.src_format) {
     case B2_SRC_NV12:

@@ -200,6 +200,20 @@ def test_unaligned_output_width(cuda_cfg):
         _compare(got, want, dtype)
 
 
+@pytest.mark.parametrize("out_w", [1, 2, 3, 4, 5, 8, 9, 28, 33, 100, 124, 132, 224, 236])
+def test_output_widths_around_the_lane_mappings(cuda_cfg, out_w):
+    """One group of four columns, groups that fill part of a warp, whole warps and a little more:
+    every way the kernel spreads a tile's columns over its lanes, with a last tile of odd height."""
+    import spdl_b200.io as io
+
+    w, h = 150, 90
+    nv = synth.nv12_batch(2, w, h, config=9, index=out_w)
+    descs, out = io.make_image_descs([w, w], [h, h], resize=(out_w, 21))
+    for layout, dtype in (("NCHW", "uint8"), ("NHWC", "float32")):
+        got, want = _run(cuda_cfg, nv.reshape(-1), descs, out, "nv12", layout, dtype)
+        _compare(got, want, dtype)
+
+
 @pytest.mark.parametrize("world", [2, 8])
 def test_sharded_ragged_batch_equals_whole(cuda_cfg, world):
     """The ragged batch split over ``world`` ranks in contiguous blocks (descriptor table sliced,
