@@ -949,17 +949,19 @@ def run_aux_workload(args) -> None:
         results["checksum_kernel"] = {"ms": ms, "bytes": b, "gb_per_s": b / ms / 1e6,
                                       "frac": b / ms / 1e6 / peak,
                                       "what": "64 x 1080p RGB frames (read only)"}
-        # 3. rows that do not start on 16-byte boundaries take the any-alignment kernel: packed
-        #    frames of width 1918 and of 854x480 (a common video size), and the 1918-wide batch
-        #    written to an odd address
+        # 3. widths that are not a multiple of 16: packed frames of width 1918, 1366x768 and 854x480
+        #    (common video sizes) take the kernel for packed frames; the 1918-wide batch written to
+        #    an odd address takes the any-alignment kernel
         for name, wq, hq, off, what in (
-                ("dense_any_kernel_1918x1080", 1918, 1080, 0,
-                 "64 x 1918x1080 NV12 -> NHWC u8 (rows on even, unaligned offsets)"),
+                ("dense_flat_kernel_1918x1080", 1918, 1080, 0,
+                 "64 x 1918x1080 NV12 -> NHWC u8 (packed frames, rows on even, unaligned offsets)"),
                 ("dense_any_kernel_odd_address", 1918, 1080, 1,
                  "the same batch written to an odd address"),
-                ("dense_any_kernel_854x480", 854, 480, 0,
+                ("dense_flat_kernel_1366x768", 1366, 768, 0,
+                 "128 x 1366x768 NV12 -> NHWC u8 (packed frames)"),
+                ("dense_flat_kernel_854x480", 854, 480, 0,
                  "256 x 854x480 NV12 -> NHWC u8 (packed 480p frames)")):
-            nq = n if hq == 1080 else 256
+            nq = {1080: n, 768: 128, 480: 256}[hq]
             hq2 = hq * 3 // 2
             srcq = [torch.randint(16, 236, (nq, hq2, wq), dtype=torch.uint8, device=dev)
                     for _ in range(2)]

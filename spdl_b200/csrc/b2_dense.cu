@@ -1,6 +1,6 @@
 // Dense colour conversion: every pixel of every frame, no resampling.
 //
-// Two kernel families.
+// Three kernels.
 //   dense_vec_kernel   the fast path.  One thread owns a 2-row x PX-pixel block (PX = 16 bytes
 //                      of output per channel: 16 px for u8, 8 for bf16, 4 for fp32), so the two
 //                      rows share one chroma load, every global load is one 4/8/16-byte vector
@@ -9,11 +9,19 @@
 //                      instruction).  Interleaved output (48 bytes per thread per row) is staged
 //                      in shared memory by the warp and leaves as one bulk asynchronous copy
 //                      (cp.async.bulk shared->global) per row segment.
-//   dense_any_kernel   rows, planes or destinations that are not 16-byte aligned (packed frames
-//                      of width 854 or 1366, crops, odd addresses): the same thread layout, the
-//                      source realigned with 4-byte loads and funnel shifts, the output laid out
-//                      in shared memory at the destination's offset modulo 16 so that its aligned
-//                      interior still leaves as one bulk copy per row segment.
+//   dense_flat_kernel  packed frames whose width is not a multiple of the vector size (854,
+//                      1366, 1918 ...): with rows back to back, a frame's pixels and its output
+//                      are two flat arrays, so a thread takes PX consecutive pixels of the frame,
+//                      counted from the first pixel whose output is 16-byte aligned.  Every store
+//                      is then an aligned vector whatever the width; only the sources are
+//                      realigned (4-byte loads and funnel shifts), a chunk that runs over the end
+//                      of a row fetches its chroma in two parts, and the ends of a frame are
+//                      stored byte by byte.
+//   dense_any_kernel   everything else (pitched rows or destinations that are not 16-byte aligned,
+//                      odd widths and addresses, pointer tables of unaligned surfaces): the vector
+//                      kernel's thread layout, the source realigned the same way, the output laid
+//                      out in shared memory at the destination's offset modulo 16 so that its
+//                      aligned interior still leaves as one bulk copy per row segment.
 //
 // The kernels are HBM-bound: 1.5 bytes read and 3*sizeof(T) written per pixel.
 #include "b2_common.cuh"
@@ -36,6 +44,10 @@ struct DenseParams {
   long long dst_plane_stride, dst_frame_stride;  // elements
   int dst_row_pitch;                              // elements
   ScaleBias sb;
+  // dense_flat_kernel only
+  int pixels;         // width * height: luma bytes of a frame
+  int chroma_limit;   // bytes of a chroma plane of a frame
+  unsigned w_recip;   // 2^32 / width, rounded down: pixel index -> row by multiply-high
 };
 
 // Load NB bytes into ceil(NB/4) words.  Streaming (read-once) cache hint.
@@ -356,6 +368,189 @@ __device__ __forceinline__ void convert_chunk(const ColorMat& m, const ScaleBias
   }
 }
 
+// ---- packed frames of any width ------------------------------------------------------------------
+// A frame whose rows lie back to back (pitch == width, even) is a flat array of width * height luma
+// bytes, its output a flat array of pixels in the same order.  A lane converts PX consecutive
+// pixels of that array (one row's worth of convert_chunk); chunks are counted from pixel i0, the
+// first even pixel of the frame whose output address is a multiple of 16, so that a lane's 48
+// interleaved bytes (or 16 bytes per plane) always leave as aligned vectors.  What is left is
+//   in:    luma and chroma windows at arbitrary byte offsets (load_window);
+//   rows:  a chunk that starts k1 < PX pixels before the end of an even row continues in the next
+//          row under the SAME chroma row: its chroma is fetched in two parts and blended (after an
+//          odd row the next chroma row follows in memory, and nothing is to be done);
+//   ends:  the first and the last chunk of a frame hold pixels outside it; their bytes are not
+//          stored (interleaved: the ragged ends of the warp's staged bytes go out byte by byte).
+constexpr int kFlatThreads = 128;
+#ifndef B2_FLAT_MB
+#define B2_FLAT_MB 10
+#endif
+#ifndef B2_FLAT_CH
+#define B2_FLAT_CH 2
+#endif
+constexpr int kFlatMinBlocks = B2_FLAT_MB;
+constexpr int kFlatChunks = B2_FLAT_CH;  // chunks per lane: a warp converts 64 consecutive chunks
+
+// load_window for a window known to lie at least 4 bytes inside its plane at both ends.
+template <int NB>
+__device__ __forceinline__ void load_window_inside(const uint8_t* base, int x, uint32_t* w) {
+  constexpr int NWD = (NB + 3) / 4;
+  const uintptr_t addr = (uintptr_t)base + (intptr_t)x;
+  const int a = (int)(addr & 3);
+  const uint32_t* q = reinterpret_cast<const uint32_t*>(addr - a);
+  uint32_t v[NWD + 1];
+#pragma unroll
+  for (int i = 0; i <= NWD; ++i) v[i] = __ldg(q + i);
+#pragma unroll
+  for (int i = 0; i < NWD; ++i) w[i] = __funnelshift_r(v[i], v[i + 1], a * 8);
+}
+
+// Luma and chroma words of the chunk that starts at pixel i of the frame (i < p.pixels; negative
+// for the partial chunk in front of the frame).
+template <int FMT, int PX, int NW, int UVW>
+__device__ __forceinline__ void flat_load(const DenseParams& p, const uint8_t* yb,
+                                          const uint8_t* ub, const uint8_t* vb, int i,
+                                          uint32_t (&yw)[1][NW], uint32_t (&uw)[UVW],
+                                          uint32_t (&vw)[UVW]) {
+  constexpr int CDIV = FMT == B2_SRC_NV12 ? 1 : 2;  // luma columns per chroma byte column
+  constexpr int UVB = PX / CDIV;
+  int y = 0, x = i;  // a negative i belongs to the partial chunk in front of row 0
+  if (i > 0) {
+    y = (int)__umulhi((unsigned)i, p.w_recip);
+    x = i - y * p.width;
+    if (x >= p.width) {  // the rounded-down reciprocal is short by at most one
+      x -= p.width;
+      ++y;
+    }
+  }
+  const int cw = p.width / CDIV;               // bytes of a chroma row
+  const int ca = (y >> 1) * cw + x / CDIV;     // x is even
+  const int k1 = p.width - x;                  // pixels of the chunk that lie in row y
+  const bool split = k1 < PX && !(y & 1);      // ... the rest under the same chroma row
+  uint32_t u2[UVW], v2[UVW];
+  (void)vw;
+  (void)v2;
+  if (i >= 4 && i + PX + 4 <= p.pixels && ca >= cw + 4 && ca + UVB + 4 <= p.chroma_limit) {
+    load_window_inside<PX>(yb, i, yw[0]);
+    load_window_inside<UVB>(ub, ca, uw);
+    if constexpr (FMT == B2_SRC_I420) load_window_inside<UVB>(vb, ca, vw);
+    if (split) {
+      load_window_inside<UVB>(ub, ca - cw, u2);
+      if constexpr (FMT == B2_SRC_I420) load_window_inside<UVB>(vb, ca - cw, v2);
+    }
+  } else {
+    load_window<PX>(yb, i, p.pixels, yw[0]);
+    load_window<UVB>(ub, ca, p.chroma_limit, uw);
+    if constexpr (FMT == B2_SRC_I420) load_window<UVB>(vb, ca, p.chroma_limit, vw);
+    if (split) {
+      load_window<UVB>(ub, ca - cw, p.chroma_limit, u2);
+      if constexpr (FMT == B2_SRC_I420) load_window<UVB>(vb, ca - cw, p.chroma_limit, v2);
+    }
+  }
+  if (split) {
+    const int kb = k1 / CDIV;  // chroma bytes that belong to row y
+#pragma unroll
+    for (int j = 0; j < UVW; ++j) {
+      const int m = kb - 4 * j;
+      const uint32_t keep = m >= 4 ? 0xffffffffu : (m <= 0 ? 0u : (1u << (8 * m)) - 1u);
+      uw[j] = (uw[j] & keep) | (u2[j] & ~keep);
+      if constexpr (FMT == B2_SRC_I420) vw[j] = (vw[j] & keep) | (v2[j] & ~keep);
+    }
+  }
+}
+
+template <int FMT, int LAYOUT, int DTYPE, bool BGR, int ARITH>
+__global__ void __launch_bounds__(kFlatThreads, kFlatMinBlocks) dense_flat_kernel(const DenseParams p) {
+  using T = typename OutT<DTYPE>::type;
+  constexpr int ESZ = (int)sizeof(T);
+  constexpr int PX = 16 / ESZ;
+  constexpr int NW = PX / 4;
+  constexpr int UVW = ((FMT == B2_SRC_NV12 ? PX : PX / 2) + 3) / 4;
+  constexpr int CH = kFlatChunks;
+  extern __shared__ __align__(128) unsigned char flat_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n = blockIdx.z;
+  uint8_t* const dstb =
+      reinterpret_cast<uint8_t*>(static_cast<T*>(p.dst) + (long long)n * p.dst_frame_stride);
+  // i0: the launcher guarantees that an even one exists (the frame starts on a multiple of
+  // 2 * ESZ bytes).  Interleaved: 3 * ESZ * i0 + d = 0 (mod 16); planar: ESZ * i0 + d = 0.
+  const int d = (int)((uintptr_t)dstb & 15);
+  int i0;
+  if constexpr (LAYOUT == B2_NHWC)
+    i0 = ESZ == 1 ? (5 * d) & 15 : (ESZ == 2 ? d >> 1 : d >> 2);
+  else
+    i0 = ((16 - d) & 15) / ESZ;
+  const int start = i0 ? i0 - PX : 0;  // first pixel of chunk 0 (negative: a partial chunk)
+  // the warp's first pixel: its lanes take chunks lane, lane + 32, ...
+  const int wi = start + (int)(blockIdx.x * (kFlatThreads / 32) + warp) * (CH * 32 * PX);
+  if (wi >= p.pixels) return;
+
+  const uint8_t* yb = p.y + (long long)n * p.y_frame_stride;
+  const uint8_t* ub = p.u + (long long)n * p.uv_frame_stride;
+  const uint8_t* vb = FMT == B2_SRC_I420 ? p.v + (long long)n * p.uv_frame_stride : nullptr;
+  uint32_t yw[CH][1][NW], uw[CH][UVW], vw[CH][UVW];
+#pragma unroll
+  for (int k = 0; k < CH; ++k) {
+    const int i = wi + (k * 32 + lane) * PX;
+    if (i < p.pixels) flat_load<FMT, PX>(p, yb, ub, vb, i, yw[k], uw[k], vw[k]);
+  }
+  unsigned char* wsm = flat_smem + warp * (CH * 32 * 48);
+#pragma unroll
+  for (int k = 0; k < CH; ++k) {
+    const int i = wi + (k * 32 + lane) * PX;
+    if (i >= p.pixels) continue;
+    uint32_t out[1][12];
+    convert_chunk<FMT, LAYOUT, DTYPE, BGR, ARITH>(p.mat, p.sb, yw[k], uw[k], vw[k], out);
+    if constexpr (LAYOUT == B2_NCHW) {
+      const bool whole = i >= 0 && i + PX <= p.pixels;
+#pragma unroll
+      for (int s = 0; s < 3; ++s) {
+        uint8_t* q = dstb + (s * p.dst_plane_stride + i) * ESZ;
+        if (whole) {
+          __stcs(reinterpret_cast<uint4*>(q), make_uint4(out[0][4 * s], out[0][4 * s + 1],
+                                                         out[0][4 * s + 2], out[0][4 * s + 3]));
+        } else {
+#pragma unroll
+          for (int b = 0; b < 16; ++b) {
+            const int px = i + b / ESZ;
+            if (px >= 0 && px < p.pixels) q[b] = (uint8_t)(out[0][4 * s + b / 4] >> (8 * (b % 4)));
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 3; ++j)
+        *reinterpret_cast<uint4*>(wsm + (k * 32 + lane) * 48 + 16 * j) =
+            make_uint4(out[0][4 * j], out[0][4 * j + 1], out[0][4 * j + 2], out[0][4 * j + 3]);
+    }
+  }
+  if constexpr (LAYOUT == B2_NHWC) {
+    // The warp's CH x 32 x 48 bytes are contiguous in the destination and start on a multiple
+    // of 16: the aligned interior leaves as one bulk copy, the ragged ends of a frame byte by byte.
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    const long long first = 3LL * ESZ * wi, total = 3LL * ESZ * p.pixels;  // bytes of the frame
+    const long long lo = first > 0 ? first : 0;
+    const long long hi = first + CH * 32 * 48 < total ? first + CH * 32 * 48 : total;
+    uint8_t* g = dstb + lo;
+    const unsigned char* data = wsm + (lo - first);  // congruent to g modulo 16
+    const int nbytes = (int)(hi - lo);
+    int head = (int)((16 - ((uintptr_t)g & 15)) & 15);
+    if (head > nbytes) head = nbytes;
+    const int body = (nbytes - head) & ~15;
+    const int tail0 = head + body;
+    if (lane < head) g[lane] = data[lane];
+    if (tail0 + lane < nbytes) g[tail0 + lane] = data[tail0 + lane];
+    if (lane == 0 && body > 0) {
+      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(g + head),
+                   "r"(smem_addr(data + head)), "r"((uint32_t)body)
+                   : "memory");
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      // the staging buffer must outlive the engine's reads of it
+      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    }
+  }
+}
+
 // ---- any-alignment path ------------------------------------------------------------------------
 // Rows on arbitrary byte boundaries (packed frames whose width is not a multiple of 16: 854x480,
 // 1366x768; crops; surfaces at odd addresses), any width >= 2.  The thread layout is the vector
@@ -496,9 +691,10 @@ __global__ void __launch_bounds__(kAnyThreads, kAnyMinBlocks) dense_any_kernel(c
 }
 
 inline bool mult(long long v, long long m) { return v % m == 0; }
+enum { kPathAny = 0, kPathVec = 1, kPathFlat = 2 };
 
 template <int FMT, int LAYOUT, int DTYPE, bool BGR, bool TABLE, int ARITH>
-int launch_t(const DenseLaunch& L, const DenseParams& p, bool vec, cudaStream_t stream) {
+int launch_t(const DenseLaunch& L, const DenseParams& p, int path, cudaStream_t stream) {
   using T = typename OutT<DTYPE>::type;
   constexpr int PX = 16 / (int)sizeof(T);
   const int He = L.height & ~1;
@@ -516,7 +712,16 @@ int launch_t(const DenseLaunch& L, const DenseParams& p, bool vec, cudaStream_t 
       if (p.v) q.v = p.v + (long long)n0 * p.uv_frame_stride;
     }
     q.dst = static_cast<T*>(p.dst) + (long long)n0 * p.dst_frame_stride;
-    if (vec) {
+    if (path == kPathFlat) {
+      if constexpr (!TABLE) {
+        // chunk 0 may start up to PX - 1 pixels before the frame: one chunk more than the pixels
+        const long long chunks = ((long long)p.pixels + PX - 1) / PX + 1;
+        const int per_cta = kFlatThreads * kFlatChunks;
+        dim3 grid((unsigned)((chunks + per_cta - 1) / per_cta), 1, nn);
+        const size_t smem = LAYOUT == B2_NHWC ? (size_t)per_cta * 48 : 0;
+        dense_flat_kernel<FMT, LAYOUT, DTYPE, BGR, ARITH><<<grid, kFlatThreads, smem, stream>>>(q);
+      }
+    } else if (path == kPathVec) {
       const int chunks = (L.width + PX - 1) / PX;
       int bx = ((chunks + 31) / 32) * 32;
       if (bx > kDenseThreads) bx = kDenseThreads;
@@ -539,25 +744,25 @@ int launch_t(const DenseLaunch& L, const DenseParams& p, bool vec, cudaStream_t 
 }
 
 template <int FMT, int LAYOUT, int DTYPE, int ARITH>
-int launch_fld(const DenseLaunch& L, const DenseParams& p, bool vec, cudaStream_t s) {
+int launch_fld(const DenseLaunch& L, const DenseParams& p, int path, cudaStream_t s) {
   const bool bgr = L.order == B2_BGR, table = L.y_table != nullptr;
-  if (bgr) return table ? launch_t<FMT, LAYOUT, DTYPE, true, true, ARITH>(L, p, vec, s)
-                        : launch_t<FMT, LAYOUT, DTYPE, true, false, ARITH>(L, p, vec, s);
-  return table ? launch_t<FMT, LAYOUT, DTYPE, false, true, ARITH>(L, p, vec, s)
-               : launch_t<FMT, LAYOUT, DTYPE, false, false, ARITH>(L, p, vec, s);
+  if (bgr) return table ? launch_t<FMT, LAYOUT, DTYPE, true, true, ARITH>(L, p, path, s)
+                        : launch_t<FMT, LAYOUT, DTYPE, true, false, ARITH>(L, p, path, s);
+  return table ? launch_t<FMT, LAYOUT, DTYPE, false, true, ARITH>(L, p, path, s)
+               : launch_t<FMT, LAYOUT, DTYPE, false, false, ARITH>(L, p, path, s);
 }
 template <int FMT, int LAYOUT, int ARITH>
-int launch_fla(const DenseLaunch& L, const DenseParams& p, bool vec, cudaStream_t s) {
+int launch_fla(const DenseLaunch& L, const DenseParams& p, int path, cudaStream_t s) {
   switch (L.dtype) {
-    case B2_U8: return launch_fld<FMT, LAYOUT, B2_U8, ARITH>(L, p, vec, s);
-    case B2_F32: return launch_fld<FMT, LAYOUT, B2_F32, ARITH>(L, p, vec, s);
-    default: return launch_fld<FMT, LAYOUT, B2_BF16, ARITH>(L, p, vec, s);
+    case B2_U8: return launch_fld<FMT, LAYOUT, B2_U8, ARITH>(L, p, path, s);
+    case B2_F32: return launch_fld<FMT, LAYOUT, B2_F32, ARITH>(L, p, path, s);
+    default: return launch_fld<FMT, LAYOUT, B2_BF16, ARITH>(L, p, path, s);
   }
 }
 template <int FMT, int LAYOUT>
-int launch_fl(const DenseLaunch& L, const DenseParams& p, bool vec, cudaStream_t s) {
-  return L.arith == B2_ARITH_SWSCALE ? launch_fla<FMT, LAYOUT, B2_ARITH_SWSCALE>(L, p, vec, s)
-                                     : launch_fla<FMT, LAYOUT, B2_ARITH_REFERENCE>(L, p, vec, s);
+int launch_fl(const DenseLaunch& L, const DenseParams& p, int path, cudaStream_t s) {
+  return L.arith == B2_ARITH_SWSCALE ? launch_fla<FMT, LAYOUT, B2_ARITH_SWSCALE>(L, p, path, s)
+                                     : launch_fla<FMT, LAYOUT, B2_ARITH_REFERENCE>(L, p, path, s);
 }
 
 }  // namespace
@@ -595,11 +800,26 @@ int launch_dense(const DenseLaunch& L, cudaStream_t stream) {
           mult(L.y_frame_stride, px) && mult(L.uv_frame_stride, uvb);
     if (L.src_format == B2_SRC_I420) vec = vec && mult((long long)(uintptr_t)L.v, uvb);
   }
-  if (L.src_format == B2_SRC_NV12)
-    return L.layout == B2_NCHW ? launch_fl<B2_SRC_NV12, B2_NCHW>(L, p, vec, stream)
-                               : launch_fl<B2_SRC_NV12, B2_NHWC>(L, p, vec, stream);
-  return L.layout == B2_NCHW ? launch_fl<B2_SRC_I420, B2_NCHW>(L, p, vec, stream)
-                             : launch_fl<B2_SRC_I420, B2_NHWC>(L, p, vec, stream);
+  int path = vec ? kPathVec : kPathAny;
+  // Packed frames (rows back to back on both sides, even width of at least one chunk, every frame
+  // of the destination on a multiple of two elements, planes a multiple of 16 bytes apart).
+  const long long He = L.height & ~1;
+  const bool nv12 = L.src_format == B2_SRC_NV12;
+  if (!vec && !table && L.width % 2 == 0 && L.width >= px && L.y_pitch == L.width &&
+      L.uv_pitch == (nv12 ? L.width : L.width / 2) && L.width * He < (1LL << 30) &&
+      L.dst_row_pitch == (L.layout == B2_NCHW ? L.width : 3LL * L.width) &&
+      mult((long long)(uintptr_t)L.dst, 2 * esz) && mult(L.dst_frame_stride, 2) &&
+      (L.layout != B2_NCHW || mult(L.dst_plane_stride * esz, 16))) {
+    path = kPathFlat;
+    p.pixels = (int)(L.width * He);
+    p.chroma_limit = (int)(nv12 ? L.width * (He / 2) : (L.width / 2) * (He / 2));
+    p.w_recip = (unsigned)((1ULL << 32) / (unsigned)L.width);
+  }
+  if (nv12)
+    return L.layout == B2_NCHW ? launch_fl<B2_SRC_NV12, B2_NCHW>(L, p, path, stream)
+                               : launch_fl<B2_SRC_NV12, B2_NHWC>(L, p, path, stream);
+  return L.layout == B2_NCHW ? launch_fl<B2_SRC_I420, B2_NCHW>(L, p, path, stream)
+                             : launch_fl<B2_SRC_I420, B2_NHWC>(L, p, path, stream);
 }
 
 }  // namespace b2

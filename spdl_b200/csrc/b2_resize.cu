@@ -70,7 +70,6 @@ constexpr int kResizeWarps = kResizeThreads / 32;
 // 128-thread CTAs, 8 resident per SM (32 warps, no spills): measured best; larger CTAs or
 // tighter register caps (more warps, spills) were slower.
 constexpr int kResizeMinBlocks = 8;
-constexpr int kMaxSpans = kRows * 6;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);

@@ -1,5 +1,6 @@
-"""Frames whose rows start on arbitrary byte boundaries (widths that are not a multiple of 16):
-the window and shift kernels against the oracle, at real-world sizes."""
+"""Frames whose rows start on arbitrary byte boundaries (widths that are not a multiple of 16,
+sources and destinations at odd offsets): the kernel for packed frames of any even width and the
+any-alignment kernel against the oracle, at real-world sizes and at sizes of a chunk or two."""
 
 import numpy as np
 import pytest
@@ -12,7 +13,8 @@ pytestmark = pytest.mark.gpu
 MEAN, STD = (0.485, 0.456, 0.406), (0.229, 0.224, 0.225)
 
 
-@pytest.mark.parametrize("w,h", [(854, 480), (426, 240), (1918, 20), (1366, 18), (30, 6)])
+@pytest.mark.parametrize("w,h", [(854, 480), (426, 240), (1918, 20), (1366, 18), (30, 6), (16, 2),
+                                 (18, 4), (22, 12), (46, 6), (130, 10), (8, 4), (4, 2)])
 @pytest.mark.parametrize("fmt", ["nv12", "i420"])
 @pytest.mark.parametrize("layout,dtype", [("NCHW", "uint8"), ("NHWC", "uint8"),
                                           ("NHWC", "bfloat16"), ("NCHW", "float32")])
@@ -53,11 +55,11 @@ def test_unaligned_widths(cuda_cfg, w, h, fmt, layout, dtype):
 @pytest.mark.parametrize("w,h", [(31, 6), (854, 10), (1918, 4), (50, 8)])
 @pytest.mark.parametrize("layout", ["NCHW", "NHWC"])
 @pytest.mark.parametrize("dtype", ["uint8", "bfloat16", "float32"])
-@pytest.mark.parametrize("dst_off", [1, 2])
+@pytest.mark.parametrize("dst_off", [1, 2, 6])
 def test_destination_on_odd_elements(cuda_cfg, w, h, layout, dtype, dst_off):
     """Through the C ABI with a destination that starts ``dst_off`` elements into its buffer
-    (odd: the general kernel; even but unaligned: the window kernel), odd widths included.  The
-    bytes around the output and the trailing odd column keep their sentinel value."""
+    (odd offsets and odd widths: the any-alignment kernel; even ones: the kernel for packed
+    frames).  The bytes around the output and the trailing odd column keep their sentinel value."""
     import ctypes
 
     import torch
