@@ -22,7 +22,7 @@
  *   - No source or destination pointer, pitch, stride or width needs any alignment.
  *     The kernels read whole aligned segments, though: a source buffer must allow
  *     reads of every aligned 16-byte segment that holds at least one byte of it
- *     (b2_convert_resize) resp. every aligned 4-byte word (b2_convert_dense on rows
+ *     (b2_convert_resize) resp. every aligned 8-byte word (b2_convert_dense on rows
  *     that are not 16-byte aligned).  Any allocation that starts and ends on such
  *     boundaries -- cudaMalloc, every framework allocator -- satisfies this; a
  *     sub-allocation whose last bytes share a 16-byte segment with an unmapped page

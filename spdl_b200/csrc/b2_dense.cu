@@ -48,6 +48,7 @@ struct DenseParams {
   int pixels;         // width * height: luma bytes of a frame
   int chroma_limit;   // bytes of a chroma plane of a frame
   unsigned w_recip;   // 2^32 / width, rounded down: pixel index -> row by multiply-high
+  int rows_per_warp;  // rows a warp's run of consecutive pixels can touch
 };
 
 // Load NB bytes into ceil(NB/4) words.  Streaming (read-once) cache hint.
@@ -380,47 +381,61 @@ __device__ __forceinline__ void convert_chunk(const ColorMat& m, const ScaleBias
 //          odd row the next chroma row follows in memory, and nothing is to be done);
 //   ends:  the first and the last chunk of a frame hold pixels outside it; their bytes are not
 //          stored (interleaved: the ragged ends of the warp's staged bytes go out byte by byte).
+// 128 threads, two chunks per lane (a warp converts 64 consecutive chunks), 12 CTAs per SM:
+// measured best (one or three chunks per lane, CTAs of 64 threads and 10 or 16 CTAs per SM are
+// 1-8 % slower).
 constexpr int kFlatThreads = 128;
-#ifndef B2_FLAT_MB
-#define B2_FLAT_MB 10
-#endif
-#ifndef B2_FLAT_CH
-#define B2_FLAT_CH 2
-#endif
-constexpr int kFlatMinBlocks = B2_FLAT_MB;
-constexpr int kFlatChunks = B2_FLAT_CH;  // chunks per lane: a warp converts 64 consecutive chunks
+constexpr int kFlatMinBlocks = 12;
+constexpr int kFlatChunks = 2;  // chunks per lane: a warp converts 64 consecutive chunks
 
-// load_window for a window known to lie at least 4 bytes inside its plane at both ends.
+// load_window for a window that lies at least 8 bytes inside its plane at both ends.  Sixteen
+// bytes come as the three aligned 8-byte vectors that cover them (fewer, wider requests than five
+// 4-byte words: the lanes of a warp are 16 bytes apart, so every load instruction touches four
+// cache lines whatever its width), then a word select and a funnel shift per word; no branch, so
+// the loads of all the windows of a lane are in flight together.
 template <int NB>
 __device__ __forceinline__ void load_window_inside(const uint8_t* base, int x, uint32_t* w) {
   constexpr int NWD = (NB + 3) / 4;
   const uintptr_t addr = (uintptr_t)base + (intptr_t)x;
-  const int a = (int)(addr & 3);
-  const uint32_t* q = reinterpret_cast<const uint32_t*>(addr - a);
-  uint32_t v[NWD + 1];
+  if constexpr (NB == 16) {
+    const int a = (int)(addr & 7);
+    const uint2* q = reinterpret_cast<const uint2*>(addr - a);
+    const uint2 v0 = __ldg(q), v1 = __ldg(q + 1), v2 = __ldg(q + 2);
+    const bool up = a >= 4;  // the window starts in the upper word of v0
+    const uint32_t t0 = up ? v0.y : v0.x, t1 = up ? v1.x : v0.y, t2 = up ? v1.y : v1.x,
+                   t3 = up ? v2.x : v1.y, t4 = up ? v2.y : v2.x;
+    const int sh = (a & 3) * 8;
+    w[0] = __funnelshift_r(t0, t1, sh);
+    w[1] = __funnelshift_r(t1, t2, sh);
+    w[2] = __funnelshift_r(t2, t3, sh);
+    w[3] = __funnelshift_r(t3, t4, sh);
+  } else {
+    const int a = (int)(addr & 3);
+    const uint32_t* q = reinterpret_cast<const uint32_t*>(addr - a);
+    uint32_t v[NWD + 1];
 #pragma unroll
-  for (int i = 0; i <= NWD; ++i) v[i] = __ldg(q + i);
+    for (int i = 0; i <= NWD; ++i) v[i] = __ldg(q + i);
 #pragma unroll
-  for (int i = 0; i < NWD; ++i) w[i] = __funnelshift_r(v[i], v[i + 1], a * 8);
+    for (int i = 0; i < NWD; ++i) w[i] = __funnelshift_r(v[i], v[i + 1], a * 8);
+  }
 }
 
 // Luma and chroma words of the chunk that starts at pixel i of the frame (i < p.pixels; negative
-// for the partial chunk in front of the frame).
-template <int FMT, int PX, int NW, int UVW>
+// for the partial chunk in front of the frame).  INSIDE: the caller knows that the chunk lies at
+// least four rows away from both ends of the frame, so no window needs a bounds check.
+template <int FMT, int PX, bool INSIDE, int NW, int UVW>
 __device__ __forceinline__ void flat_load(const DenseParams& p, const uint8_t* yb,
                                           const uint8_t* ub, const uint8_t* vb, int i,
                                           uint32_t (&yw)[1][NW], uint32_t (&uw)[UVW],
                                           uint32_t (&vw)[UVW]) {
   constexpr int CDIV = FMT == B2_SRC_NV12 ? 1 : 2;  // luma columns per chroma byte column
   constexpr int UVB = PX / CDIV;
-  int y = 0, x = i;  // a negative i belongs to the partial chunk in front of row 0
-  if (i > 0) {
-    y = (int)__umulhi((unsigned)i, p.w_recip);
-    x = i - y * p.width;
-    if (x >= p.width) {  // the rounded-down reciprocal is short by at most one
-      x -= p.width;
-      ++y;
-    }
+  // row and column of pixel i; a negative i belongs to the partial chunk in front of row 0
+  int y = INSIDE || i > 0 ? (int)__umulhi((unsigned)i, p.w_recip) : 0;
+  int x = i - y * p.width;
+  if (x >= p.width) {  // the rounded-down reciprocal is short by at most one
+    x -= p.width;
+    ++y;
   }
   const int cw = p.width / CDIV;               // bytes of a chroma row
   const int ca = (y >> 1) * cw + x / CDIV;     // x is even
@@ -429,7 +444,8 @@ __device__ __forceinline__ void flat_load(const DenseParams& p, const uint8_t* y
   uint32_t u2[UVW], v2[UVW];
   (void)vw;
   (void)v2;
-  if (i >= 4 && i + PX + 4 <= p.pixels && ca >= cw + 4 && ca + UVB + 4 <= p.chroma_limit) {
+  if (INSIDE ||
+      (i >= 4 && i + PX + 4 <= p.pixels && ca >= cw + 4 && ca + UVB + 4 <= p.chroma_limit)) {
     load_window_inside<PX>(yb, i, yw[0]);
     load_window_inside<UVB>(ub, ca, uw);
     if constexpr (FMT == B2_SRC_I420) load_window_inside<UVB>(vb, ca, vw);
@@ -488,20 +504,30 @@ __global__ void __launch_bounds__(kFlatThreads, kFlatMinBlocks) dense_flat_kerne
   const uint8_t* ub = p.u + (long long)n * p.uv_frame_stride;
   const uint8_t* vb = FMT == B2_SRC_I420 ? p.v + (long long)n * p.uv_frame_stride : nullptr;
   uint32_t yw[CH][1][NW], uw[CH][UVW], vw[CH][UVW];
+  // Four rows or more from both ends of the frame (the row estimate may be short by one), every
+  // chunk of the warp is whole and none of its windows needs a bounds check.
+  const int row0 = wi > 0 ? (int)__umulhi((unsigned)wi, p.w_recip) : 0;
+  const bool inside = row0 >= 4 && row0 + p.rows_per_warp + 8 <= p.height;
+  if (inside) {
 #pragma unroll
-  for (int k = 0; k < CH; ++k) {
-    const int i = wi + (k * 32 + lane) * PX;
-    if (i < p.pixels) flat_load<FMT, PX>(p, yb, ub, vb, i, yw[k], uw[k], vw[k]);
+    for (int k = 0; k < CH; ++k)
+      flat_load<FMT, PX, true>(p, yb, ub, vb, wi + (k * 32 + lane) * PX, yw[k], uw[k], vw[k]);
+  } else {
+#pragma unroll
+    for (int k = 0; k < CH; ++k) {
+      const int i = wi + (k * 32 + lane) * PX;
+      if (i < p.pixels) flat_load<FMT, PX, false>(p, yb, ub, vb, i, yw[k], uw[k], vw[k]);
+    }
   }
   unsigned char* wsm = flat_smem + warp * (CH * 32 * 48);
 #pragma unroll
   for (int k = 0; k < CH; ++k) {
     const int i = wi + (k * 32 + lane) * PX;
-    if (i >= p.pixels) continue;
+    if (!inside && i >= p.pixels) continue;
     uint32_t out[1][12];
     convert_chunk<FMT, LAYOUT, DTYPE, BGR, ARITH>(p.mat, p.sb, yw[k], uw[k], vw[k], out);
     if constexpr (LAYOUT == B2_NCHW) {
-      const bool whole = i >= 0 && i + PX <= p.pixels;
+      const bool whole = inside || (i >= 0 && i + PX <= p.pixels);
 #pragma unroll
       for (int s = 0; s < 3; ++s) {
         uint8_t* q = dstb + (s * p.dst_plane_stride + i) * ESZ;
@@ -814,6 +840,7 @@ int launch_dense(const DenseLaunch& L, cudaStream_t stream) {
     p.pixels = (int)(L.width * He);
     p.chroma_limit = (int)(nv12 ? L.width * (He / 2) : (L.width / 2) * (He / 2));
     p.w_recip = (unsigned)((1ULL << 32) / (unsigned)L.width);
+    p.rows_per_warp = (kFlatChunks * 32 * px + L.width - 1) / L.width + 1;
   }
   if (nv12)
     return L.layout == B2_NCHW ? launch_fl<B2_SRC_NV12, B2_NCHW>(L, p, path, stream)

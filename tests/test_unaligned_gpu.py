@@ -14,7 +14,8 @@ MEAN, STD = (0.485, 0.456, 0.406), (0.229, 0.224, 0.225)
 
 
 @pytest.mark.parametrize("w,h", [(854, 480), (426, 240), (1918, 20), (1366, 18), (30, 6), (16, 2),
-                                 (18, 4), (22, 12), (46, 6), (130, 10), (8, 4), (4, 2)])
+                                 (18, 4), (22, 12), (46, 6), (130, 10), (8, 4), (4, 2), (46, 64),
+                                 (18, 160), (130, 40)])
 @pytest.mark.parametrize("fmt", ["nv12", "i420"])
 @pytest.mark.parametrize("layout,dtype", [("NCHW", "uint8"), ("NHWC", "uint8"),
                                           ("NHWC", "bfloat16"), ("NCHW", "float32")])
