@@ -52,6 +52,8 @@ struct ResizeParams {
   float ch_scale[3], ch_bias[3];         // per colour channel; scale carries the 2^24 of kTapScale
   float ch_pad[3];                       // pad colour per channel, scaled by 2^-24 like the taps
   int span_cap;                          // bytes reserved per staged row span (multiple of 16)
+  int span_cap2;                         // I420: bytes reserved per staged row of the half-width
+                                         // planes (span_cap covers the first plane only)
   int vec_store;                         // 1: whole groups of four pixels may use vector stores
   int rows;                              // output rows per tile: 4, or 2 for wide sources
   int tiles;                             // tiles a CTA converts, one after the other
@@ -385,7 +387,10 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
                                         : xhi;
   // A descriptor wider than the caller's max_src_w would overrun the staging rows: such an image
   // is skipped (its output is left untouched) rather than allowed to write out of bounds.
-  if (bhi - blo + 15 > p.span_cap || cxhi - cxlo + 15 > p.span_cap) {
+  // I420's second and third plane have rows half as wide, and slots half as large
+  constexpr bool kHalfSlots = FMT == B2_SRC_I420;
+  if (bhi - blo + 15 > p.span_cap ||
+      cxhi - cxlo + 15 > (kHalfSlots ? p.span_cap2 : p.span_cap)) {
     report(B2_STATUS_IMAGE_TOO_WIDE);
     return;
   }
@@ -397,7 +402,9 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
   // of a warp read neighbouring entries, and the four weights of a group form one vector.
   const int groups = (p.out_w + 3) >> 2;
   const uint32_t sbase = smem_u32(smem);
-  const uint32_t xoffs = sbase + (uint32_t)(p.rows * kPlanes * p.span_cap);
+  const uint32_t xoffs =
+      sbase + (uint32_t)(kHalfSlots ? p.rows * (2 * p.span_cap + (kPlanes - 2) * p.span_cap2)
+                                    : p.rows * kPlanes * p.span_cap);
   const uint32_t xw = xoffs + 64u * (uint32_t)groups;
   const int warp = tid >> 5, lane = tid & 31;
   const int r = warp % p.rows;  // p.rows is 2 or 4: the output row of a tile this warp converts
@@ -469,7 +476,18 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
       const unsigned same = __match_any_sync(0xffffffffu, key);
       const int owner = __ffs(same) - 1;
       const bool fetch = active && owner == lane;
-      if (active) s_rows[sr].row[pl] = sbase + (uint32_t)(owner * p.span_cap + head);
+      // every lane owns a slot; with half-size slots the first-plane slots come first
+      uint32_t slot, owner_slot;
+      if constexpr (kHalfSlots) {
+        slot = sbase + (uint32_t)(pl < 2 ? (2 * sr + pl) * p.span_cap
+                                         : 2 * p.rows * p.span_cap +
+                                               ((kPlanes - 2) * sr + pl - 2) * p.span_cap2);
+        owner_slot = __shfl_sync(0xffffffffu, slot, owner);
+      } else {
+        slot = sbase + (uint32_t)(lane * p.span_cap);
+        owner_slot = sbase + (uint32_t)(owner * p.span_cap);
+      }
+      if (active) s_rows[sr].row[pl] = owner_slot + (uint32_t)head;
       if constexpr (FMT == B2_SRC_NV12) {
         const bool odd = __any_sync(0xffffffffu, active && pl >= 2 && (head & 1));
         if (lane == 0) s_odd_chroma = odd;
@@ -488,7 +506,7 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
         // byte of a touched row (true of any allocation that starts and ends on such boundaries).
         asm volatile(
             "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
-                "r"(sbase + (uint32_t)(lane * p.span_cap)),
+                "r"(slot),
             "l"(src + lo - head), "r"(bytes), "r"(smem_u32(&bar[0]))
             : "memory");
     }
@@ -678,18 +696,23 @@ int launch_resize(const b2_resize_args& a, cudaStream_t stream) {
   const long long row_bytes =
       a.src_format == B2_SRC_RGB_INTERLEAVED ? 3LL * a.max_src_w : (long long)a.max_src_w;
   const long long span = ((row_bytes + 2 + 15 + 15) / 16) * 16;
+  // the rows of I420's second and third plane are half as wide
+  const long long span2 =
+      a.src_format == B2_SRC_I420 ? (((a.max_src_w + 1LL) / 2 + 2 + 15 + 15) / 16) * 16 : span;
   const int planes = a.src_format == B2_SRC_NV12 ? 4 : (a.src_format == B2_SRC_RGB_INTERLEAVED ? 2 : 6);
+  const size_t per_row = (size_t)(2 * span + (planes - 2) * span2);  // staging per output row
   // per column 16 bytes of offsets + 4 bytes of weight, for whole groups of four columns
   const size_t table = (size_t)((a.out_w + 3) / 4) * 80;
   // Four output rows per CTA amortise the per-CTA work best; wide sources (4K rows) take two,
   // which halves the staging buffer and lets more CTAs share an SM.
-  p.rows = (size_t)kRows * planes * span + table > 40 * 1024 ? 2 : kRows;
-  const size_t smem = (size_t)p.rows * planes * span + table;
+  p.rows = (size_t)kRows * per_row + table > 40 * 1024 ? 2 : kRows;
+  const size_t smem = (size_t)p.rows * per_row + table;
   if (span >= 65536 || smem > 200 * 1024)
     return fail(B2_ERR_LIMIT,
                 "max_src_w %d and out_w %d need %zu bytes of staging; the limit is %d bytes",
                 a.max_src_w, a.out_w, smem, 200 * 1024);
   p.span_cap = (int)span;
+  p.span_cap2 = (int)span2;
   // Tiles per CTA: enough to spread the per-image work of a CTA over many rows, few enough to
   // leave every SM several CTAs' worth of an image batch (148 SMs x 8 resident CTAs).
   p.tiles = 8;
