@@ -420,6 +420,39 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
   T* const dimg = static_cast<T*>(p.dst) + img;
   const MatPairs<ARITH> m(p.mat);  // the coefficients as register pairs, built once
 
+  // Where the staged span of plane slot pl (0/1: first plane, 2/3: second, 4/5: third; odd slots
+  // hold the lower tap row) starts for source row yrow: the 16-byte aligned address to copy from,
+  // the bytes to copy (a multiple of 16) and how far into them the span begins (head).  key
+  // identifies (plane, row) for finding spans that several output rows share.  With row maps the
+  // caller stored only the touched rows, back to back; a row the map does not cover is a hole:
+  // the span then stays inside the buffer (row 0) and the caller reports it.
+  auto span_start = [&](int yrow, int pl, long long& key, bool& hole, int& bytes,
+                        int& head) -> const uint8_t* {
+    const uint8_t* row;
+    int lo, n;
+    if (pl < 2) {
+      key = yrow;
+      int at = p.luma_map != nullptr ? __ldg(p.luma_map + yrow) : yrow;
+      hole = at < 0;
+      row = p.base + d.y_off + (size_t)max(at, 0) * d.y_pitch;
+      lo = blo;
+      n = bhi - blo;
+    } else {
+      const int plane = pl < 4 ? 1 : 2;
+      const int prow = kYuv ? yrow >> 1 : yrow;  // chroma planes are half height
+      key = ((long long)plane << 32) | (uint32_t)prow;
+      const int* map = kYuv ? p.chroma_map : p.luma_map;
+      int at = map != nullptr ? __ldg(map + prow) : prow;
+      hole = at < 0;
+      row = p.base + (plane == 1 ? d.u_off : d.v_off) + (size_t)max(at, 0) * d.uv_pitch;
+      lo = cxlo;
+      n = cxhi - cxlo;
+    }
+    head = (int)((uintptr_t)(row + lo) & 15);
+    bytes = (n + head + 15) & ~15;
+    return row + lo - head;
+  };
+
   // A CTA converts p.tiles consecutive tiles of p.rows output rows, one after the other through
   // the same staging buffer: what depends on the image only (descriptor, geometry, the column
   // table) is then worked out once for all of them.
@@ -435,42 +468,17 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
       const int oy = oy0 + sr;
       const bool active = lane < nspans && oy >= rin0 && oy < rin1;
       long long key = -1 - lane;  // unique for idle lanes
-      const uint8_t* src = nullptr;
-      int lo = 0, bytes = 0, head = 0;
+      const uint8_t* src = nullptr;  // 16-byte aligned start of the span in global memory
+      int bytes = 0, head = 0;
       if (active) {
         const Axis ay = axis_of(d.scale_y, (float)(d.crop_y + oy), d.src_h);
-        const int yrow = (pl & 1) ? ay.i1 : ay.i0;
         if (pl == 0) {
           s_rows[sr].wy0 = __fsub_rn(1.0f, ay.w1);
           s_rows[sr].wy1 = ay.w1;
         }
-        // with row maps the caller stored only the touched rows, back to back
-        if (pl < 2) {
-          key = yrow;
-          int at = p.luma_map != nullptr ? __ldg(p.luma_map + yrow) : yrow;
-          if (at < 0) {  // the map does not cover a row the geometry reads: stay in the buffer
-            at = 0;
-            if (p.status != nullptr) atomicOr(p.status, B2_STATUS_BAD_GEOMETRY);
-          }
-          src = p.base + d.y_off + (size_t)at * d.y_pitch;
-          lo = blo;
-          bytes = bhi - blo;
-        } else {
-          const int plane = pl < 4 ? 1 : 2;          // second / third plane
-          const int prow = kYuv ? yrow >> 1 : yrow;  // chroma planes are half height
-          key = ((long long)plane << 32) | (uint32_t)prow;
-          const int* map = kYuv ? p.chroma_map : p.luma_map;
-          int at = map != nullptr ? __ldg(map + prow) : prow;
-          if (at < 0) {
-            at = 0;
-            if (p.status != nullptr) atomicOr(p.status, B2_STATUS_BAD_GEOMETRY);
-          }
-          src = p.base + (plane == 1 ? d.u_off : d.v_off) + (size_t)at * d.uv_pitch;
-          lo = cxlo;
-          bytes = cxhi - cxlo;
-        }
-        head = (int)((uintptr_t)(src + lo) & 15);
-        bytes = (bytes + head + 15) & ~15;
+        bool hole;
+        src = span_start((pl & 1) ? ay.i1 : ay.i0, pl, key, hole, bytes, head);
+        if (hole && p.status != nullptr) atomicOr(p.status, B2_STATUS_BAD_GEOMETRY);
       }
       // the first lane holding a given (plane, source row) fetches it; the others alias its slot
       const unsigned same = __match_any_sync(0xffffffffu, key);
@@ -507,8 +515,24 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
         asm volatile(
             "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
                 "r"(slot),
-            "l"(src + lo - head), "r"(bytes), "r"(smem_u32(&bar[0]))
+            "l"(src), "r"(bytes), "r"(smem_u32(&bar[0]))
             : "memory");
+      // Ask for the next tile's rows in L2 while this one is converted, where a tile is short next
+      // to the latency of its copies: interleaved RGB (two long spans per output row; measured
+      // 4.5 % faster) and the two-row tiles of wide sources.  With the four-row tiles of the
+      // planar formats the extra work of this warp, on which the others wait, costs more than
+      // the shorter wait saves (3-5 % slower).
+      const int oyn = oy + p.rows;
+      if ((FMT == B2_SRC_RGB_INTERLEAVED || p.rows == 2) && tile + 1 < p.tiles &&
+          lane < p.rows * kPlanes && oyn >= rin0 && oyn < rin1) {
+        const Axis ay = axis_of(d.scale_y, (float)(d.crop_y + oyn), d.src_h);
+        long long k2;
+        bool hole;
+        int n2, h2;
+        const uint8_t* nxt = span_start((pl & 1) ? ay.i1 : ay.i0, pl, k2, hole, n2, h2);
+        if (!hole)
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(nxt), "r"(n2) : "memory");
+      }
     }
     if (tile == 0) {
       // the column table, while the first copies are in flight
