@@ -64,9 +64,19 @@ struct ResizeParams {
   int* status;                           // optional device word for B2_STATUS_* bits
   unsigned wait_limit;                   // polls of a bounded wait
   int debug_flags;
+  int prefetch;                          // 1: ask for the next tile's rows in L2 one tile ahead
 };
 
 constexpr int kRows = 4;  // output rows per CTA, at most
+
+// One staged row span as the staging warp locates it.
+struct SpanLoc {
+  const uint8_t* src;  // 16-byte aligned start in global memory
+  long long key;       // (plane, source row): equal keys are fetched once
+  int bytes, head;     // bytes to copy (a multiple of 16); offset of the span's first byte in them
+  float wy1;           // weight of the lower tap row
+  int active;
+};
 constexpr int kResizeThreads = 128;
 constexpr int kResizeWarps = kResizeThreads / 32;
 // 128-thread CTAs, 8 resident per SM (32 warps, no spills): measured best; larger CTAs or
@@ -320,6 +330,7 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
   __shared__ b2_image_desc sd;
   __shared__ RowInfo s_rows[kRows];
   __shared__ int s_odd_chroma;  // a staged interleaved-chroma row of this tile has an odd address
+  __shared__ SpanLoc s_next[32];  // the next tile's spans, per lane of the staging warp
   // bar[0]: the staged rows.  bar[1]: nothing ever arrives on it (B2_DEBUG_EXPIRE_WAIT).
   __shared__ __align__(8) unsigned long long bar[2];
 
@@ -389,6 +400,7 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
   // is skipped (its output is left untouched) rather than allowed to write out of bounds.
   // I420's second and third plane have rows half as wide, and slots half as large
   constexpr bool kHalfSlots = FMT == B2_SRC_I420;
+  constexpr bool kLocateAhead = FMT != B2_SRC_RGB_INTERLEAVED;
   if (bhi - blo + 15 > p.span_cap ||
       cxhi - cxlo + 15 > (kHalfSlots ? p.span_cap2 : p.span_cap)) {
     report(B2_STATUS_IMAGE_TOO_WIDE);
@@ -463,22 +475,38 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
     if (tile > 0) __syncthreads();  // every warp is done with the rows of the previous tile
     bool arrived = true;
     if (tid < 32) {
-      const int nspans = rows_here * kPlanes;
       const int sr = lane / kPlanes, pl = lane - sr * kPlanes;
-      const int oy = oy0 + sr;
-      const bool active = lane < nspans && oy >= rin0 && oy < rin1;
-      long long key = -1 - lane;  // unique for idle lanes
-      const uint8_t* src = nullptr;  // 16-byte aligned start of the span in global memory
-      int bytes = 0, head = 0;
-      if (active) {
-        const Axis ay = axis_of(d.scale_y, (float)(d.crop_y + oy), d.src_h);
-        if (pl == 0) {
-          s_rows[sr].wy0 = __fsub_rn(1.0f, ay.w1);
-          s_rows[sr].wy1 = ay.w1;
+      // Locating a span (tap rows, row maps, addresses) is the long part of staging, and the
+      // other warps wait for it.  For the planar formats (16-24 spans per tile) the spans of tile
+      // t + 1 are therefore located while the copies of tile t are in flight and kept in shared
+      // memory (one entry per lane, read back by the lane that wrote it), so that a tile's
+      // copies start as soon as its buffer is free: 1.5 % faster.  Interleaved RGB (two long
+      // spans per output row) gains nothing from that but 4.5 % from having the next tile's rows
+      // fetched into L2 early, which in turn costs the planar formats' four-row tiles 2-3 %.
+      auto locate = [&](int oy) {
+        SpanLoc L;
+        L.src = nullptr;
+        L.key = -1 - lane;  // unique for idle lanes
+        L.bytes = L.head = 0;
+        L.wy1 = 0.0f;
+        L.active = lane < p.rows * kPlanes && oy >= rin0 && oy < rin1;
+        if (L.active) {
+          const Axis ay = axis_of(d.scale_y, (float)(d.crop_y + oy), d.src_h);
+          L.wy1 = ay.w1;
+          bool hole;
+          L.src = span_start((pl & 1) ? ay.i1 : ay.i0, pl, L.key, hole, L.bytes, L.head);
+          if (hole && p.status != nullptr) atomicOr(p.status, B2_STATUS_BAD_GEOMETRY);
         }
-        bool hole;
-        src = span_start((pl & 1) ? ay.i1 : ay.i0, pl, key, hole, bytes, head);
-        if (hole && p.status != nullptr) atomicOr(p.status, B2_STATUS_BAD_GEOMETRY);
+        return L;
+      };
+      const SpanLoc cur = tile == 0 || !kLocateAhead ? locate(oy0 + sr) : s_next[lane];
+      const bool active = cur.active;
+      const long long key = cur.key;
+      const uint8_t* const src = cur.src;  // 16-byte aligned start of the span in global memory
+      const int bytes = cur.bytes, head = cur.head;
+      if (active && pl == 0) {
+        s_rows[sr].wy0 = __fsub_rn(1.0f, cur.wy1);
+        s_rows[sr].wy1 = cur.wy1;
       }
       // the first lane holding a given (plane, source row) fetches it; the others alias its slot
       const unsigned same = __match_any_sync(0xffffffffu, key);
@@ -517,21 +545,13 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
                 "r"(slot),
             "l"(src), "r"(bytes), "r"(smem_u32(&bar[0]))
             : "memory");
-      // Ask for the next tile's rows in L2 while this one is converted, where a tile is short next
-      // to the latency of its copies: interleaved RGB (two long spans per output row; measured
-      // 4.5 % faster) and the two-row tiles of wide sources.  With the four-row tiles of the
-      // planar formats the extra work of this warp, on which the others wait, costs more than
-      // the shorter wait saves (3-5 % slower).
-      const int oyn = oy + p.rows;
-      if ((FMT == B2_SRC_RGB_INTERLEAVED || p.rows == 2) && tile + 1 < p.tiles &&
-          lane < p.rows * kPlanes && oyn >= rin0 && oyn < rin1) {
-        const Axis ay = axis_of(d.scale_y, (float)(d.crop_y + oyn), d.src_h);
-        long long k2;
-        bool hole;
-        int n2, h2;
-        const uint8_t* nxt = span_start((pl & 1) ? ay.i1 : ay.i0, pl, k2, hole, n2, h2);
-        if (!hole)
-          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(nxt), "r"(n2) : "memory");
+      if ((kLocateAhead || p.prefetch) && tile + 1 < p.tiles && oy0 + p.rows < p.out_h) {
+        const SpanLoc nxt = locate(oy0 + p.rows + sr);
+        if constexpr (kLocateAhead) s_next[lane] = nxt;
+        // ... and, where a tile is short next to the latency of its copies, asked for in L2
+        if (p.prefetch && nxt.active)
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(nxt.src), "r"(nxt.bytes)
+                       : "memory");
       }
     }
     if (tile == 0) {
@@ -737,6 +757,7 @@ int launch_resize(const b2_resize_args& a, cudaStream_t stream) {
                 a.max_src_w, a.out_w, smem, 200 * 1024);
   p.span_cap = (int)span;
   p.span_cap2 = (int)span2;
+  p.prefetch = a.src_format == B2_SRC_RGB_INTERLEAVED || p.rows == 2;
   // Tiles per CTA: enough to spread the per-image work of a CTA over many rows, few enough to
   // leave every SM several CTAs' worth of an image batch (148 SMs x 8 resident CTAs).
   p.tiles = 8;
