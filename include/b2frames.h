@@ -260,7 +260,10 @@ B2_API int b2_touched_rows(const b2_image_desc* desc, int src_format, int out_h,
  * src + f * src_frame_stride + rows[i] * src_pitch to dst + f * dst_frame_stride + i * row_bytes.
  * It takes the place of the whole-frame copy with which the reference batches decoded frames
  * (src/libspdl/core/detail/ffmpeg/conversion.cpp:171-216) when only the touched rows are to be
- * uploaded; dst is typically page-locked. */
+ * uploaded; dst is typically page-locked.  With num_rows = 1, rows = {0} and row_bytes = the
+ * frame size it is the whole-frame staging copy.  Batches of several MiB are cut into ranges for
+ * several host threads (B2_HOST_COPY_THREADS; default half the hardware threads, at most 8), and
+ * consecutive rows of a tightly pitched source go as one memcpy. */
 B2_API int b2_copy_rows(void* dst, int64_t dst_frame_stride, const void* src, int64_t src_frame_stride,
                  int64_t src_pitch, const int32_t* rows, int num_rows, int64_t row_bytes,
                  int num_frames);

@@ -3,7 +3,10 @@
 #include <cstdarg>
 #include <cstddef>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
+#include <thread>
+#include <vector>
 
 #include "b2_common.cuh"
 
@@ -357,6 +360,18 @@ B2_API int b2_touched_rows(const b2_image_desc* d, int src_format, int out_h, in
   return B2_OK;
 }
 
+// Host threads a large b2_copy_rows call may use: B2_HOST_COPY_THREADS, else half the hardware
+// threads, eight at most (callers are pipeline worker threads, several at a time).
+static long long host_copy_threads() {
+  if (const char* e = std::getenv("B2_HOST_COPY_THREADS")) {
+    const long long v = std::atoll(e);
+    if (v >= 1) return v < 64 ? v : 64;
+  }
+  const unsigned hw = std::thread::hardware_concurrency();
+  const long long half = hw / 2;
+  return half < 1 ? 1 : (half > 8 ? 8 : half);
+}
+
 B2_API int b2_copy_rows(void* dst, int64_t dst_frame_stride, const void* src, int64_t src_frame_stride,
                  int64_t src_pitch, const int32_t* rows, int num_rows, int64_t row_bytes,
                  int num_frames) {
@@ -368,12 +383,43 @@ B2_API int b2_copy_rows(void* dst, int64_t dst_frame_stride, const void* src, in
   if (!dst || !src || !rows) return fail(B2_ERR_INVALID, "null pointer argument");
   for (int i = 0; i < num_rows; ++i)
     if (rows[i] < 0) return fail(B2_ERR_INVALID, "rows[%d] = %d is negative", i, rows[i]);
-  for (int f = 0; f < num_frames; ++f) {
-    char* d = static_cast<char*>(dst) + (long long)f * dst_frame_stride;
-    const char* s0 = static_cast<const char*>(src) + (long long)f * src_frame_stride;
-    for (int i = 0; i < num_rows; ++i)
-      memcpy(d + (long long)i * row_bytes, s0 + (long long)rows[i] * src_pitch, (size_t)row_bytes);
+  // (frame, row) items in frame-major order, cut into one contiguous range per thread; inside a
+  // range, rows that follow one another in the source and in the destination go as one memcpy.
+  const long long items = (long long)num_frames * num_rows;
+  auto copy_range = [=](long long first, long long last) {
+    long long it = first;
+    while (it < last) {
+      const long long f = it / num_rows;
+      const int i = (int)(it - f * num_rows);
+      const long long frame_end = (f + 1) * (long long)num_rows < last ? (f + 1) * (long long)num_rows : last;
+      int run = 1;
+      if (src_pitch == row_bytes)
+        while (it + run < frame_end && rows[i + run] == rows[i] + run) ++run;
+      memcpy(static_cast<char*>(dst) + f * dst_frame_stride + (long long)i * row_bytes,
+             static_cast<const char*>(src) + f * src_frame_stride + (long long)rows[i] * src_pitch,
+             (size_t)row_bytes * run);
+      it += run;
+    }
+  };
+  const long long total = items * row_bytes;
+  long long threads = total / (2LL << 20);  // a thread per 2 MiB at least
+  const long long cap = host_copy_threads();
+  if (threads > cap) threads = cap;
+  if (threads > items) threads = items;
+  if (threads <= 1) {
+    copy_range(0, items);
+    return B2_OK;
   }
+  std::vector<std::thread> pool;
+  pool.reserve((size_t)threads - 1);
+  try {
+    for (long long t = 1; t < threads; ++t)
+      pool.emplace_back(copy_range, items * t / threads, items * (t + 1) / threads);
+  } catch (...) {  // no more threads to be had: this one does what the missing ones would have
+    copy_range(items * ((long long)pool.size() + 1) / threads, items);
+  }
+  copy_range(0, items / threads);
+  for (auto& th : pool) th.join();
   return B2_OK;
 }
 

@@ -45,9 +45,13 @@ class FrameStage:
     over PCIe, only the source rows the geometry reads -- a quarter of a 4K frame that becomes
     224x224, four fifths of a 720p frame that becomes 256x256 -- instead of whole frames; the
     kernel finds the rows through the maps of :func:`touched_rows`.  The result is identical.
-    ``sparse_upload="auto"`` does so when the geometry reads less than half of a frame's bytes
-    (measured on a B200 host: 3.3 times the frames per second for 4K -> 224x224, but 0.8 times
-    for 720p -> 256x256, where packing 81 % of the rows costs more than sending all of them).
+    ``sparse_upload="auto"`` does so when the geometry reads less than 85 % of a frame's bytes.
+    Frames in pageable memory are first copied into the page-locked staging buffer by several
+    host threads (``b2_copy_rows``; whole frames or the touched rows) and uploaded from there
+    asynchronously; that copy, at about 30 GB/s, is what bounds the stage (measured on a B200
+    host, 16 cores, two worker threads: 4K -> 224x224 2.4 k frames/s whole, 5-6 k sparse; 720p ->
+    256x256 22 k whole, 24-26 k sparse; the driver's own staging of pageable sources gave 0.8 k
+    and 7 k).
     """
 
     def __init__(self, *, src_format: str = "i420", layout: str = "NCHW", dtype: str = "float32",
@@ -98,7 +102,8 @@ class FrameStage:
                                    f"{torch.cuda.device_count()} CUDA device(s).")
             stream = torch.cuda.Stream(torch.device("cuda", index))
             st = {"stream": stream, "cfg": cuda_config(index, stream=stream.cuda_stream),
-                  "cache": [None] * self._num_caches, "descs": {}}
+                  "cache": [None] * self._num_caches, "descs": {},
+                  "uploads": {"sparse": 0, "whole": 0}}  # calls of this thread by upload kind
             self._local.state = st
         return st
 
@@ -162,6 +167,20 @@ class FrameStage:
                                 crows.ctypes.data, nc, cw, n))
         return CPUBuffer((need,), "u", 1, store)
 
+    def _stage_whole(self, st, frames: np.ndarray) -> CPUBuffer:
+        """Copy a batch of pageable frames into the thread's page-locked staging buffer (several
+        host threads for large batches), from where the upload runs asynchronously at the
+        link's rate; the driver's own staging of a pageable source is several times slower."""
+        need = frames.nbytes
+        store = st.get("pinned")
+        if store is None or store.size < need:
+            store = st["pinned"] = CPUStorage(max(need, 1 << 20), pin_memory=True)
+        n, fb = frames.shape[0], frames.strides[0]
+        one = np.zeros(1, np.int32)  # every frame is one "row"
+        _lib.check(_lib.lib().b2_copy_rows(store.data_ptr, fb, frames.ctypes.data, fb, fb,
+                                           one.ctypes.data, 1, fb, n))
+        return CPUBuffer(frames.shape, "u", 1, store)
+
     @staticmethod
     def _upload(view, cfg: CUDAConfig):
         """Host frames to the device on the thread's stream.  Page-locked sources are queued
@@ -197,12 +216,13 @@ class FrameStage:
         plan = None
         if self._sparse and not (w % 2 or h % 2):
             plan = self._sparse_plan(st, n, w, h)
-            if self._sparse == "auto" and plan["fraction"] >= 0.5:
-                plan = None  # packing most of the rows costs more than sending all of them
+            if self._sparse == "auto" and plan["fraction"] >= 0.85:
+                plan = None  # nearly every row is read: one copy per frame is cheaper
         elif self._sparse is True:
             raise RuntimeError(f"sparse_upload needs even frame sizes. Found: {w}x{h}")
         if plan is not None:
             host = np.ascontiguousarray(np.asarray(frames).reshape(shape))
+            st["uploads"]["sparse"] += 1
             dev = self._upload(self._gather_rows(st, host, plan, w, h), cfg)
             result = convert_resize(dev, plan["descs"], out_size=plan["out"], max_src_w=w,
                                     device_config=cfg, row_maps=plan["maps"], sync=True,
@@ -217,6 +237,9 @@ class FrameStage:
             view = CPUBuffer(shape, frames.elem_class, frames.depth, frames.storage)
         else:
             view = np.ascontiguousarray(frames).reshape(shape)
+            if view.dtype == np.uint8 and view.nbytes:
+                view = self._stage_whole(st, view)
+        st["uploads"]["whole"] += 1
         dev = self._upload(view, cfg)
         if self._resizing:
             descs, out = self._descs_for(st, n, w, h)

@@ -462,6 +462,33 @@ def test_touched_rows_of_the_benchmark_geometries():
         io.touched_rows(bad[0], src_format="rgb24", out_h=10)
 
 
+@pytest.mark.parametrize("threads", ["1", "3", "8"])
+@pytest.mark.parametrize("pitch_pad", [0, 48])
+def test_copy_rows_large_batches_over_several_threads(monkeypatch, threads, pitch_pad):
+    """Batches of more than a few MiB are cut into ranges for several host threads, and runs of
+    consecutive rows of a tightly pitched source go as one copy: same bytes either way."""
+    monkeypatch.setenv("B2_HOST_COPY_THREADS", threads)
+    L = _lib.lib()
+    rng = np.random.default_rng(11)
+    n, rows_total, row_bytes = 5, 400, 4096
+    pitch = row_bytes + pitch_pad
+    src = rng.integers(0, 256, (n, rows_total, pitch), dtype=np.uint8)
+    rows = np.sort(rng.choice(rows_total, 300, replace=False)).astype(np.int32)  # runs and gaps
+    dst = np.full((n, len(rows) * row_bytes + 7), 0xA5, np.uint8)
+    assert L.b2_copy_rows(dst.ctypes.data, dst.strides[0], src.ctypes.data, src.strides[0], pitch,
+                          rows.ctypes.data, len(rows), row_bytes, n) == 0
+    want = src[:, rows, :row_bytes].reshape(n, -1)
+    assert (dst[:, :len(rows) * row_bytes] == want).all()
+    assert (dst[:, len(rows) * row_bytes:] == 0xA5).all()
+    # whole frames as one "row" each: the staging copy of a batch of frames
+    frame = rows_total * pitch
+    whole = np.zeros((n, frame), np.uint8)
+    zero = np.zeros(1, np.int32)
+    assert L.b2_copy_rows(whole.ctypes.data, frame, src.ctypes.data, frame, frame,
+                          zero.ctypes.data, 1, frame, n) == 0
+    assert (whole == src.reshape(n, -1)).all()
+
+
 def test_copy_rows_packs_selected_rows_of_every_frame():
     """``b2_copy_rows``: the host-side packing step of a row-sparse upload (no CUDA call)."""
     L = _lib.lib()

@@ -84,6 +84,8 @@ def test_stage_under_the_reference_pipeline_builder_host_stand_ins(monkeypatch):
             self.cuda_stream = 0x1000 + len(streams_made)
 
     monkeypatch.setattr(_stage, "transfer_buffer", fake_transfer)
+    # no page-locked memory without a driver: the staging copy hands the frames through
+    monkeypatch.setattr(_stage.FrameStage, "_stage_whole", lambda self, st, frames: frames)
     monkeypatch.setattr(_stage, "convert_resize", fake_resize)
     monkeypatch.setattr(_stage, "to_torch", lambda buf, dtype=None: torch.from_numpy(buf.array))
     monkeypatch.setattr(torch.cuda, "Stream", FakeStream)

@@ -440,4 +440,5 @@ def test_frame_stage_sparse_upload_equals_whole_frames():
         auto = io.FrameStage(src_format="nv12", dtype="uint8", sparse_upload="auto", **geom)
         whole = io.FrameStage(src_format="nv12", dtype="uint8", **geom)
         assert torch.equal(auto(frames), whole(frames))
-        assert ("pinned" in auto._state()) == expect_sparse
+        assert auto._state()["uploads"] == ({"sparse": 1, "whole": 0} if expect_sparse
+                                            else {"sparse": 0, "whole": 1})
