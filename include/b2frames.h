@@ -268,6 +268,12 @@ B2_API int b2_copy_rows(void* dst, int64_t dst_frame_stride, const void* src, in
                  int64_t src_pitch, const int32_t* rows, int num_rows, int64_t row_bytes,
                  int num_frames);
 
+/* Host helper (no CUDA call): memcpy of nbytes, cut into slices for several host threads when it
+ * is several MiB long (same thread count as b2_copy_rows).  The staging copy of one large host
+ * array into page-locked memory; the reference pins such arrays with Tensor.pin_memory() in
+ * spdl.io.transfer_tensor (src/spdl/io/_transfer.py:84), a single-threaded copy. */
+B2_API int b2_copy_host(void* dst, const void* src, size_t nbytes);
+
 /* ------------------------------------------------------------------------------------------
  * Frame batching.
  *
@@ -295,6 +301,14 @@ B2_API int b2_transfer_h2d(void* dst, const void* host_src, size_t nbytes, int s
                     void* stream);
 B2_API int b2_transfer_h2d_async(void* dst, const void* host_src, size_t nbytes, int device,
                           void* stream);
+/* The pageable branch of transfer_buffer_impl (src/libspdl/cuda/transfer.cpp:59-63: a blocking
+ * cudaMemcpy, which the driver stages on one thread at about a fifth of the link's rate) through
+ * the CALLER's page-locked staging buffer instead: the buffer is cut into two halves, the staging
+ * copy of one half (b2_copy_host, several host threads) overlaps the asynchronous upload of the
+ * other on `stream`.  Returns when all the data is on the device, like b2_transfer_h2d.
+ * staging_bytes >= 512; a few tens of MiB are enough. */
+B2_API int b2_transfer_h2d_staged(void* dst, const void* host_src, size_t nbytes, void* staging,
+                           size_t staging_bytes, int device, void* stream);
 B2_API int b2_transfer_d2h(void* host_dst, const void* src, size_t nbytes, int device);
 B2_API int b2_alloc_pinned(void** host_ptr, size_t nbytes);
 B2_API int b2_free_pinned(void* host_ptr);

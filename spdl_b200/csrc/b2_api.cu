@@ -372,6 +372,43 @@ static long long host_copy_threads() {
   return half < 1 ? 1 : (half > 8 ? 8 : half);
 }
 
+// memcpy by several host threads: one per 2 MiB at least, slices cut on 4 KiB boundaries.
+static void host_copy(void* dst, const void* src, size_t n) {
+  long long threads = (long long)(n / (2u << 20));
+  const long long cap = host_copy_threads();
+  if (threads > cap) threads = cap;
+  if (threads <= 1) {
+    memcpy(dst, src, n);
+    return;
+  }
+  const size_t slice = ((n / (size_t)threads) + 4095) & ~(size_t)4095;
+  auto part = [=](size_t first) {
+    if (first < n)
+      memcpy(static_cast<char*>(dst) + first, static_cast<const char*>(src) + first,
+             n - first < slice ? n - first : slice);
+  };
+  std::vector<std::thread> pool;
+  pool.reserve((size_t)threads - 1);
+  size_t mine = 0;  // slices from here on are still to be copied by this thread
+  try {
+    for (long long t = 1; t < threads; ++t) pool.emplace_back(part, (size_t)t * slice);
+  } catch (...) {  // no more threads to be had
+    mine = (pool.size() + 1) * slice;
+  }
+  part(0);
+  if (mine)
+    for (size_t first = mine; first < n; first += slice) part(first);
+  for (auto& th : pool) th.join();
+}
+
+B2_API int b2_copy_host(void* dst, const void* src, size_t nbytes) {
+  clear_error();
+  if (nbytes == 0) return B2_OK;
+  if (!dst || !src) return fail(B2_ERR_INVALID, "null pointer argument");
+  host_copy(dst, src, nbytes);
+  return B2_OK;
+}
+
 B2_API int b2_copy_rows(void* dst, int64_t dst_frame_stride, const void* src, int64_t src_frame_stride,
                  int64_t src_pitch, const int32_t* rows, int num_rows, int64_t row_bytes,
                  int num_frames) {
@@ -467,6 +504,49 @@ B2_API int b2_transfer_h2d_async(void* dst, const void* host_src, size_t nbytes,
   B2_CUDA(cudaMemcpyAsync(dst, host_src, nbytes, cudaMemcpyHostToDevice,
                           static_cast<cudaStream_t>(stream)),
           "Failed to initiate async memory copy from host to device.");
+  return B2_OK;
+}
+
+namespace {
+struct EventPair {  // two events without timing, destroyed on every way out
+  cudaEvent_t ev[2] = {nullptr, nullptr};
+  ~EventPair() {
+    for (auto e : ev)
+      if (e) cudaEventDestroy(e);
+  }
+};
+}  // namespace
+
+B2_API int b2_transfer_h2d_staged(void* dst, const void* host_src, size_t nbytes, void* staging,
+                           size_t staging_bytes, int device, void* stream) {
+  clear_error();
+  if (nbytes == 0) return B2_OK;
+  if (!dst || !host_src || !staging) return fail(B2_ERR_INVALID, "null pointer argument");
+  const size_t half = (staging_bytes / 2) & ~(size_t)255;
+  if (half == 0)
+    return fail(B2_ERR_INVALID, "the staging buffer must hold 512 bytes at least. Found: %zu",
+                staging_bytes);
+  DeviceGuard g(device);
+  B2_CUDA(g.status(), "selecting the device failed");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  EventPair done;
+  for (auto& e : done.ev)
+    B2_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "Failed to create an event.");
+  bool used[2] = {false, false};
+  int k = 0;
+  for (size_t off = 0; off < nbytes; k ^= 1) {
+    const size_t n = nbytes - off < half ? nbytes - off : half;
+    char* slot = static_cast<char*>(staging) + (size_t)k * half;
+    if (used[k])  // the upload that last read this half has finished
+      B2_CUDA(cudaEventSynchronize(done.ev[k]), "Failed to wait for an upload.");
+    host_copy(slot, static_cast<const char*>(host_src) + off, n);
+    B2_CUDA(cudaMemcpyAsync(static_cast<char*>(dst) + off, slot, n, cudaMemcpyHostToDevice, s),
+            "Failed to initiate async memory copy from host to device.");
+    B2_CUDA(cudaEventRecord(done.ev[k], s), "Failed to record an event.");
+    used[k] = true;
+    off += n;
+  }
+  B2_CUDA(cudaStreamSynchronize(s), "Failed to synchronize the stream.");
   return B2_OK;
 }
 

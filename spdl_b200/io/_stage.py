@@ -47,7 +47,7 @@ class FrameStage:
     kernel finds the rows through the maps of :func:`touched_rows`.  The result is identical.
     ``sparse_upload="auto"`` does so when the geometry reads less than 85 % of a frame's bytes.
     Frames in pageable memory are first copied into the page-locked staging buffer by several
-    host threads (``b2_copy_rows``; whole frames or the touched rows) and uploaded from there
+    host threads (``b2_copy_host`` for whole frames, ``b2_copy_rows`` for the touched rows) and uploaded from there
     asynchronously; that copy, at about 30 GB/s, is what bounds the stage (measured on a B200
     host, 16 cores, two worker threads: 4K -> 224x224 2.4 k frames/s whole, 5-6 k sparse; 720p ->
     256x256 22 k whole, 24-26 k sparse; the driver's own staging of pageable sources gave 0.8 k
@@ -175,10 +175,7 @@ class FrameStage:
         store = st.get("pinned")
         if store is None or store.size < need:
             store = st["pinned"] = CPUStorage(max(need, 1 << 20), pin_memory=True)
-        n, fb = frames.shape[0], frames.strides[0]
-        one = np.zeros(1, np.int32)  # every frame is one "row"
-        _lib.check(_lib.lib().b2_copy_rows(store.data_ptr, fb, frames.ctypes.data, fb, fb,
-                                           one.ctypes.data, 1, fb, n))
+        _lib.check(_lib.lib().b2_copy_host(store.data_ptr, frames.ctypes.data, need))
         return CPUBuffer(frames.shape, "u", 1, store)
 
     @staticmethod

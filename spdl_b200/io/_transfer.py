@@ -9,8 +9,9 @@ their memory to another stream while a consumer still reads it.
 
 The transport is this package's own.  Each thread owns one page-locked staging arena
 (``b2_alloc_pinned``), grown geometrically and reused by every call: a batch is packed into it
-with plain memory copies (the reference pins every tensor anew with ``Tensor.pin_memory()``, one
-``cudaHostAlloc`` per tensor per call), each tensor goes to the device with
+with plain memory copies, cut into slices for several host threads when a tensor is several MiB
+long (``b2_copy_host``; the reference pins every tensor anew with ``Tensor.pin_memory()``, one
+``cudaHostAlloc`` and a single-threaded copy per tensor per call), each tensor goes to the device with
 ``b2_transfer_h2d_async`` on the thread's stream, and the stream is synchronised once per batch.
 Tensors that are already page-locked are copied from where they are.
 """
@@ -155,7 +156,8 @@ class _ThreadTransfer:
                 host = src.data_ptr()
                 if offset is not None:
                     host = base + offset
-                    ctypes.memmove(host, src.data_ptr(), nbytes)  # drops the GIL while it copies
+                    # outside the GIL; several host threads for tensors of several MiB
+                    _lib.check(_lib.lib().b2_copy_host(host, src.data_ptr(), nbytes))
                 self._copy_async(out.data_ptr(), host, nbytes)
             return out
 

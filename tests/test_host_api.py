@@ -489,6 +489,27 @@ def test_copy_rows_large_batches_over_several_threads(monkeypatch, threads, pitc
     assert (whole == src.reshape(n, -1)).all()
 
 
+@pytest.mark.parametrize("threads", ["1", "5"])
+def test_copy_host_and_the_arguments_of_the_staged_transfer(monkeypatch, threads):
+    """``b2_copy_host`` moves every byte whatever the number of host threads;
+    ``b2_transfer_h2d_staged`` rejects null pointers and a staging buffer without room for two
+    halves before it makes any CUDA call."""
+    monkeypatch.setenv("B2_HOST_COPY_THREADS", threads)
+    L = _lib.lib()
+    n = (9 << 20) + 4321
+    src = np.random.default_rng(5).integers(0, 256, n, dtype=np.uint8)
+    dst = np.zeros(n + 3, np.uint8)
+    assert L.b2_copy_host(dst.ctypes.data, src.ctypes.data, n) == 0
+    assert (dst[:n] == src).all() and (dst[n:] == 0).all()
+    assert L.b2_copy_host(None, None, 0) == 0
+    assert L.b2_copy_host(None, src.ctypes.data, 8) == 1
+    assert L.b2_transfer_h2d_staged(None, None, 0, None, 0, 0, None) == 0  # nothing to do
+    assert L.b2_transfer_h2d_staged(None, src.ctypes.data, 8, dst.ctypes.data, 1024, 0, None) == 1
+    assert L.b2_transfer_h2d_staged(dst.ctypes.data, src.ctypes.data, 8, dst.ctypes.data, 300, 0,
+                                    None) == 1
+    assert b"staging" in L.b2_last_error()
+
+
 def test_copy_rows_packs_selected_rows_of_every_frame():
     """``b2_copy_rows``: the host-side packing step of a row-sparse upload (no CUDA call)."""
     L = _lib.lib()

@@ -105,6 +105,46 @@ def test_array_round_trip(cuda_cfg, dtype):
         assert back.dtype == a.dtype and (back == a).all()
 
 
+@pytest.mark.parametrize("nbytes", [8 << 20, (40 << 20) + 12345])
+def test_large_pageable_arrays_go_through_the_staging_buffer(cuda_cfg, nbytes):
+    """From 8 MiB on a pageable source is staged in halves of this thread's page-locked buffer
+    under the uploads of the other half; the data arrives unchanged."""
+    import torch
+
+    import spdl_b200.io as io
+
+    a = np.random.default_rng(nbytes & 0xFFFF).integers(0, 256, nbytes, dtype=np.uint8)
+    dev = io.transfer_buffer(a, device_config=cuda_cfg)
+    assert (io.to_torch(dev).cpu().numpy() == a).all()
+    if nbytes % 4 == 0:  # a pageable torch tensor of another element type takes the same route
+        t = torch.from_numpy(a.view(np.int32))
+        assert torch.equal(io.to_torch(io.transfer_buffer(t, device_config=cuda_cfg)).cpu(), t)
+
+
+def test_staged_transfer_with_a_tiny_staging_buffer(cuda_cfg):
+    """``b2_transfer_h2d_staged`` through the C ABI with halves of 512 bytes: many chunks, a
+    ragged last one, both halves reused."""
+    import ctypes
+
+    import torch
+
+    from spdl_b200 import _lib
+
+    L = _lib.lib()
+    a = np.random.default_rng(3).integers(0, 256, 5000, dtype=np.uint8)
+    staging = ctypes.c_void_p()
+    _lib.check(L.b2_alloc_pinned(ctypes.byref(staging), 1100))
+    try:
+        dst = torch.zeros(5000 + 16, dtype=torch.uint8, device="cuda")
+        stream = torch.cuda.current_stream().cuda_stream
+        _lib.check(L.b2_transfer_h2d_staged(dst.data_ptr(), a.ctypes.data, a.size, staging, 1100, 0,
+                                            stream))
+        got = dst.cpu().numpy()
+        assert (got[:5000] == a).all() and (got[5000:] == 0).all()
+    finally:
+        _lib.check(L.b2_free_pinned(staging))
+
+
 def test_non_contiguous_inputs(cuda_cfg):
     import torch
 
