@@ -274,6 +274,15 @@ B2_API int b2_copy_rows(void* dst, int64_t dst_frame_stride, const void* src, in
  * spdl.io.transfer_tensor (src/spdl/io/_transfer.py:84), a single-threaded copy. */
 B2_API int b2_copy_host(void* dst, const void* src, size_t nbytes);
 
+/* Host helper (no CUDA call): packs num_items host arrays of different sizes into one buffer,
+ * item i (sizes[i] bytes at srcs[i]) to dst + dst_offsets[i]; whole items are dealt out to several
+ * host threads when the batch is several MiB long.  The staging copy of a list of decoded
+ * images of different sizes, which the reference cannot batch at all (its convert_frames wants
+ * equal sizes, src/libspdl/core/detail/ffmpeg/conversion.cpp:307-390, so such images are
+ * resized one by one on the CPU first: load_image_batch, src/spdl/io/_composite.py:438-463). */
+B2_API int b2_pack_host(void* dst, const void* const* srcs, const int64_t* sizes,
+                 const int64_t* dst_offsets, int num_items);
+
 /* ------------------------------------------------------------------------------------------
  * Frame batching.
  *

@@ -409,6 +409,57 @@ B2_API int b2_copy_host(void* dst, const void* src, size_t nbytes) {
   return B2_OK;
 }
 
+B2_API int b2_pack_host(void* dst, const void* const* srcs, const int64_t* sizes,
+                 const int64_t* dst_offsets, int num_items) {
+  clear_error();
+  if (num_items < 0) return fail(B2_ERR_INVALID, "negative number of items: %d", num_items);
+  if (num_items == 0) return B2_OK;
+  if (!dst || !srcs || !sizes || !dst_offsets) return fail(B2_ERR_INVALID, "null pointer argument");
+  long long total = 0;
+  for (int i = 0; i < num_items; ++i) {
+    if (sizes[i] < 0 || dst_offsets[i] < 0 || (sizes[i] > 0 && !srcs[i]))
+      return fail(B2_ERR_INVALID, "item %d: size %lld, offset %lld, source %p", i,
+                  (long long)sizes[i], (long long)dst_offsets[i], srcs[i]);
+    total += sizes[i];
+  }
+  // whole items per thread, cut where the running byte count passes a multiple of total / threads
+  long long threads = total / (2LL << 20);
+  const long long cap = host_copy_threads();
+  if (threads > cap) threads = cap;
+  if (threads > num_items) threads = num_items;
+  if (threads < 1) threads = 1;
+  auto copy_items = [=](int first, int last) {
+    for (int i = first; i < last; ++i)
+      if (sizes[i])
+        memcpy(static_cast<char*>(dst) + dst_offsets[i], srcs[i], (size_t)sizes[i]);
+  };
+  if (threads == 1) {
+    copy_items(0, num_items);
+    return B2_OK;
+  }
+  std::vector<int> cut((size_t)threads + 1, num_items);
+  cut[0] = 0;
+  long long seen = 0;
+  int t = 1;
+  for (int i = 0; i < num_items && t < threads; ++i) {
+    seen += sizes[i];
+    while (t < threads && seen >= total * t / threads) cut[(size_t)t++] = i + 1;
+  }
+  std::vector<std::thread> pool;
+  pool.reserve((size_t)threads - 1);
+  int mine_from = num_items;  // items from here on are still to be copied by this thread
+  try {
+    for (long long k = 1; k < threads; ++k)
+      pool.emplace_back(copy_items, cut[(size_t)k], cut[(size_t)k + 1]);
+  } catch (...) {  // no more threads to be had
+    mine_from = cut[pool.size() + 1];
+  }
+  copy_items(0, cut[1]);
+  copy_items(mine_from, num_items);
+  for (auto& th : pool) th.join();
+  return B2_OK;
+}
+
 B2_API int b2_copy_rows(void* dst, int64_t dst_frame_stride, const void* src, int64_t src_frame_stride,
                  int64_t src_pitch, const int32_t* rows, int num_rows, int64_t row_bytes,
                  int num_frames) {

@@ -590,6 +590,85 @@ def resize_image_list(images: Sequence[Any], *, device_config: CUDAConfig,
     return out
 
 
+def resize_host_images(images: Sequence[Any], *, device_config: CUDAConfig,
+                       src_format: str = "rgb24", resize: tuple[int, int] | None = None,
+                       resize_shorter: int | None = None, crop: tuple[int, int] | None = None,
+                       scale_mode: str | None = None,
+                       pad_color: tuple[float, float, float] = (0.0, 0.0, 0.0),
+                       layout: str = "NCHW", dtype: str = "uint8", order: str = "rgb",
+                       coeff: int = 1, full_range: bool = False, arith: str = "reference",
+                       mean=None, std=None) -> CUDABuffer:
+    """Upload a list of decoded HOST images of different sizes and resize, crop, convert and
+    normalise them in one launch.
+
+    ``images`` are C-contiguous ``uint8`` NumPy arrays or CPU tensors: ``[H, W, 3]`` for
+    ``src_format="rgb24"``, ``[3, H, W]`` for ``"rgb_planar"``, and the packed planes a decoder
+    leaves for ``"i420"`` / ``"nv12"`` -- ``[H*3/2, W]``, the luma rows followed by the chroma
+    (even ``W`` and ``H``).  The images are packed back to back (16-byte aligned) into the
+    calling thread's page-locked staging buffer by several host threads (``b2_pack_host``), go
+    up in ONE asynchronous copy on ``device_config.stream`` and are read by the fused kernel
+    through an offset table; the call returns when the result is complete.
+
+    The reference's ``load_image_batch`` (``src/spdl/io/_composite.py:438-463``) resizes every
+    image on the CPU so that ``convert_frames`` can batch equal sizes, then uploads the batch.
+    """
+    fmt = src_format.lower()
+    fmt = "i420" if fmt == "yuv420p" else fmt
+    if fmt not in ("rgb24", "rgb_planar", "i420", "nv12"):
+        raise RuntimeError(f"Unsupported source format for an image list: {src_format}")
+    if len(images) == 0:
+        raise RuntimeError("The image list is empty.")
+    arrays, ws, hs = [], [], []
+    for img in images:
+        if hasattr(img, "is_cuda") and hasattr(img, "numpy"):  # torch tensor
+            if img.is_cuda:
+                raise RuntimeError("resize_host_images expects CPU images.")
+            img = img.contiguous().numpy()
+        arr = np.ascontiguousarray(img)
+        want_dims = 2 if fmt in ("i420", "nv12") else 3
+        if arr.dtype != np.uint8 or arr.ndim != want_dims:
+            raise RuntimeError(
+                f"Images must be {want_dims}-D uint8 arrays, got {arr.dtype} {arr.shape}")
+        if fmt == "rgb24":
+            h, w, c = arr.shape
+        elif fmt == "rgb_planar":
+            c, h, w = arr.shape
+        else:
+            h2, w = arr.shape
+            if h2 % 3 or (h2 // 3 * 2) % 2 or w % 2:
+                raise RuntimeError(f"Planes of an even-sized 4:2:0 image are [H*3/2, W]. Found: "
+                                   f"{arr.shape}")
+            h, c = h2 // 3 * 2, 3
+        if c != 3:
+            raise RuntimeError(f"Images must have three channels, got shape {arr.shape}")
+        arrays.append(arr)
+        ws.append(w)
+        hs.append(h)
+    n = len(arrays)
+    sizes = np.array([a.nbytes for a in arrays], np.int64)
+    offsets = np.zeros(n, np.int64)
+    np.cumsum((sizes[:-1] + 15) & ~15, out=offsets[1:])
+    total = int(offsets[-1] + sizes[-1])
+    host = _staging_arena().reserve(total)
+    srcs = np.array([a.ctypes.data for a in arrays], np.uint64)
+    L = _lib.lib()
+    _lib.check(L.b2_pack_host(host, srcs.ctypes.data, sizes.ctypes.data, offsets.ctypes.data, n))
+    base = cuda_buffer((total,), device_config, "u", 1)
+    _lib.check(L.b2_transfer_h2d_async(base.data_ptr, host, total, device_config.device_index,
+                                       device_config.stream))
+    descs, out_size = make_image_descs(ws, hs, src_format=fmt, offsets=offsets, resize=resize,
+                                       resize_shorter=resize_shorter, crop=crop,
+                                       scale_mode=scale_mode)
+    table = transfer_buffer(descs.view(np.uint8), device_config=device_config)
+    # sync=True: the staging buffer is this thread's, and free again when the call returns
+    out = convert_resize(base, table, out_size=out_size, max_src_w=max(ws),
+                         device_config=device_config, src_format=fmt, coeff=coeff,
+                         full_range=full_range, arith=arith, layout=layout, dtype=dtype,
+                         order=order, mean=mean, std=std, pad_color=pad_color, sync=True)
+    _tracing.record("resize_host_images", n, total, out.nbytes)
+    return out
+
+
 # ---- transfer ----------------------------------------------------------------------------------
 
 _NP_CLASS = {"u": "u", "i": "i", "f": "f", "b": "u"}

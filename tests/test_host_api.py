@@ -510,6 +510,34 @@ def test_copy_host_and_the_arguments_of_the_staged_transfer(monkeypatch, threads
     assert b"staging" in L.b2_last_error()
 
 
+@pytest.mark.parametrize("threads", ["1", "4"])
+def test_pack_host_packs_items_of_different_sizes(monkeypatch, threads):
+    """``b2_pack_host``: every item lands at its offset, nothing else is touched, whatever the
+    number of host threads the items are dealt out to."""
+    monkeypatch.setenv("B2_HOST_COPY_THREADS", threads)
+    L = _lib.lib()
+    rng = np.random.default_rng(8)
+    items = [rng.integers(0, 256, int(k), dtype=np.uint8)
+             for k in rng.integers(0, 3 << 20, 11)] + [np.zeros(0, np.uint8)]
+    sizes = np.array([a.size for a in items], np.int64)
+    offsets = np.zeros(len(items), np.int64)
+    np.cumsum((sizes[:-1] + 15) & ~15, out=offsets[1:])
+    total = int(offsets[-1] + sizes[-1])
+    dst = np.full(total + 9, 0xA5, np.uint8)
+    srcs = np.array([a.ctypes.data for a in items], np.uint64)
+    assert L.b2_pack_host(dst.ctypes.data, srcs.ctypes.data, sizes.ctypes.data,
+                          offsets.ctypes.data, len(items)) == 0
+    covered = np.zeros(dst.size, bool)
+    for a, o in zip(items, offsets):
+        assert (dst[o:o + a.size] == a).all()
+        covered[o:o + a.size] = True
+    assert (dst[~covered] == 0xA5).all()
+    assert L.b2_pack_host(None, None, None, None, 0) == 0
+    sizes[2] = -1
+    assert L.b2_pack_host(dst.ctypes.data, srcs.ctypes.data, sizes.ctypes.data,
+                          offsets.ctypes.data, len(items)) == 1
+
+
 def test_copy_rows_packs_selected_rows_of_every_frame():
     """``b2_copy_rows``: the host-side packing step of a row-sparse upload (no CUDA call)."""
     L = _lib.lib()

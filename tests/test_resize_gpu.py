@@ -288,6 +288,46 @@ def test_resize_image_list_reads_images_where_they_lie(cuda_cfg, fmt):
                              resize=(8, 8))
 
 
+@pytest.mark.parametrize("fmt", ["rgb24", "rgb_planar", "i420", "nv12"])
+def test_resize_host_images_packs_uploads_and_resizes_in_one_go(cuda_cfg, fmt):
+    """Host images of different sizes (a CPU decoder's output list): packed into page-locked
+    staging, one upload, one launch; the result equals the oracle on the same images packed back
+    to back."""
+    import torch
+
+    import spdl_b200.io as io
+
+    rng = np.random.default_rng(35)
+    ws, hs = 2 * rng.integers(20, 90, 9), 2 * rng.integers(20, 90, 9)
+    shape = {"rgb24": lambda w, h: (h, w, 3), "rgb_planar": lambda w, h: (3, h, w),
+             "i420": lambda w, h: (h * 3 // 2, w), "nv12": lambda w, h: (h * 3 // 2, w)}[fmt]
+    host = [rng.integers(0, 256, shape(w, h), dtype=np.uint8) for w, h in zip(ws, hs)]
+    images = [torch.from_numpy(a) if i % 2 else a for i, a in enumerate(host)]
+    kw = dict(resize_shorter=48, crop=(40, 32))
+    got = io.to_torch(io.resize_host_images(images, device_config=cuda_cfg, src_format=fmt,
+                                            dtype="float32", mean=MEAN, std=STD, coeff=6,
+                                            **kw)).cpu().numpy()
+    sizes = np.array([a.nbytes for a in host])
+    offs = np.concatenate([[0], np.cumsum(sizes)[:-1]])
+    packed = np.concatenate([a.reshape(-1) for a in host])
+    descs, out = io.make_image_descs(ws, hs, src_format=fmt, offsets=offs, **kw)
+    ofmt = {"rgb24": oracle.RGBI, "rgb_planar": oracle.RGBP, "i420": oracle.I420,
+            "nv12": oracle.NV12}[fmt]
+    want = oracle.convert_resize(packed, descs, out_w=out[0], out_h=out[1], src_format=ofmt,
+                                 coeff=6, dtype=oracle.F32, sb=oracle.scale_bias(MEAN, STD))
+    _compare(got, want, "float32")
+    # a second call of the same thread reuses the staging buffer
+    again = io.to_torch(io.resize_host_images(images[:3], device_config=cuda_cfg, src_format=fmt,
+                                              dtype="float32", mean=MEAN, std=STD, coeff=6,
+                                              **kw)).cpu().numpy()
+    _compare(again, want[:3], "float32")
+    with pytest.raises(RuntimeError):
+        io.resize_host_images([], device_config=cuda_cfg, resize=(8, 8))
+    with pytest.raises(RuntimeError):
+        io.resize_host_images([host[0].astype(np.float32)], device_config=cuda_cfg,
+                              src_format=fmt, resize=(8, 8))
+
+
 def _sample_against_oracle(got, base_host, descs, picks, out, fmt, dtype, **kw):
     """Oracle on a few images of a large batch: their descriptors still point into the shared
     buffer, so the oracle reads exactly the bytes the kernel read."""
