@@ -319,6 +319,13 @@ B2_API int b2_transfer_h2d_async(void* dst, const void* host_src, size_t nbytes,
 B2_API int b2_transfer_h2d_staged(void* dst, const void* host_src, size_t nbytes, void* staging,
                            size_t staging_bytes, int device, void* stream);
 B2_API int b2_transfer_d2h(void* host_dst, const void* src, size_t nbytes, int device);
+/* b2_transfer_d2h for a large pageable destination, through the CALLER's page-locked staging
+ * buffer cut into two halves: the download of one half on `stream` overlaps the copy of the other
+ * half out to host_dst (b2_copy_host, several host threads).  Returns when host_dst is complete.
+ * The reference's device->host transfer (src/libspdl/cuda/transfer.cpp:91-118) is one blocking
+ * cudaMemcpy into pageable memory. */
+B2_API int b2_transfer_d2h_staged(void* host_dst, const void* src, size_t nbytes, void* staging,
+                           size_t staging_bytes, int device, void* stream);
 B2_API int b2_alloc_pinned(void** host_ptr, size_t nbytes);
 B2_API int b2_free_pinned(void* host_ptr);
 B2_API int b2_device_alloc(void** ptr, size_t nbytes, int device);

@@ -28,7 +28,7 @@ EXPORTS = (
     "b2_last_error", "b2_abi_version", "b2_init", "b2_device_count", "b2_stream_synchronize",
     "b2_nv12_to_planar_rgb", "b2_nv12_to_planar_bgr", "b2_convert_dense", "b2_convert_resize",
     "b2_touched_rows", "b2_copy_rows", "b2_copy_host", "b2_pack_host", "b2_gather_surfaces", "b2_transfer_h2d",
-    "b2_transfer_h2d_async", "b2_transfer_h2d_staged", "b2_transfer_d2h",
+    "b2_transfer_h2d_async", "b2_transfer_h2d_staged", "b2_transfer_d2h", "b2_transfer_d2h_staged",
     "b2_alloc_pinned", "b2_free_pinned", "b2_device_alloc", "b2_device_free", "b2_frame_checksum",
 )
 
@@ -106,6 +106,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.b2_copy_host.argtypes = [c_void_p, c_void_p, c_size_t]
     lib.b2_pack_host.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int]
     lib.b2_transfer_d2h.argtypes = [c_void_p, c_void_p, c_size_t, c_int]
+    lib.b2_transfer_d2h_staged.argtypes = [c_void_p, c_void_p, c_size_t, c_void_p, c_size_t, c_int,
+                                           c_void_p]
     lib.b2_alloc_pinned.argtypes = [POINTER(c_void_p), c_size_t]
     lib.b2_free_pinned.argtypes = [c_void_p]
     lib.b2_device_alloc.argtypes = [POINTER(c_void_p), c_size_t, c_int]

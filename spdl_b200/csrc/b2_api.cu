@@ -612,6 +612,41 @@ B2_API int b2_transfer_d2h(void* host_dst, const void* src, size_t nbytes, int d
   return B2_OK;
 }
 
+B2_API int b2_transfer_d2h_staged(void* host_dst, const void* src, size_t nbytes, void* staging,
+                           size_t staging_bytes, int device, void* stream) {
+  clear_error();
+  if (nbytes == 0) return B2_OK;
+  if (!host_dst || !src || !staging) return fail(B2_ERR_INVALID, "null pointer argument");
+  const size_t half = (staging_bytes / 2) & ~(size_t)255;
+  if (half == 0)
+    return fail(B2_ERR_INVALID, "the staging buffer must hold 512 bytes at least. Found: %zu",
+                staging_bytes);
+  DeviceGuard g(device);
+  B2_CUDA(g.status(), "selecting the device failed");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  EventPair done;
+  for (auto& e : done.ev)
+    B2_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "Failed to create an event.");
+  // the download of chunk i + 1 into one half runs under the copy of chunk i out of the other
+  const size_t chunks = (nbytes + half - 1) / half;
+  auto download = [&](size_t i) -> cudaError_t {
+    const size_t off = i * half, n = nbytes - off < half ? nbytes - off : half;
+    cudaError_t e = cudaMemcpyAsync(static_cast<char*>(staging) + (i & 1) * half,
+                                    static_cast<const char*>(src) + off, n,
+                                    cudaMemcpyDeviceToHost, s);
+    return e != cudaSuccess ? e : cudaEventRecord(done.ev[i & 1], s);
+  };
+  B2_CUDA(download(0), "Failed to initiate async memory copy from device to host.");
+  for (size_t i = 0; i < chunks; ++i) {
+    if (i + 1 < chunks)
+      B2_CUDA(download(i + 1), "Failed to initiate async memory copy from device to host.");
+    B2_CUDA(cudaEventSynchronize(done.ev[i & 1]), "Failed to wait for a download.");
+    const size_t off = i * half, n = nbytes - off < half ? nbytes - off : half;
+    host_copy(static_cast<char*>(host_dst) + off, static_cast<char*>(staging) + (i & 1) * half, n);
+  }
+  return B2_OK;
+}
+
 B2_API int b2_alloc_pinned(void** host_ptr, size_t nbytes) {
   clear_error();
   if (!host_ptr) return fail(B2_ERR_INVALID, "null pointer argument");

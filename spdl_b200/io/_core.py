@@ -688,6 +688,7 @@ def _warn_legacy_stream_once() -> None:
 
 
 _STAGED_MIN_BYTES = 8 << 20   # pageable sources from this size on are staged by this package
+_PER_THREAD_STREAM = 0x2      # cudaStreamPerThread: what a blocking copy of this library uses
 _STAGING_BYTES = 32 << 20     # page-locked staging per calling thread (two halves of 16 MiB)
 _STAGING_LOCAL = threading.local()
 
@@ -759,7 +760,14 @@ def transfer_buffer_cpu(buffer: Any) -> CPUBuffer:
     if dev is None:
         dev = getattr(getattr(buffer, "device", None), "index", 0) or 0
     out = CPUBuffer(shape, _NP_CLASS.get(ec, "u"), depth)
-    _lib.check(_lib.lib().b2_transfer_d2h(out.data_ptr, ptr, out.nbytes, dev))
+    if out.nbytes >= _STAGED_MIN_BYTES:
+        # through this thread's page-locked staging buffer, downloads under the copies out
+        arena = _staging_arena()
+        _lib.check(_lib.lib().b2_transfer_d2h_staged(
+            out.data_ptr, ptr, out.nbytes, arena.reserve(_STAGING_BYTES), _STAGING_BYTES, dev,
+            _PER_THREAD_STREAM))
+    else:
+        _lib.check(_lib.lib().b2_transfer_d2h(out.data_ptr, ptr, out.nbytes, dev))
     return out
 
 

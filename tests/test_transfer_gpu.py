@@ -145,6 +145,37 @@ def test_staged_transfer_with_a_tiny_staging_buffer(cuda_cfg):
         _lib.check(L.b2_free_pinned(staging))
 
 
+def test_large_device_arrays_come_back_through_the_staging_buffer(cuda_cfg):
+    """``transfer_buffer_cpu`` of 8 MiB and more downloads in halves of this thread's
+    page-locked buffer under the copies out; and the C entry point with halves of 512 bytes."""
+    import ctypes
+
+    import torch
+
+    import spdl_b200.io as io
+    from spdl_b200 import _lib
+
+    n = (24 << 20) + 777
+    t = torch.randint(0, 256, (n,), dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+    back = io.to_numpy(io.transfer_buffer_cpu(t))
+    assert back.shape == (n,) and (back == t.cpu().numpy()).all()
+
+    L = _lib.lib()
+    staging = ctypes.c_void_p()
+    _lib.check(L.b2_alloc_pinned(ctypes.byref(staging), 1100))
+    try:
+        host = np.full(5000 + 16, 0xA5, np.uint8)
+        stream = torch.cuda.current_stream().cuda_stream
+        _lib.check(L.b2_transfer_d2h_staged(host.ctypes.data, t.data_ptr(), 5000, staging, 1100,
+                                            0, stream))
+        assert (host[:5000] == back[:5000]).all() and (host[5000:] == 0xA5).all()
+        assert L.b2_transfer_d2h_staged(host.ctypes.data, t.data_ptr(), 8, staging, 100, 0,
+                                        stream) == 1
+    finally:
+        _lib.check(L.b2_free_pinned(staging))
+
+
 def test_non_contiguous_inputs(cuda_cfg):
     import torch
 
