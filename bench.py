@@ -990,6 +990,38 @@ def run_aux_workload(args) -> None:
             "ms": ms, "bytes": b, "gb_per_s": b / ms / 1e6, "frac": b / ms / 1e6 / peak,
             "what": "64 x 1080p NV12 surfaces, pitch 2048, through the pointer table -> NHWC u8"}
         del rgb_out
+        # 1c. 256 decoder surfaces of a width that is no multiple of 16 (854x480, pitch 1024)
+        #     through the pointer table into a packed batch: the flat kernel's pitched variant
+        nq, wq, hq, pq = 256, 854, 480, 1024
+        surf_q = torch.randint(16, 236, (2, nq, hq * 3 // 2, pq), dtype=torch.uint8, device=dev)
+        out_q = torch.empty((nq, hq, wq, 3), dtype=torch.uint8, device=dev)
+        qcalls = []
+        for c in range(2):
+            ytab = torch.tensor([surf_q[c, k].data_ptr() for k in range(nq)], dtype=torch.int64,
+                                device=dev)
+            utab = ytab + hq * pq
+            a = _lib.DenseArgs()
+            a.struct_size = ctypes.sizeof(_lib.DenseArgs)
+            a.device, a.y_table, a.u_table = 0, ytab.data_ptr(), utab.data_ptr()
+            a.y_pitch = a.uv_pitch = pq
+            a.src_format, a.width, a.height, a.num_frames = _lib.NV12, wq, hq, nq
+            a.matrix_coeff, a.dst = 1, out_q.data_ptr()
+            a.layout, a.dtype, a.order = _lib.NHWC, _lib.U8, _lib.RGB
+            a.scale = (ctypes.c_float * 3)(1, 1, 1)
+            qcalls.append((a, ytab, utab))
+        stream.synchronize()
+
+        def table_convert_854():
+            i[0] += 1
+            _lib.check(L.b2_convert_dense(ctypes.byref(qcalls[i[0] % 2][0]), stream.cuda_stream))
+
+        ms = timed(table_convert_854)
+        b = nq * hq * wq * 9 // 2
+        results["dense_flat_kernel_854x480_surfaces"] = {
+            "ms": ms, "bytes": b, "gb_per_s": b / ms / 1e6, "frac": b / ms / 1e6 / peak,
+            "what": "256 x 854x480 NV12 surfaces, pitch 1024, through the pointer table -> packed "
+                    "NHWC u8"}
+        del surf_q, out_q, qcalls
         # 2. checksum of a 64 x 1080p RGB batch
         rgb = [torch.randint(0, 256, (n, h, w, 3), dtype=torch.uint8, device=dev)
                for _ in range(2)]

@@ -9,19 +9,21 @@
 //                      instruction).  Interleaved output (48 bytes per thread per row) is staged
 //                      in shared memory by the warp and leaves as one bulk asynchronous copy
 //                      (cp.async.bulk shared->global) per row segment.
-//   dense_flat_kernel  packed frames whose width is not a multiple of the vector size (854,
-//                      1366, 1918 ...): with rows back to back, a frame's pixels and its output
-//                      are two flat arrays, so a thread takes PX consecutive pixels of the frame,
-//                      counted from the first pixel whose output is 16-byte aligned.  Every store
-//                      is then an aligned vector whatever the width; only the sources are
-//                      realigned (4-byte loads and funnel shifts), a chunk that runs over the end
-//                      of a row fetches its chroma in two parts, and the ends of a frame are
-//                      stored byte by byte.
-//   dense_any_kernel   everything else (pitched rows or destinations that are not 16-byte aligned,
-//                      odd widths and addresses, pointer tables of unaligned surfaces): the vector
-//                      kernel's thread layout, the source realigned the same way, the output laid
-//                      out in shared memory at the destination's offset modulo 16 so that its
-//                      aligned interior still leaves as one bulk copy per row segment.
+//   dense_flat_kernel  packed OUTPUT frames whose width is not a multiple of the vector size
+//                      (854, 1366, 1918 ...) or that start on an unaligned address.  With rows
+//                      back to back a frame's output is a flat array in pixel order, so a thread
+//                      takes PX consecutive pixels of the frame, counted from the first pixel
+//                      whose output is 16-byte aligned.  Every store is then an aligned vector
+//                      whatever the width; only the sources are realigned (8-byte loads, word
+//                      selects and funnel shifts), a chunk that runs over the end of a row
+//                      fetches its second part separately, and the ends of a frame are stored
+//                      byte by byte.  Two variants: source rows back to back too (luma is then
+//                      one flat array as well), and pitched surfaces / pointer tables.
+//   dense_any_kernel   everything else (destinations with a row pitch or on odd addresses, odd
+//                      widths): the vector kernel's thread layout, the source realigned with
+//                      4-byte loads, the output laid out in shared memory at the destination's
+//                      offset modulo 16 so that its aligned interior still leaves as one bulk
+//                      copy per row segment.
 //
 // The kernels are HBM-bound: 1.5 bytes read and 3*sizeof(T) written per pixel.
 #include "b2_common.cuh"
@@ -45,10 +47,12 @@ struct DenseParams {
   int dst_row_pitch;                              // elements
   ScaleBias sb;
   // dense_flat_kernel only
-  int pixels;         // width * height: luma bytes of a frame
-  int chroma_limit;   // bytes of a chroma plane of a frame
+  int pixels;         // width * height: pixels of a frame
+  int y_limit;        // bytes from the start of the luma plane to the end of its last row
+  int chroma_limit;   // ... of a chroma plane
   unsigned w_recip;   // 2^32 / width, rounded down: pixel index -> row by multiply-high
   int rows_per_warp;  // rows a warp's run of consecutive pixels can touch
+  int flat_packed;    // source rows lie back to back too (pitch == width, no pointer table)
 };
 
 // Load NB bytes into ceil(NB/4) words.  Streaming (read-once) cache hint.
@@ -423,7 +427,7 @@ __device__ __forceinline__ void load_window_inside(const uint8_t* base, int x, u
 // Luma and chroma words of the chunk that starts at pixel i of the frame (i < p.pixels; negative
 // for the partial chunk in front of the frame).  INSIDE: the caller knows that the chunk lies at
 // least four rows away from both ends of the frame, so no window needs a bounds check.
-template <int FMT, int PX, bool INSIDE, int NW, int UVW>
+template <int FMT, int PX, bool INSIDE, bool PACKED, int NW, int UVW>
 __device__ __forceinline__ void flat_load(const DenseParams& p, const uint8_t* yb,
                                           const uint8_t* ub, const uint8_t* vb, int i,
                                           uint32_t (&yw)[1][NW], uint32_t (&uw)[UVW],
@@ -437,13 +441,59 @@ __device__ __forceinline__ void flat_load(const DenseParams& p, const uint8_t* y
     x -= p.width;
     ++y;
   }
-  const int cw = p.width / CDIV;               // bytes of a chroma row
-  const int ca = (y >> 1) * cw + x / CDIV;     // x is even
-  const int k1 = p.width - x;                  // pixels of the chunk that lie in row y
-  const bool split = k1 < PX && !(y & 1);      // ... the rest under the same chroma row
+  const int k1 = p.width - x;  // pixels of the chunk that lie in row y
   uint32_t u2[UVW], v2[UVW];
   (void)vw;
   (void)v2;
+  if constexpr (!PACKED) {
+    // Pitched source rows (decoder surfaces, a pointer per frame): a chunk that runs over the end
+    // of row y continues at the start of row y + 1, so its luma comes in two parts as well, and
+    // its chroma from the row that y + 1 belongs to.
+    const bool split = k1 < PX;
+    const int la = y * p.y_pitch + x, lb = (y + 1) * p.y_pitch - k1;
+    const int ca = (y >> 1) * p.uv_pitch + x / CDIV;  // x is even
+    const int cb = ((y + 1) >> 1) * p.uv_pitch - k1 / CDIV;
+    uint32_t y2[NW];
+    if constexpr (INSIDE) {
+      load_window_inside<PX>(yb, la, yw[0]);
+      load_window_inside<UVB>(ub, ca, uw);
+      if constexpr (FMT == B2_SRC_I420) load_window_inside<UVB>(vb, ca, vw);
+      if (split) {
+        load_window_inside<PX>(yb, lb, y2);
+        load_window_inside<UVB>(ub, cb, u2);
+        if constexpr (FMT == B2_SRC_I420) load_window_inside<UVB>(vb, cb, v2);
+      }
+    } else {
+      load_window<PX>(yb, la, p.y_limit, yw[0]);
+      load_window<UVB>(ub, ca, p.chroma_limit, uw);
+      if constexpr (FMT == B2_SRC_I420) load_window<UVB>(vb, ca, p.chroma_limit, vw);
+      if (split) {
+        load_window<PX>(yb, lb, p.y_limit, y2);
+        load_window<UVB>(ub, cb, p.chroma_limit, u2);
+        if constexpr (FMT == B2_SRC_I420) load_window<UVB>(vb, cb, p.chroma_limit, v2);
+      }
+    }
+    if (split) {
+      auto keep_mask = [](int m) {  // the low m bytes of a word
+        return m >= 4 ? 0xffffffffu : (m <= 0 ? 0u : (1u << (8 * m)) - 1u);
+      };
+#pragma unroll
+      for (int j = 0; j < NW; ++j) {
+        const uint32_t keep = keep_mask(k1 - 4 * j);
+        yw[0][j] = (yw[0][j] & keep) | (y2[j] & ~keep);
+      }
+#pragma unroll
+      for (int j = 0; j < UVW; ++j) {
+        const uint32_t keep = keep_mask(k1 / CDIV - 4 * j);
+        uw[j] = (uw[j] & keep) | (u2[j] & ~keep);
+        if constexpr (FMT == B2_SRC_I420) vw[j] = (vw[j] & keep) | (v2[j] & ~keep);
+      }
+    }
+    return;
+  }
+  const int cw = p.width / CDIV;               // bytes of a chroma row
+  const int ca = (y >> 1) * cw + x / CDIV;     // x is even
+  const bool split = k1 < PX && !(y & 1);      // ... the rest under the same chroma row
   if (INSIDE ||
       (i >= 4 && i + PX + 4 <= p.pixels && ca >= cw + 4 && ca + UVB + 4 <= p.chroma_limit)) {
     load_window_inside<PX>(yb, i, yw[0]);
@@ -474,7 +524,7 @@ __device__ __forceinline__ void flat_load(const DenseParams& p, const uint8_t* y
   }
 }
 
-template <int FMT, int LAYOUT, int DTYPE, bool BGR, int ARITH>
+template <int FMT, int LAYOUT, int DTYPE, bool BGR, int ARITH, bool PACKED>
 __global__ void __launch_bounds__(kFlatThreads, kFlatMinBlocks) dense_flat_kernel(const DenseParams p) {
   using T = typename OutT<DTYPE>::type;
   constexpr int ESZ = (int)sizeof(T);
@@ -500,9 +550,16 @@ __global__ void __launch_bounds__(kFlatThreads, kFlatMinBlocks) dense_flat_kerne
   const int wi = start + (int)(blockIdx.x * (kFlatThreads / 32) + warp) * (CH * 32 * PX);
   if (wi >= p.pixels) return;
 
-  const uint8_t* yb = p.y + (long long)n * p.y_frame_stride;
-  const uint8_t* ub = p.u + (long long)n * p.uv_frame_stride;
-  const uint8_t* vb = FMT == B2_SRC_I420 ? p.v + (long long)n * p.uv_frame_stride : nullptr;
+  const uint8_t *yb, *ub, *vb = nullptr;
+  if (!PACKED && p.y_table != nullptr) {  // a pointer per frame and plane
+    yb = static_cast<const uint8_t*>(p.y_table[n]);
+    ub = static_cast<const uint8_t*>(p.u_table[n]);
+    if constexpr (FMT == B2_SRC_I420) vb = static_cast<const uint8_t*>(p.v_table[n]);
+  } else {
+    yb = p.y + (long long)n * p.y_frame_stride;
+    ub = p.u + (long long)n * p.uv_frame_stride;
+    if constexpr (FMT == B2_SRC_I420) vb = p.v + (long long)n * p.uv_frame_stride;
+  }
   uint32_t yw[CH][1][NW], uw[CH][UVW], vw[CH][UVW];
   // Four rows or more from both ends of the frame (the row estimate may be short by one), every
   // chunk of the warp is whole and none of its windows needs a bounds check.
@@ -511,12 +568,13 @@ __global__ void __launch_bounds__(kFlatThreads, kFlatMinBlocks) dense_flat_kerne
   if (inside) {
 #pragma unroll
     for (int k = 0; k < CH; ++k)
-      flat_load<FMT, PX, true>(p, yb, ub, vb, wi + (k * 32 + lane) * PX, yw[k], uw[k], vw[k]);
+      flat_load<FMT, PX, true, PACKED>(p, yb, ub, vb, wi + (k * 32 + lane) * PX, yw[k], uw[k],
+                                       vw[k]);
   } else {
 #pragma unroll
     for (int k = 0; k < CH; ++k) {
       const int i = wi + (k * 32 + lane) * PX;
-      if (i < p.pixels) flat_load<FMT, PX, false>(p, yb, ub, vb, i, yw[k], uw[k], vw[k]);
+      if (i < p.pixels) flat_load<FMT, PX, false, PACKED>(p, yb, ub, vb, i, yw[k], uw[k], vw[k]);
     }
   }
   unsigned char* wsm = flat_smem + warp * (CH * 32 * 48);
@@ -739,13 +797,18 @@ int launch_t(const DenseLaunch& L, const DenseParams& p, int path, cudaStream_t 
     }
     q.dst = static_cast<T*>(p.dst) + (long long)n0 * p.dst_frame_stride;
     if (path == kPathFlat) {
-      if constexpr (!TABLE) {
+      {
         // chunk 0 may start up to PX - 1 pixels before the frame: one chunk more than the pixels
         const long long chunks = ((long long)p.pixels + PX - 1) / PX + 1;
         const int per_cta = kFlatThreads * kFlatChunks;
         dim3 grid((unsigned)((chunks + per_cta - 1) / per_cta), 1, nn);
         const size_t smem = LAYOUT == B2_NHWC ? (size_t)per_cta * 48 : 0;
-        dense_flat_kernel<FMT, LAYOUT, DTYPE, BGR, ARITH><<<grid, kFlatThreads, smem, stream>>>(q);
+        if (p.flat_packed)
+          dense_flat_kernel<FMT, LAYOUT, DTYPE, BGR, ARITH, true>
+              <<<grid, kFlatThreads, smem, stream>>>(q);
+        else
+          dense_flat_kernel<FMT, LAYOUT, DTYPE, BGR, ARITH, false>
+              <<<grid, kFlatThreads, smem, stream>>>(q);
       }
     } else if (path == kPathVec) {
       const int chunks = (L.width + PX - 1) / PX;
@@ -827,18 +890,22 @@ int launch_dense(const DenseLaunch& L, cudaStream_t stream) {
     if (L.src_format == B2_SRC_I420) vec = vec && mult((long long)(uintptr_t)L.v, uvb);
   }
   int path = vec ? kPathVec : kPathAny;
-  // Packed frames (rows back to back on both sides, even width of at least one chunk, every frame
-  // of the destination on a multiple of two elements, planes a multiple of 16 bytes apart).
+  // A packed destination (rows back to back, even width of at least one chunk, every frame on a
+  // multiple of two elements, planes a multiple of 16 bytes apart) takes the flat kernel, whatever
+  // the pitch and alignment of the source; source rows back to back too select its leaner variant.
   const long long He = L.height & ~1;
   const bool nv12 = L.src_format == B2_SRC_NV12;
-  if (!vec && !table && L.width % 2 == 0 && L.width >= px && L.y_pitch == L.width &&
-      L.uv_pitch == (nv12 ? L.width : L.width / 2) && L.width * He < (1LL << 30) &&
+  const long long cw = nv12 ? L.width : L.width / 2;  // bytes of a chroma row
+  if (!vec && L.width % 2 == 0 && L.width >= px && L.y_pitch >= L.width && L.uv_pitch >= cw &&
+      L.y_pitch * He < (1LL << 30) && L.uv_pitch * He < (1LL << 30) &&
       L.dst_row_pitch == (L.layout == B2_NCHW ? L.width : 3LL * L.width) &&
       mult((long long)(uintptr_t)L.dst, 2 * esz) && mult(L.dst_frame_stride, 2) &&
       (L.layout != B2_NCHW || mult(L.dst_plane_stride * esz, 16))) {
     path = kPathFlat;
+    p.flat_packed = !table && L.y_pitch == L.width && L.uv_pitch == cw;
     p.pixels = (int)(L.width * He);
-    p.chroma_limit = (int)(nv12 ? L.width * (He / 2) : (L.width / 2) * (He / 2));
+    p.y_limit = (int)((He - 1) * L.y_pitch + L.width);
+    p.chroma_limit = (int)((He / 2 - 1) * L.uv_pitch + cw);
     p.w_recip = (unsigned)((1ULL << 32) / (unsigned)L.width);
     p.rows_per_warp = (kFlatChunks * 32 * px + L.width - 1) / L.width + 1;
   }
