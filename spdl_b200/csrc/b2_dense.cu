@@ -737,14 +737,27 @@ __global__ void __launch_bounds__(kAnyThreads, kAnyMinBlocks) dense_any_kernel(c
     }
     uint32_t yw[2][NW], uw[UVW], vw[UVW];
     const uint8_t* y0 = yb + (size_t)(2 * rp) * (unsigned)p.y_pitch;
-    load_window<PX>(y0, x0, we, yw[0]);
-    load_window<PX>(y0 + p.y_pitch, x0, we, yw[1]);
     const size_t uv_off = (size_t)rp * (unsigned)p.uv_pitch;
-    if constexpr (FMT == B2_SRC_NV12) {
-      load_window<UVB>(ub + uv_off, x0, we, uw);
+    if (rp >= 1 && 2 * rp + 4 <= p.height) {
+      // Not the first or last row pair: the few bytes an aligned vector reads before or behind
+      // a row belong to the neighbouring rows of the same plane, so no bounds are checked.
+      load_window_inside<PX>(y0, x0, yw[0]);
+      load_window_inside<PX>(y0 + p.y_pitch, x0, yw[1]);
+      if constexpr (FMT == B2_SRC_NV12) {
+        load_window_inside<UVB>(ub + uv_off, x0, uw);
+      } else {
+        load_window_inside<UVB>(ub + uv_off, x0 / 2, uw);
+        load_window_inside<UVB>(vb + uv_off, x0 / 2, vw);
+      }
     } else {
-      load_window<UVB>(ub + uv_off, x0 / 2, we / 2, uw);
-      load_window<UVB>(vb + uv_off, x0 / 2, we / 2, vw);
+      load_window<PX>(y0, x0, we, yw[0]);
+      load_window<PX>(y0 + p.y_pitch, x0, we, yw[1]);
+      if constexpr (FMT == B2_SRC_NV12) {
+        load_window<UVB>(ub + uv_off, x0, we, uw);
+      } else {
+        load_window<UVB>(ub + uv_off, x0 / 2, we / 2, uw);
+        load_window<UVB>(vb + uv_off, x0 / 2, we / 2, vw);
+      }
     }
     (void)vw;
     convert_chunk<FMT, LAYOUT, DTYPE, BGR, ARITH>(p.mat, p.sb, yw, uw, vw, out);
