@@ -538,6 +538,23 @@ def test_pack_host_packs_items_of_different_sizes(monkeypatch, threads):
                           offsets.ctypes.data, len(items)) == 1
 
 
+def test_resize_host_images_rejects_what_it_cannot_batch():
+    """Argument checks of ``resize_host_images`` come before any CUDA call."""
+    import spdl_b200.io as io
+
+    cfg = io.cuda_config(0)
+    rgb = np.zeros((8, 6, 3), np.uint8)
+    for images, kw in (([], {}),                                          # nothing to do
+                       ([rgb], dict(src_format="gray8")),                # unknown format
+                       ([rgb.astype(np.float32)], {}),                    # not bytes
+                       ([rgb[..., :2]], {}),                              # two channels
+                       ([np.zeros((9, 6), np.uint8)], dict(src_format="i420")),   # odd height
+                       ([np.zeros((12, 7), np.uint8)], dict(src_format="nv12")),  # odd width
+                       ([rgb], dict(src_format="i420"))):                # planes expected
+        with pytest.raises(RuntimeError):
+            io.resize_host_images(images, device_config=cfg, resize=(4, 4), **kw)
+
+
 def test_copy_rows_packs_selected_rows_of_every_frame():
     """``b2_copy_rows``: the host-side packing step of a row-sparse upload (no CUDA call)."""
     L = _lib.lib()
