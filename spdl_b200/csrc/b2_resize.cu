@@ -29,9 +29,13 @@
 //            fp32 instructions) and blends; a group goes out as vector stores when it lies inside
 //            the image and the destination is 16-byte aligned, element by element otherwise, so
 //            no destination pointer, stride or width has an alignment requirement.
+//            Interleaved RGB sources: a lane converts single pixels, neighbouring lanes
+//            neighbouring columns, whose taps lie a few bytes apart in the staged rows (far fewer
+//            shared-memory wavefronts per tap load); elements are stored one by one.
 #include <cuda_fp16.h>
 
 #include <atomic>
+#include <type_traits>
 
 #include "b2_common.cuh"
 
@@ -156,6 +160,11 @@ __device__ __forceinline__ uint32_t lds_u8(uint32_t a) {
 __device__ __forceinline__ uint32_t lds_u16(uint32_t a) {
   uint32_t v;
   asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
   return v;
 }
 __device__ __forceinline__ uint4 lds_v4(uint32_t a) {
@@ -321,6 +330,33 @@ __device__ __forceinline__ void convert_group(const ResizeParams& p, const MatPa
   }
 }
 
+// One output pixel (float outputs: their elements are stored one by one, so neighbouring lanes can
+// take neighbouring pixels, whose taps lie a few bytes apart in the staged rows: one or two
+// shared-memory wavefronts per tap load instead of one per 128 bytes of a span that is four times
+// as long).  The column table is indexed by the column here.  q[c]: where the lane's column 0 of
+// this pass goes for colour channel c; K: the pixel is column 32 * K further on (a compile-time
+// offset).  PAD: columns outside [cin0, cin1) exist and take the pad colour.
+template <int FMT, int LAYOUT, int DTYPE, int ARITH, bool UV16, bool PAD, int K, typename T>
+__device__ __forceinline__ void convert_pixel(const ResizeParams& p, const MatPairs<ARITH>& m,
+                                              const RowInfo& in, uint32_t xoffs, uint32_t xw,
+                                              T* const (&q)[3], int ox, int cin0, int cin1) {
+  constexpr int kStep = 32 * K * (LAYOUT == B2_NCHW ? 1 : 3);  // elements
+  const uint4 e = lds_v4(xoffs + 16u * (uint32_t)ox);
+  const float w1 = __uint_as_float(lds_u32(xw + 4u * (uint32_t)ox));
+  const float2 wx1 = dup2(w1), wx0 = dup2(__fsub_rn(1.0f, w1));
+  float2 t0[3], t1[3];  // [channel] of tap column x0 / x1, lanes = {row y0, row y1}
+  convert_taps<FMT, ARITH, UV16>(m, in, e.x, e.z, t0);
+  convert_taps<FMT, ARITH, UV16>(m, in, e.y, e.w, t1);
+  const bool inside = !PAD || (ox >= cin0 && ox < cin1);
+#pragma unroll
+  for (int c = 0; c < 3; ++c) {
+    const float2 tb = x2_fma(wx1, t1[c], x2_mul(wx0, t0[c]));
+    float v = finish<DTYPE>(p, __fmaf_rn(in.wy1, tb.y, __fmul_rn(in.wy0, tb.x)), c);
+    if constexpr (PAD) v = inside ? v : finish<DTYPE>(p, p.ch_pad[c], c);
+    store_elem<DTYPE>(q[c] + kStep, v);
+  }
+}
+
 template <int FMT, int LAYOUT, int DTYPE, int ARITH>
 __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kernel(const ResizeParams p) {
   using T = typename OutT<DTYPE>::type;
@@ -401,6 +437,8 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
   // I420's second and third plane have rows half as wide, and slots half as large
   constexpr bool kHalfSlots = FMT == B2_SRC_I420;
   constexpr bool kLocateAhead = FMT != B2_SRC_RGB_INTERLEAVED;
+  // a lane converts single pixels (convert_pixel) instead of groups of four
+  constexpr bool kLanePixels = FMT == B2_SRC_RGB_INTERLEAVED;
   if (bhi - blo + 15 > p.span_cap ||
       cxhi - cxlo + 15 > (kHalfSlots ? p.span_cap2 : p.span_cap)) {
     report(B2_STATUS_IMAGE_TOO_WIDE);
@@ -575,7 +613,7 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
           c1 = x1;
         }
         const int grp = ox >> 2, k = ox & 3;
-        reinterpret_cast<uint4*>(smem + (xoffs - sbase))[k * groups + grp] =
+        reinterpret_cast<uint4*>(smem + (xoffs - sbase))[kLanePixels ? ox : k * groups + grp] =
             make_uint4(x0, x1, c0, c1);
         reinterpret_cast<float*>(smem + (xw - sbase))[ox] = ax.w1;
       }
@@ -602,6 +640,55 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
     // interleaved chroma pairs can be fetched with one 16-bit load when the staged rows kept an
     // even address (they do whenever the source plane and pitch are even)
     const bool uv16 = FMT == B2_SRC_NV12 && !s_odd_chroma;
+    if constexpr (kLanePixels) {
+      // a warp (or two) per output row, its lanes on 32 consecutive columns per pass
+      if (r >= rows_here) continue;
+      const int oy = oy0 + r;
+      T* const drow = dimg + (long long)oy * p.row_stride;
+      const int nsub = kResizeWarps / p.rows;  // warps that share the row take blocks of 128
+      if (oy < rin0 || oy >= rin1) {           // a row of padding
+        for (int ox = g0; ox < p.out_w; ox += 32 * nsub)
+#pragma unroll
+          for (int c = 0; c < 3; ++c)
+            store_elem<DTYPE>(drow + p.chan_off[c] + (long long)ox * p.px_stride,
+                              finish<DTYPE>(p, p.ch_pad[c], c));
+        continue;
+      }
+      const RowInfo in = s_rows[r];
+      constexpr int kPx = LAYOUT == B2_NCHW ? 1 : 3;  // elements between pixels of a channel
+      auto row_pixels = [&](auto pairs16, auto pad) {
+        constexpr bool U16 = decltype(pairs16)::value, PAD = decltype(pad)::value;
+        // columns lane, lane + 32, lane + 64, lane + 96 of a block: four independent pixels
+        const int first = lane + 128 * (warp / p.rows);
+        T* q[3];
+#pragma unroll
+        for (int c = 0; c < 3; ++c) q[c] = drow + p.chan_off[c] + (long long)first * kPx;
+        for (int ox = first; ox < p.out_w; ox += 128 * nsub) {
+          convert_pixel<FMT, LAYOUT, DTYPE, ARITH, U16, PAD, 0>(p, m, in, xoffs, xw, q, ox, cin0,
+                                                                cin1);
+          if (ox + 32 < p.out_w)
+            convert_pixel<FMT, LAYOUT, DTYPE, ARITH, U16, PAD, 1>(p, m, in, xoffs, xw, q, ox + 32,
+                                                                  cin0, cin1);
+          if (ox + 64 < p.out_w)
+            convert_pixel<FMT, LAYOUT, DTYPE, ARITH, U16, PAD, 2>(p, m, in, xoffs, xw, q, ox + 64,
+                                                                  cin0, cin1);
+          if (ox + 96 < p.out_w)
+            convert_pixel<FMT, LAYOUT, DTYPE, ARITH, U16, PAD, 3>(p, m, in, xoffs, xw, q, ox + 96,
+                                                                  cin0, cin1);
+#pragma unroll
+          for (int c = 0; c < 3; ++c) q[c] += 128 * nsub * kPx;
+        }
+      };
+      const bool pad = cin0 > 0 || cin1 < p.out_w;
+      if (uv16) {
+        if (pad) row_pixels(std::true_type{}, std::true_type{});
+        else row_pixels(std::true_type{}, std::false_type{});
+      } else {
+        if (pad) row_pixels(std::false_type{}, std::true_type{});
+        else row_pixels(std::false_type{}, std::false_type{});
+      }
+      continue;
+    }
     if (p.flat) {
       // The row's groups do not fill whole warps: the CTA's lanes take the (row, group) items of
       // the tile in turn instead, so that only the tile's last warp has idle lanes.
