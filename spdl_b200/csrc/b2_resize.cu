@@ -29,7 +29,7 @@
 //            fp32 instructions) and blends; a group goes out as vector stores when it lies inside
 //            the image and the destination is 16-byte aligned, element by element otherwise, so
 //            no destination pointer, stride or width has an alignment requirement.
-//            Interleaved RGB sources: a lane converts single pixels, neighbouring lanes
+//            RGB sources (no colour conversion): a lane converts single pixels, neighbouring lanes
 //            neighbouring columns, whose taps lie a few bytes apart in the staged rows (far fewer
 //            shared-memory wavefronts per tap load); elements are stored one by one.
 #include <cuda_fp16.h>
@@ -438,7 +438,7 @@ __global__ void __launch_bounds__(kResizeThreads, kResizeMinBlocks) resize_kerne
   constexpr bool kHalfSlots = FMT == B2_SRC_I420;
   constexpr bool kLocateAhead = FMT != B2_SRC_RGB_INTERLEAVED;
   // a lane converts single pixels (convert_pixel) instead of groups of four
-  constexpr bool kLanePixels = FMT == B2_SRC_RGB_INTERLEAVED;
+  constexpr bool kLanePixels = FMT == B2_SRC_RGB_INTERLEAVED || FMT == B2_SRC_RGB_PLANAR;
   if (bhi - blo + 15 > p.span_cap ||
       cxhi - cxlo + 15 > (kHalfSlots ? p.span_cap2 : p.span_cap)) {
     report(B2_STATUS_IMAGE_TOO_WIDE);
