@@ -188,6 +188,35 @@ def test_rgb_sources_ragged(cuda_cfg, fmt, layout, dtype):
     _compare(got, want, dtype)
 
 
+@pytest.mark.parametrize("fmt", ["rgb_planar", "rgb24"])
+@pytest.mark.parametrize("out_w,mode", [(97, None), (160, "pad"), (300, "crop")])
+def test_wide_rgb_sources_take_two_row_tiles(cuda_cfg, fmt, out_w, mode):
+    """RGB sources wide enough for two-row tiles (two warps share an output row and take
+    alternate blocks of 128 columns), with output widths that end inside a block, letterbox bars
+    and a cover crop."""
+    import spdl_b200.io as io
+
+    rng = np.random.default_rng(77 + out_w)
+    ws, hs = np.array([4000, 3600, 2200]), np.array([12, 30, 21])
+    sizes = 3 * ws * hs
+    offs = np.concatenate([[0], np.cumsum(sizes)[:-1]])
+    data = rng.integers(0, 256, int(sizes.sum()), dtype=np.uint8)
+    kw = dict(scale_mode=mode) if mode else {}
+    descs, out = io.make_image_descs(ws, hs, src_format=fmt, offsets=offs, resize=(out_w, 11), **kw)
+    for layout, dtype in (("NCHW", "uint8"), ("NHWC", "float32")):
+        norm = dict(mean=MEAN, std=STD) if dtype != "uint8" else {}
+        buf = io.convert_resize(_dev(data), _dev(descs.view(np.uint8)), out_size=out,
+                                max_src_w=int(ws.max()), device_config=cuda_cfg, src_format=fmt,
+                                layout=layout, dtype=dtype, pad_color=(12.0, 200.0, 77.0),
+                                sync=True, **norm)
+        want = oracle.convert_resize(
+            data, descs, out_w=out[0], out_h=out[1],
+            src_format=oracle.RGBP if fmt == "rgb_planar" else oracle.RGBI,
+            layout=oracle.NCHW if layout == "NCHW" else oracle.NHWC, dtype=_O_DT[dtype],
+            pad_value=(12.0, 200.0, 77.0), sb=oracle.scale_bias(MEAN, STD) if norm else None)
+        _compare(io.to_torch(buf).cpu().numpy(), want, dtype)
+
+
 def test_unaligned_output_width(cuda_cfg):
     """out_w not a multiple of 4 takes the element-store path."""
     import spdl_b200.io as io
