@@ -138,6 +138,8 @@ def test_long_sweep(cuda_cfg):
         test_dense_random_cases(cuda_cfg, seed)
         test_resize_random_cases(cuda_cfg, seed)
         test_dense_random_memory_layouts(cuda_cfg, seed)
+        if seed % 16 == 0:
+            _dense_memory_layout_case(cuda_cfg, seed, larger=True)
 
 
 @pytest.mark.parametrize("seed", range(48))
@@ -146,6 +148,18 @@ def test_dense_random_memory_layouts(cuda_cfg, seed):
     source pitch, and a destination at a random element offset with a random frame stride: every
     alignment path of the dense kernels against the oracle, with sentinel checks around the
     output."""
+    _dense_memory_layout_case(cuda_cfg, seed, larger=False)
+
+
+@pytest.mark.parametrize("seed", range(32))
+def test_dense_random_memory_layouts_larger_frames(cuda_cfg, seed):
+    """The same with frames of tens to a hundred rows and widths up to 1400: enough rows for the
+    kernels' unchecked interior paths, row ends inside a warp's run of pixels, several warps per
+    row."""
+    _dense_memory_layout_case(cuda_cfg, 500 + seed, larger=True)
+
+
+def _dense_memory_layout_case(cuda_cfg, seed, larger):
     import ctypes
 
     import torch
@@ -154,8 +168,12 @@ def test_dense_random_memory_layouts(cuda_cfg, seed):
 
     r = np.random.default_rng(12000 + seed)
     n = int(r.integers(1, 4))
-    w = int(r.choice([16, 32, 48, 64, 100, 130, 200, 31, 854]))
-    h = int(r.integers(1, 9)) * 2
+    if larger:
+        w = int(r.integers(16, 1400))
+        h = int(r.integers(9, 60)) * 2
+    else:
+        w = int(r.choice([16, 32, 48, 64, 100, 130, 200, 31, 854]))
+        h = int(r.integers(1, 9)) * 2
     h2 = h * 3 // 2
     layout = str(r.choice(["NCHW", "NHWC"]))
     dtype = str(r.choice(["uint8", "float32", "bfloat16"]))
