@@ -130,14 +130,32 @@ def convert_frames(frames: Frames | Sequence[Frames],
     buf = CPUBuffer(full, "u", 1, storage)
     flat = np.frombuffer((__import__("ctypes").c_uint8 * max(buf.nbytes, 1)).from_address(
         buf.data_ptr), np.uint8, count=buf.nbytes)
+    # Planes whose rows lie back to back are packed by one call of the library's host helper,
+    # which deals them out to several threads when the batch is several MiB long (the reference
+    # copies frame by frame on one thread: av_image_copy_to_buffer in
+    # src/libspdl/core/detail/ffmpeg/conversion.cpp:171-216); pitched planes row by row here.
     pos = 0
     shapes = ref._plane_shapes()
+    srcs, sizes, offsets = [], [], []
     for fr in batch:
         for planes in fr.planes:
             for arr, (rows, cols) in zip(planes, shapes):
                 n = rows * cols
-                flat[pos:pos + n].reshape(rows, cols)[...] = arr[:rows, :cols]
+                view = arr[:rows, :cols]
+                if view.dtype == np.uint8 and view.flags.c_contiguous:
+                    srcs.append(view.ctypes.data)
+                    sizes.append(n)
+                    offsets.append(pos)
+                else:
+                    flat[pos:pos + n].reshape(rows, cols)[...] = view
                 pos += n
+    if srcs:
+        from .. import _lib
+
+        s_arr, z_arr, o_arr = (np.array(v, t) for v, t in ((srcs, np.uint64), (sizes, np.int64),
+                                                           (offsets, np.int64)))
+        _lib.check(_lib.lib().b2_pack_host(buf.data_ptr, s_arr.ctypes.data, z_arr.ctypes.data,
+                                           o_arr.ctypes.data, len(srcs)))
     shape = full
     if ref.media == "image":
         shape = (shape[0], *shape[2:])
