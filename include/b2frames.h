@@ -269,9 +269,11 @@ B2_API int b2_copy_rows(void* dst, int64_t dst_frame_stride, const void* src, in
                  int num_frames);
 
 /* Host helper (no CUDA call): memcpy of nbytes, cut into slices for several host threads when it
- * is several MiB long (same thread count as b2_copy_rows).  The staging copy of one large host
- * array into page-locked memory; the reference pins such arrays with Tensor.pin_memory() in
- * spdl.io.transfer_tensor (src/spdl/io/_transfer.py:84), a single-threaded copy. */
+ * is several MiB long (same thread count as b2_copy_rows).  Like b2_copy_rows and b2_pack_host
+ * it writes with streaming stores: it is the staging copy of host data into page-locked memory,
+ * which the copy engine reads next, and an upload right after a cached copy runs at half the
+ * link's rate.  The reference pins such arrays with Tensor.pin_memory() in
+ * spdl.io.transfer_tensor (src/spdl/io/_transfer.py:84). */
 B2_API int b2_copy_host(void* dst, const void* src, size_t nbytes);
 
 /* Host helper (no CUDA call): packs num_items host arrays of different sizes into one buffer,

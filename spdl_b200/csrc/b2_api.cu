@@ -6,6 +6,9 @@
 #include <cstdlib>
 #include <cstring>
 #include <thread>
+#if defined(__x86_64__)
+#include <emmintrin.h>
+#endif
 #include <vector>
 
 #include "b2_common.cuh"
@@ -372,20 +375,48 @@ static long long host_copy_threads() {
   return half < 1 ? 1 : (half > 8 ? 8 : half);
 }
 
+// A copy into a staging buffer that the copy engine reads next: streaming stores (the data goes
+// to memory instead of lingering in this core's cache, from where the engine would have to fetch
+// it line by line: an upload right after a cached copy ran at half the link's rate).
+static void stream_copy(char* dst, const char* src, size_t n) {
+#if defined(__x86_64__)
+  if (n >= 1024) {
+    const size_t head = (16 - ((uintptr_t)dst & 15)) & 15;
+    memcpy(dst, src, head);
+    dst += head; src += head; n -= head;
+    const size_t body = n & ~(size_t)63;
+    for (size_t i = 0; i < body; i += 64) {
+      const __m128i a0 = _mm_loadu_si128(reinterpret_cast<const __m128i*>(src + i));
+      const __m128i a1 = _mm_loadu_si128(reinterpret_cast<const __m128i*>(src + i + 16));
+      const __m128i a2 = _mm_loadu_si128(reinterpret_cast<const __m128i*>(src + i + 32));
+      const __m128i a3 = _mm_loadu_si128(reinterpret_cast<const __m128i*>(src + i + 48));
+      _mm_stream_si128(reinterpret_cast<__m128i*>(dst + i), a0);
+      _mm_stream_si128(reinterpret_cast<__m128i*>(dst + i + 16), a1);
+      _mm_stream_si128(reinterpret_cast<__m128i*>(dst + i + 32), a2);
+      _mm_stream_si128(reinterpret_cast<__m128i*>(dst + i + 48), a3);
+    }
+    _mm_sfence();
+    memcpy(dst + body, src + body, n - body);
+    return;
+  }
+#endif
+  memcpy(dst, src, n);
+}
+
 // memcpy by several host threads: one per 2 MiB at least, slices cut on 4 KiB boundaries.
 static void host_copy(void* dst, const void* src, size_t n) {
   long long threads = (long long)(n / (2u << 20));
   const long long cap = host_copy_threads();
   if (threads > cap) threads = cap;
   if (threads <= 1) {
-    memcpy(dst, src, n);
+    stream_copy(static_cast<char*>(dst), static_cast<const char*>(src), n);
     return;
   }
   const size_t slice = ((n / (size_t)threads) + 4095) & ~(size_t)4095;
   auto part = [=](size_t first) {
     if (first < n)
-      memcpy(static_cast<char*>(dst) + first, static_cast<const char*>(src) + first,
-             n - first < slice ? n - first : slice);
+      stream_copy(static_cast<char*>(dst) + first, static_cast<const char*>(src) + first,
+                  n - first < slice ? n - first : slice);
   };
   std::vector<std::thread> pool;
   pool.reserve((size_t)threads - 1);
@@ -431,7 +462,8 @@ B2_API int b2_pack_host(void* dst, const void* const* srcs, const int64_t* sizes
   auto copy_items = [=](int first, int last) {
     for (int i = first; i < last; ++i)
       if (sizes[i])
-        memcpy(static_cast<char*>(dst) + dst_offsets[i], srcs[i], (size_t)sizes[i]);
+        stream_copy(static_cast<char*>(dst) + dst_offsets[i], static_cast<const char*>(srcs[i]),
+                    (size_t)sizes[i]);
   };
   if (threads == 1) {
     copy_items(0, num_items);
@@ -483,9 +515,10 @@ B2_API int b2_copy_rows(void* dst, int64_t dst_frame_stride, const void* src, in
       int run = 1;
       if (src_pitch == row_bytes)
         while (it + run < frame_end && rows[i + run] == rows[i] + run) ++run;
-      memcpy(static_cast<char*>(dst) + f * dst_frame_stride + (long long)i * row_bytes,
-             static_cast<const char*>(src) + f * src_frame_stride + (long long)rows[i] * src_pitch,
-             (size_t)row_bytes * run);
+      stream_copy(static_cast<char*>(dst) + f * dst_frame_stride + (long long)i * row_bytes,
+                  static_cast<const char*>(src) + f * src_frame_stride +
+                      (long long)rows[i] * src_pitch,
+                  (size_t)row_bytes * run);
       it += run;
     }
   };

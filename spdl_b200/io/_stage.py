@@ -47,11 +47,11 @@ class FrameStage:
     kernel finds the rows through the maps of :func:`touched_rows`.  The result is identical.
     ``sparse_upload="auto"`` does so when the geometry reads less than 85 % of a frame's bytes.
     Frames in pageable memory are first copied into the page-locked staging buffer by several
-    host threads (``b2_copy_host`` for whole frames, ``b2_copy_rows`` for the touched rows) and uploaded from there
-    asynchronously; that copy, at about 30 GB/s, is what bounds the stage (measured on a B200
-    host, 16 cores, two worker threads: 4K -> 224x224 2.4 k frames/s whole, 5-6 k sparse; 720p ->
-    256x256 22 k whole, 24-26 k sparse; the driver's own staging of pageable sources gave 0.8 k
-    and 7 k).
+    host threads with streaming stores (``b2_copy_host`` for whole frames, ``b2_copy_rows`` for
+    the touched rows) and uploaded from there asynchronously; that copy, at about 45 GB/s, is what
+    bounds the stage (measured on a B200 host, 16 cores, two worker threads: 4K -> 224x224 3.5 k
+    frames/s whole, 11 k sparse; 720p -> 256x256 33 k whole, 36 k sparse; the driver's own
+    staging of pageable sources gave 0.8 k and 7 k).
     """
 
     def __init__(self, *, src_format: str = "i420", layout: str = "NCHW", dtype: str = "float32",
